@@ -1,0 +1,107 @@
+/* C ABI of the B200 (sm_100a) routed-expert MoE kernels.
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" is a CUDA device
+ * pointer valid on the current device; `stream` is a cudaStream_t passed as
+ * void*.  Calls enqueue work on `stream` and return without synchronising;
+ * they allocate nothing and own nothing: inputs, outputs and workspaces belong
+ * to the caller.  Return value: 0 on success, a negative UMAQ_ERR_* code
+ * otherwise (umaq_last_error() then holds a message for the calling thread).
+ *
+ * The entry points are what a host binding of the UMA-QMoE reference calls in
+ * place of its pybind11 extension (src/uma_qmoe/native/packed_q4_binding.cpp:490-515
+ * in the reference: q4_linear, q8_linear, q4_moe_forward, q4_moe_prefill,
+ * q8_moe_forward, q8_moe_prefill).
+ */
+#ifndef UMAQ_B200_H
+#define UMAQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { UMAQ_ENC_Q4 = 0, UMAQ_ENC_Q8 = 1, UMAQ_ENC_BF16 = 2 };
+
+enum {
+  UMAQ_OK = 0,
+  UMAQ_ERR_BAD_ARGUMENT = -1,
+  UMAQ_ERR_WORKSPACE = -2,
+  UMAQ_ERR_LAUNCH = -3,
+  UMAQ_ERR_DEVICE_TIMEOUT = -4,
+  UMAQ_ERR_UNSUPPORTED = -5
+};
+
+/* One staged MoE layer: all experts of a projection concatenated in expert
+ * order, each expert's tensor in its canonical pack bytes (row-major [rows, K],
+ * K contiguous; Q4: K/2 bytes per row, low nibble first; Q8: K int8; BF16: 2K
+ * bytes) and, for Q4/Q8, float32 scales [rows, K/128].  This is the device
+ * layout the reference's backend builds in
+ * src/uma_qmoe/native_backend.py:374-455 (Q4), :769-842 (Q8), :876-956 (BF16,
+ * there as one stacked gate_up tensor; here gate and up stay separate). */
+typedef struct umaq_layer {
+  const void* gate;          /* device [E, I, K=H] codes */
+  const void* up;            /* device [E, I, K=H] codes */
+  const void* down;          /* device [E, H, K=I] codes */
+  const float* gate_scales;  /* device [E, I, H/128] or NULL for BF16 */
+  const float* up_scales;
+  const float* down_scales;  /* device [E, H, I/128] or NULL for BF16 */
+  int32_t encoding;          /* UMAQ_ENC_* */
+  int32_t num_experts;       /* E */
+  int32_t hidden;            /* H */
+  int32_t intermediate;      /* I */
+} umaq_layer;
+
+/* Qwen shared expert (BF16 nn.Linear weights) and its sigmoid gate vector:
+ * src/uma_qmoe/qwen_compressed_loader.py:72,82-85. */
+typedef struct umaq_shared_expert {
+  const void* gate;       /* device bf16 [S, H] */
+  const void* up;         /* device bf16 [S, H] */
+  const void* down;       /* device bf16 [H, S] */
+  const void* gate_vec;   /* device bf16 [H] (shared_expert_gate.weight) */
+  int32_t intermediate;   /* S */
+} umaq_shared_expert;
+
+/* "sm_100a;<git-independent build id>" into buf; returns bytes needed. */
+int umaq_build_info(char* buf, int len);
+/* Message of the last failing call made by this thread ("" if none). */
+const char* umaq_last_error(void);
+/* Number of SMs of the current device (the grid of the persistent kernels). */
+int umaq_sm_count(void);
+
+/* ---- batch-1 decode --------------------------------------------------------
+ * out[H] = sum over the top_k routes of w * Down_e(SiLU(Gate_e x) * Up_e x),
+ * accumulated like the reference's CPU correctness path (ascending expert
+ * number, BF16 running sum); with `shared` != NULL additionally
+ * + sigmoid(x . gate_vec) * SharedExpert(x) with BF16 nn.Linear roundings.
+ * Replaces q4_moe_forward / q8_moe_forward
+ * (src/uma_qmoe/native/packed_q4_binding.cpp:197-265, :407-440) and the Qwen
+ * per-expert q4_linear / q8_linear loops (src/uma_qmoe/native_backend.py:319-372,
+ * :722-753).
+ *
+ * workspace: umaq_decode_workspace_bytes() bytes, 256-byte aligned, zeroed once
+ * by the caller before its first use; calls sharing a workspace must not overlap
+ * on the device.  Word 2 (uint32 at byte offset 8) is a sticky device-side
+ * status: 0, or a UMAQ_ERR_* code if a bounded wait gave up or an expert index
+ * was out of range (then re-zero the workspace before reusing it). */
+size_t umaq_decode_workspace_bytes(int top_k, int intermediate, int shared_intermediate);
+int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /* may be NULL */,
+                    const void* hidden_bf16 /* device [H] */,
+                    const void* expert_indices /* device [top_k] */, int indices_are_int64,
+                    const float* routing_weights /* device [top_k] */, int top_k,
+                    void* out_bf16 /* device [H] */, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* ---- device-side packer -------------------------------------------------------
+ * Quantises `elements` (a multiple of 128) BF16 values, row-major, into the
+ * canonical Q4 (elements/2 bytes) or Q8 (elements bytes) codes and elements/128
+ * float32 scales, bit-identical to the reference's host packer
+ * (src/uma_qmoe/q4.py:136-165, src/uma_qmoe/target_pack.py:92-112). */
+int umaq_quantize_groups(const void* src_bf16 /* device */, long long elements, int encoding,
+                         void* codes /* device */, float* scales /* device */, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UMAQ_B200_H */

@@ -45,3 +45,37 @@ def ulp_bf16(x: torch.Tensor) -> torch.Tensor:
     """Size of one BF16 ulp at |x| (float32)."""
     a = x.float().abs().clamp_min(2.0 ** -126)
     return torch.exp2(torch.floor(torch.log2(a)) - 7)
+
+
+# ---- device staging (GPU tests) ----------------------------------------------------------
+
+def stage_layer(experts: dict, num_experts: int, hidden: int, inter: int, encoding: str, device):
+    """Concatenate canonical bytes of the given experts {e: (gate, up, down) EncodedMatrix}
+    into a DeviceLayer; experts not listed stay zero (scales 1)."""
+    from uma_qmoe_b200.formats import row_bytes
+    from uma_qmoe_b200.ops import DeviceLayer
+
+    q = encoding != "bf16_le"
+    gu = np.zeros((num_experts, inter * row_bytes(encoding, hidden)), np.uint8)
+    up = np.zeros_like(gu)
+    dn = np.zeros((num_experts, hidden * row_bytes(encoding, inter)), np.uint8)
+    gs = np.ones((num_experts, inter * hidden // 128), np.float32)
+    us = np.ones_like(gs)
+    ds = np.ones((num_experts, hidden * inter // 128), np.float32)
+    for e, (g, u, d) in experts.items():
+        gu[e] = np.frombuffer(g.data.tobytes(), np.uint8)
+        up[e] = np.frombuffer(u.data.tobytes(), np.uint8)
+        dn[e] = np.frombuffer(d.data.tobytes(), np.uint8)
+        if q:
+            gs[e], us[e], ds[e] = g.scales, u.scales, d.scales
+    dev = lambda a: torch.from_numpy(a).to(device)
+    return DeviceLayer(encoding, num_experts, hidden, inter, dev(gu), dev(up), dev(dn),
+                       dev(gs) if q else None, dev(us) if q else None, dev(ds) if q else None)
+
+
+def assert_parity(actual: torch.Tensor, expected: torch.Tensor, max_abs: float = 2e-2, cosine: float = 0.9999):
+    """The activation tolerance of the operator contract: max-abs <= 2e-2 and cosine >= 0.9999
+    against the CPU correctness path."""
+    m = orc.compare(actual, expected)
+    assert m["max_abs"] <= max_abs and m["cosine"] >= cosine, m
+    return m

@@ -1,0 +1,125 @@
+"""Thin torch-facing wrappers over the C ABI: they check shapes and dtypes (the
+job ``TORCH_CHECK`` does in the reference's
+``src/uma_qmoe/native/packed_q4_binding.cpp:12-58,137-160,208-253``), pass raw
+device pointers and the current stream, and never compute anything themselves.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _native
+from .formats import ENC_BF16, ENC_Q4, ENC_Q8, ENCODING_ID
+
+
+@dataclass
+class DeviceLayer:
+    """One staged layer: every expert's canonical bytes concatenated per projection."""
+
+    encoding: str
+    num_experts: int
+    hidden: int
+    intermediate: int
+    gate: torch.Tensor
+    up: torch.Tensor
+    down: torch.Tensor
+    gate_scales: Optional[torch.Tensor] = None
+    up_scales: Optional[torch.Tensor] = None
+    down_scales: Optional[torch.Tensor] = None
+
+    @property
+    def tensors(self) -> tuple[torch.Tensor, ...]:
+        return tuple(t for t in (self.gate, self.gate_scales, self.up, self.up_scales, self.down,
+                                 self.down_scales) if t is not None)
+
+    @property
+    def device_storage_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors)
+
+    def struct(self) -> _native.Layer:
+        ptr = lambda t: None if t is None else t.data_ptr()
+        return _native.Layer(ptr(self.gate), ptr(self.up), ptr(self.down), ptr(self.gate_scales),
+                             ptr(self.up_scales), ptr(self.down_scales), ENCODING_ID[self.encoding],
+                             self.num_experts, self.hidden, self.intermediate)
+
+
+@dataclass
+class DeviceSharedExpert:
+    gate: torch.Tensor      # [S, H] bf16
+    up: torch.Tensor        # [S, H] bf16
+    down: torch.Tensor      # [H, S] bf16
+    gate_vec: torch.Tensor  # [H] or [1, H] bf16
+
+    def struct(self) -> _native.SharedExpert:
+        return _native.SharedExpert(self.gate.data_ptr(), self.up.data_ptr(), self.down.data_ptr(),
+                                    self.gate_vec.data_ptr(), int(self.gate.shape[0]))
+
+
+def _stream(device: torch.device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda_bf16(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA tensor; there is no CPU path")
+    if t.dtype != torch.bfloat16:
+        raise RuntimeError(f"{what} must be BF16")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{what} must be contiguous")
+
+
+def decode_workspace(layer: DeviceLayer, top_k: int, shared: Optional[DeviceSharedExpert],
+                     device: torch.device) -> torch.Tensor:
+    """Zeroed workspace for :func:`moe_decode` (one per stream of calls)."""
+    s_inter = int(shared.gate.shape[0]) if shared is not None else 0
+    n = _native.lib().umaq_decode_workspace_bytes(top_k, layer.intermediate, s_inter)
+    return torch.zeros((n + 255) // 256 * 256, dtype=torch.uint8, device=device)
+
+
+def moe_decode(layer: DeviceLayer, hidden: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+               workspace: torch.Tensor, shared: Optional[DeviceSharedExpert] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token through the routed experts (and the Qwen shared expert)."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    if hidden.numel() != layer.hidden:
+        raise RuntimeError(f"decode path takes exactly one token of hidden size {layer.hidden}")
+    top_k = indices.numel()
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("expert_indices must use int32 or int64")
+    if weights.dtype != torch.float32 or weights.numel() != top_k:
+        raise RuntimeError("routing_weights must be float32 with one weight per route")
+    if not (indices.is_contiguous() and weights.is_contiguous()):
+        raise RuntimeError("routes must be contiguous")
+    if out is None:
+        out = torch.empty_like(hidden)
+    code = _native.lib().umaq_moe_decode(
+        C.byref(layer.struct()), C.byref(shared.struct()) if shared is not None else None,
+        hidden.data_ptr(), indices.data_ptr(), int(indices.dtype == torch.int64), weights.data_ptr(), top_k,
+        out.data_ptr(), workspace.data_ptr(), workspace.numel(), _stream(hidden.device))
+    _native.check(code, "umaq_moe_decode")
+    return out
+
+
+def workspace_status(workspace: torch.Tensor) -> int:
+    """Sticky device-side status word of a workspace (synchronises)."""
+    return int(workspace[8:12].view(torch.int32).item())
+
+
+def quantize_groups(values: torch.Tensor, encoding: str) -> tuple[torch.Tensor, torch.Tensor]:
+    """Device-side packer: BF16 tensor -> (canonical codes as uint8/int8, float32 scales)."""
+    _require_cuda_bf16(values, "values")
+    n = values.numel()
+    enc = ENCODING_ID[encoding]
+    if enc == ENC_BF16:
+        raise RuntimeError("bf16_le needs no quantisation")
+    codes = torch.empty(n // 2 if enc == ENC_Q4 else n, dtype=torch.uint8 if enc == ENC_Q4 else torch.int8,
+                        device=values.device)
+    scales = torch.empty(n // 128, dtype=torch.float32, device=values.device)
+    code = _native.lib().umaq_quantize_groups(values.data_ptr(), n, enc, codes.data_ptr(), scales.data_ptr(),
+                                              _stream(values.device))
+    _native.check(code, "umaq_quantize_groups")
+    return codes, scales
