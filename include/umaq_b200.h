@@ -93,6 +93,38 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /*
                     void* out_bf16 /* device [H] */, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* ---- router ---------------------------------------------------------------------
+ * logits = bf16(x . Wr^T), softmax over the experts in float32, top-k (ties to the
+ * lowest expert index), optional division by the top-k sum: the arithmetic of the
+ * Hugging Face OlmoeTopKRouter / Qwen2MoeTopKRouter modules the reference calls
+ * before the operator (src/uma_qmoe/compressed_loader.py:59,
+ * src/uma_qmoe/qwen_compressed_loader.py:73; restated in
+ * benchmarks/runners/capture_qwen_route_trace.py:46-66).  out_logits may be NULL. */
+int umaq_route_topk(const void* hidden_bf16 /* device [tokens, hidden] */,
+                    const void* router_weight_bf16 /* device [experts, hidden] */, int tokens, int hidden,
+                    int experts, int top_k, int renormalize, float* out_weights /* device [tokens, top_k] */,
+                    long long* out_indices /* device [tokens, top_k] */,
+                    void* out_logits_bf16 /* device [tokens, experts] or NULL */, void* stream);
+
+/* ---- prefill / batched tokens ----------------------------------------------------
+ * Same result contract as umaq_moe_decode for `tokens` rows: stable sort of the
+ * routes by expert (replaces the host-side argsort / bincount / cumsum of
+ * src/uma_qmoe/native_backend.py:531-543), grouped gate/up GEMM with SwiGLU,
+ * grouped down GEMM with the routing weight, ordered BF16 top-k combine; with
+ * `shared` != NULL the Qwen shared expert and its sigmoid gate are added.
+ * Replaces q4_moe_prefill / q8_moe_prefill
+ * (src/uma_qmoe/native/packed_q4_binding.cpp:267-347, :442-488) and the BF16
+ * torch._grouped_mm path (src/uma_qmoe/native_backend.py:958-1005).
+ * workspace: umaq_prefill_workspace_bytes() bytes, 256-byte aligned; its first
+ * uint32 is a sticky device-side status (zero it before the first call). */
+size_t umaq_prefill_workspace_bytes(long long tokens, int top_k, int num_experts, int hidden, int intermediate,
+                                    int shared_intermediate);
+int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared /* may be NULL */,
+                     const void* hidden_bf16 /* device [tokens, H] */,
+                     const void* expert_indices /* device [tokens, top_k] */, int indices_are_int64,
+                     const float* routing_weights /* device [tokens, top_k] */, long long tokens, int top_k,
+                     void* out_bf16 /* device [tokens, H] */, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- device-side packer -------------------------------------------------------
  * Quantises `elements` (a multiple of 128) BF16 values, row-major, into the
  * canonical Q4 (elements/2 bytes) or Q8 (elements bytes) codes and elements/128

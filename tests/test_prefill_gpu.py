@@ -1,0 +1,101 @@
+"""Prefill path (route sort, tcgen05 grouped GEMMs, ordered combine) and the fused router vs the
+CPU oracle and the reference-made golden vectors, through the C ABI."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+from tests.helpers import SEED, assert_parity, bits_to_bf16, expert_source, stage_layer
+from uma_qmoe_b200 import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run_prefill(layer, x, idx, w, shared=None):
+    from uma_qmoe_b200 import ops
+    ws = ops.prefill_workspace(layer, x.shape[0], idx.shape[1], shared, torch.device(DEV))
+    args = (layer, x.to(DEV).contiguous(), idx.to(DEV).contiguous(), w.to(DEV).contiguous(), ws, shared)
+    y = ops.moe_prefill(*args)
+    y2 = ops.moe_prefill(*args)
+    torch.cuda.synchronize()
+    assert ops.prefill_status(ws) == 0
+    assert torch.equal(y, y2), "two calls must give identical bits"
+    return y.cpu()
+
+
+def test_olmoe_prefill_golden(golden_dir):
+    g = np.load(golden_dir / "olmoe_prefill.npz")
+    x = bits_to_bf16(g["x_bits"])
+    idx, w = torch.from_numpy(g["idx"]), torch.from_numpy(g["w"])
+    src = expert_source(SEED, 3, "olmoe", "q4_group128")
+    experts = {int(e): src(int(e)) for e in set(idx.reshape(-1).tolist())}
+    layer = stage_layer(experts, 64, 2048, 1024, "q4_group128", DEV)
+    assert_parity(_run_prefill(layer, x, idx, w), bits_to_bf16(g["y_bits"]))
+
+
+@pytest.mark.parametrize("layer_index", [0, 1, 2])
+def test_qwen_prefill_golden(golden_dir, layer_index):
+    from uma_qmoe_b200.ops import DeviceSharedExpert
+    g = np.load(golden_dir / "qwen_layers.npz")
+    enc = str(g[f"L{layer_index}_encoding"])
+    src = expert_source(SEED, layer_index, "qwen", enc)
+    x = bits_to_bf16(g["x8_bits"])
+    idx = torch.from_numpy(g[f"L{layer_index}_i8"])
+    w = torch.from_numpy(g[f"L{layer_index}_w8"])
+    experts = {int(e): src(int(e)) for e in set(idx.reshape(-1).tolist())}
+    layer = stage_layer(experts, 60, 2048, 1408, enc, DEV)
+    assert_parity(_run_prefill(layer, x, idx, w), bits_to_bf16(g[f"L{layer_index}_y8_bits"]))
+    sg, su, sd, sgate = (t.to(DEV).contiguous() for t in syn.shared_expert_weights(SEED, layer_index, syn.QWEN))
+    b = _run_prefill(layer, x, idx, w, DeviceSharedExpert(sg, su, sd, sgate))
+    assert_parity(b, bits_to_bf16(g[f"L{layer_index}_b8_bits"]))
+
+
+def test_prefill_many_tokens_few_experts_matches_oracle():
+    """300 tokens over 4 experts: several 128-route tiles per expert, ragged last tiles, one empty expert."""
+    src = expert_source(SEED, 9, "olmoe", "q4_group128")
+    tokens = 300
+    rng = np.random.default_rng(5)
+    idx = torch.from_numpy(np.stack([rng.permutation([0, 1, 2, 4, 5, 6, 7, 8])[:8] for _ in range(tokens)]).astype(np.int64))
+    idx[:, 4:] = idx[:, :4]          # every token hits only 4 distinct experts, each twice
+    w = torch.from_numpy(rng.random((tokens, 8), dtype=np.float32) / 8)
+    used = sorted(set(idx.reshape(-1).tolist()))
+    layer = stage_layer({e: src(e) for e in used}, 16, 2048, 1024, "q4_group128", DEV)
+    x = syn.activations(SEED + 21, tokens)
+    want = orc.moe_forward(x, idx, w, src, num_experts=64, top_k=8, qwen=False)
+    assert_parity(_run_prefill(layer, x, idx, w), want)
+
+
+@pytest.mark.parametrize("model,renorm", [("olmoe", True), ("olmoe", False), ("qwen", False)])
+def test_router_matches_oracle(model, renorm):
+    from uma_qmoe_b200 import ops
+    shape = syn.OLMOE if model == "olmoe" else syn.QWEN
+    wr = syn.router_weight(SEED, 1, shape, skew=1.5)
+    x = syn.activations(SEED + 31, 512)
+    probs, w_ref, idx_ref = orc.router_topk(x, wr, shape.top_k, renorm)
+    w, idx, logits = ops.route_topk(x.to(DEV), wr.to(DEV), shape.top_k, renorm, return_logits=True)
+    w, idx, logits = w.cpu(), idx.cpu(), logits.cpu()
+    ref_logits = torch.nn.functional.linear(x, wr)
+    same_logits = (logits == ref_logits).all(dim=1)
+    # BF16 logits are coarse, so equal probabilities are common.  Rows whose logits agree with the
+    # oracle's and whose k-th and (k+1)-th probabilities differ must select the same expert SET with
+    # the same weights; if no two of the top k+1 are equal the order must match too.
+    srt = probs.sort(dim=1, descending=True).values
+    k = shape.top_k
+    boundary_clear = same_logits & (srt[:, k - 1] != srt[:, k])
+    all_clear = same_logits & (srt[:, : k + 1].diff(dim=1) != 0).all(dim=1)
+    # the kernel rounds an exactly summed dot product; the CPU GEMM of the oracle is off by one BF16 ulp on
+    # about 1 logit in 5000, i.e. on 1-2 % of the rows
+    assert same_logits.float().mean() >= 0.97 and boundary_clear.float().mean() > 0.9 and all_clear.any()
+    assert torch.equal(idx[boundary_clear].sort(dim=1).values, idx_ref[boundary_clear].sort(dim=1).values)
+    assert torch.allclose(w[boundary_clear].sort(dim=1).values, w_ref[boundary_clear].sort(dim=1).values,
+                          rtol=2e-5, atol=1e-8)
+    assert torch.equal(idx[all_clear], idx_ref[all_clear])
+    assert torch.allclose(w[all_clear], w_ref[all_clear], rtol=2e-5, atol=1e-8)
+    # every other row must still pick a valid top-k of its own logits
+    own = torch.softmax(logits.float(), dim=1)
+    chosen = own.gather(1, idx)
+    kth = own.sort(dim=1, descending=True).values[:, shape.top_k - 1]
+    assert bool((chosen >= kth[:, None] - 1e-9).all())
+    assert int((~same_logits).sum()) <= 0.01 * x.shape[0]

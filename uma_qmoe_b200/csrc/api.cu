@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "aux.cuh"
 #include "decode.cuh"
+#include "grouped.cuh"
 
 namespace umaq {
 
@@ -106,6 +107,146 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared, c
 int umaq_quantize_groups(const void* src_bf16, long long elements, int encoding, void* codes, float* scales,
                          void* stream) {
   return launch_quantize_groups(src_bf16, elements, encoding, codes, scales, static_cast<cudaStream_t>(stream));
+}
+
+int umaq_route_topk(const void* hidden_bf16, const void* router_weight_bf16, int tokens, int hidden, int experts,
+                    int top_k, int renormalize, float* out_weights, long long* out_indices, void* out_logits_bf16,
+                    void* stream) {
+  if (!hidden_bf16 || !router_weight_bf16 || !out_weights || !out_indices) {
+    set_error("umaq_route_topk: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  RouterArgs a{};
+  a.x = static_cast<const __nv_bfloat16*>(hidden_bf16);
+  a.weight = static_cast<const __nv_bfloat16*>(router_weight_bf16);
+  a.tokens = tokens; a.hidden = hidden; a.experts = experts; a.top_k = top_k; a.renormalize = renormalize;
+  a.out_weights = out_weights; a.out_indices = out_indices;
+  a.out_logits = static_cast<__nv_bfloat16*>(out_logits_bf16);
+  return launch_router_topk(a, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+struct PrefillPlan {
+  size_t status, counts, offsets, num_tiles, tiles, sorted_route, route_pos, sorted_weight, xs, inter, yw;
+  size_t s_num_tiles, s_tiles, s_inter, s_out, total;
+  int max_tiles, s_max_tiles;
+};
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+PrefillPlan prefill_plan(long long tokens, int top_k, int experts, int hidden, int inter, int shared_inter) {
+  PrefillPlan p{};
+  const size_t routes = (size_t)tokens * top_k;
+  p.max_tiles = (int)((routes + 127) / 128) + experts;
+  p.s_max_tiles = (int)((tokens + 127) / 128);
+  size_t cur = 0;
+  auto take = [&](size_t bytes) { const size_t at = cur; cur = align256(cur + bytes); return at; };
+  p.status = take(256);
+  p.counts = take((size_t)experts * 4);
+  p.offsets = take((size_t)(experts + 1) * 4);
+  p.num_tiles = take(4);
+  p.tiles = take((size_t)p.max_tiles * 12);
+  p.sorted_route = take(routes * 4);
+  p.route_pos = take(routes * 4);
+  p.sorted_weight = take(routes * 4);
+  p.xs = take(routes * hidden * 2);
+  p.inter = take(routes * inter * 2);
+  p.yw = take(routes * hidden * 2);
+  if (shared_inter) {
+    p.s_num_tiles = take(4);
+    p.s_tiles = take((size_t)p.s_max_tiles * 12);
+    p.s_inter = take((size_t)tokens * shared_inter * 2);
+    p.s_out = take((size_t)tokens * hidden * 2);
+  }
+  p.total = cur;
+  return p;
+}
+}  // namespace
+
+size_t umaq_prefill_workspace_bytes(long long tokens, int top_k, int num_experts, int hidden, int intermediate,
+                                    int shared_intermediate) {
+  return prefill_plan(tokens, top_k, num_experts, hidden, intermediate, shared_intermediate).total;
+}
+
+int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, const void* hidden_bf16,
+                     const void* expert_indices, int indices_are_int64, const float* routing_weights, long long tokens,
+                     int top_k, void* out_bf16, void* workspace, size_t workspace_bytes, void* stream_) {
+  if (!layer || !hidden_bf16 || !expert_indices || !routing_weights || !out_bf16 || !workspace || tokens <= 0) {
+    set_error("umaq_moe_prefill: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  const int H = layer->hidden, I = layer->intermediate, E = layer->num_experts;
+  const int S = shared ? shared->intermediate : 0;
+  if (tokens * (long long)top_k > 0x7fffffffLL || top_k < 1 || top_k > 8) {
+    set_error("umaq_moe_prefill: unsupported route count");
+    return ERR_BAD_ARGUMENT;
+  }
+  const PrefillPlan pl = prefill_plan(tokens, top_k, E, H, I, S);
+  if (workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("umaq_moe_prefill: workspace too small or not 256-byte aligned");
+    return ERR_WORKSPACE;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  auto at = [&](size_t off) { return ws + off; };
+  unsigned* status = reinterpret_cast<unsigned*>(at(pl.status));
+  int* tiles = reinterpret_cast<int*>(at(pl.tiles));
+  const long long routes = tokens * top_k;
+  const int quant = layer->encoding != ENC_BF16;
+
+  SortArgs sa{};
+  sa.indices = expert_indices; sa.idx64 = indices_are_int64; sa.weights = routing_weights;
+  sa.tokens = (int)tokens; sa.top_k = top_k; sa.experts = E;
+  sa.counts = reinterpret_cast<int*>(at(pl.counts)); sa.offsets = reinterpret_cast<int*>(at(pl.offsets));
+  sa.sorted_route = reinterpret_cast<int*>(at(pl.sorted_route)); sa.route_pos = reinterpret_cast<int*>(at(pl.route_pos));
+  sa.sorted_weight = reinterpret_cast<float*>(at(pl.sorted_weight));
+  sa.num_tiles = reinterpret_cast<int*>(at(pl.num_tiles));
+  sa.tile_expert = tiles; sa.tile_row0 = tiles + pl.max_tiles; sa.tile_rows = tiles + 2 * pl.max_tiles;
+  sa.max_tiles = pl.max_tiles; sa.status = status;
+  int rc = launch_route_sort(sa, stream);
+  if (rc) return rc;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(at(pl.xs));
+  rc = launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sa.sorted_route, top_k, routes, H, quant, xs, stream);
+  if (rc) return rc;
+
+  GroupedGemmArgs g{};
+  g.mode = 0; g.enc = layer->encoding; g.num_experts = E; g.n_rows = I; g.k = H;
+  g.act = xs; g.total_rows = routes;
+  g.w0 = layer->gate; g.s0 = layer->gate_scales; g.w1 = layer->up; g.s1 = layer->up_scales;
+  g.num_tiles = sa.num_tiles; g.tile_expert = sa.tile_expert; g.tile_row0 = sa.tile_row0; g.tile_rows = sa.tile_rows;
+  g.max_tiles = pl.max_tiles;
+  g.out = reinterpret_cast<__nv_bfloat16*>(at(pl.inter)); g.out_stride = I; g.permute_out = quant; g.status = status;
+  rc = launch_grouped_gemm(g, stream);
+  if (rc) return rc;
+  g.mode = 1; g.n_rows = H; g.k = I; g.act = g.out;
+  g.w0 = layer->down; g.s0 = layer->down_scales; g.w1 = nullptr; g.s1 = nullptr;
+  g.out = reinterpret_cast<__nv_bfloat16*>(at(pl.yw)); g.out_stride = H; g.route_weight = sa.sorted_weight; g.permute_out = 0;
+  rc = launch_grouped_gemm(g, stream);
+  if (rc) return rc;
+
+  const __nv_bfloat16* shared_out = nullptr;
+  if (shared) {
+    int* st = reinterpret_cast<int*>(at(pl.s_tiles));
+    int* snt = reinterpret_cast<int*>(at(pl.s_num_tiles));
+    rc = launch_dense_tiles((int)tokens, snt, st, st + pl.s_max_tiles, st + 2 * pl.s_max_tiles, stream);
+    if (rc) return rc;
+    GroupedGemmArgs d{};
+    d.mode = 0; d.enc = ENC_BF16; d.num_experts = 1; d.n_rows = S; d.k = H;
+    d.act = hidden_bf16; d.total_rows = tokens;
+    d.w0 = shared->gate; d.w1 = shared->up;
+    d.num_tiles = snt; d.tile_expert = st; d.tile_row0 = st + pl.s_max_tiles; d.tile_rows = st + 2 * pl.s_max_tiles;
+    d.max_tiles = pl.s_max_tiles;
+    d.out = reinterpret_cast<__nv_bfloat16*>(at(pl.s_inter)); d.out_stride = S; d.status = status;
+    rc = launch_grouped_gemm(d, stream);
+    if (rc) return rc;
+    d.mode = 1; d.n_rows = H; d.k = S; d.act = d.out; d.w0 = shared->down; d.w1 = nullptr;
+    d.out = reinterpret_cast<__nv_bfloat16*>(at(pl.s_out)); d.out_stride = H; d.route_weight = nullptr;
+    rc = launch_grouped_gemm(d, stream);
+    if (rc) return rc;
+    shared_out = d.out;
+  }
+  return launch_combine(reinterpret_cast<const __nv_bfloat16*>(at(pl.yw)), expert_indices, indices_are_int64, sa.route_pos,
+                        (int)tokens, top_k, H, shared_out, static_cast<const __nv_bfloat16*>(hidden_bf16),
+                        shared ? static_cast<const __nv_bfloat16*>(shared->gate_vec) : nullptr,
+                        static_cast<__nv_bfloat16*>(out_bf16), stream);
 }
 
 }  // extern "C"

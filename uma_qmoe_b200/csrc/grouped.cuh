@@ -1,0 +1,83 @@
+// Parameter blocks and host launchers of the prefill path (grouped.cu, route.cu).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace umaq {
+
+// Device-side view handed to the grouped GEMM kernel.
+struct GroupedParams {
+  int k;                      // contraction length
+  int n_rows;                 // weight rows per expert in this projection
+  const float* scales0;       // [E * n_rows, k/128] (gate or down)
+  const float* scales1;       // up (mode 0)
+  const int* num_tiles;       // device: number of valid 128-route tiles
+  const int* tile_expert;     // device [max_tiles]
+  const int* tile_row0;       // first sorted route row of the tile
+  const int* tile_rows;       // valid rows (<= 128)
+  int max_tiles;
+  __nv_bfloat16* out;         // mode 0: intermediate [routes, n_rows]; mode 1: weighted outputs [routes, n_rows]
+  long long out_stride;       // elements
+  const float* route_weight;  // mode 1: routing weight per sorted route
+  int permute_out;            // mode 0: write the [k0,k4,k1,k5,k2,k6,k3,k7] order a quantised GEMM 2 expects
+  unsigned* status;           // sticky error word
+};
+
+struct GroupedGemmArgs {
+  int mode;                   // 0 gate/up + SwiGLU, 1 down + routing weight
+  int enc;
+  int num_experts;
+  int n_rows;                 // I (mode 0) or H (mode 1)
+  int k;                      // H (mode 0) or I (mode 1)
+  const void* act;            // bf16 [total_rows, k], sorted by expert
+  long long total_rows;
+  const void* w0; const float* s0;   // gate or down
+  const void* w1; const float* s1;   // up
+  const int* num_tiles; const int* tile_expert; const int* tile_row0; const int* tile_rows;
+  int max_tiles;
+  __nv_bfloat16* out; long long out_stride;
+  const float* route_weight;
+  int permute_out;
+  unsigned* status;
+};
+
+int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
+
+// ---- routing (route.cu) ---------------------------------------------------------------------------
+struct RouterArgs {
+  const __nv_bfloat16* x;        // [tokens, hidden]
+  const __nv_bfloat16* weight;   // [experts, hidden]
+  int tokens, hidden, experts, top_k, renormalize;
+  float* out_weights;            // [tokens, top_k] float32
+  long long* out_indices;        // [tokens, top_k] int64
+  __nv_bfloat16* out_logits;     // optional [tokens, experts]
+};
+int launch_router_topk(const RouterArgs& a, cudaStream_t stream);
+
+struct SortArgs {
+  const void* indices; int idx64;  // [tokens, top_k]
+  const float* weights;            // [tokens, top_k]
+  int tokens, top_k, experts;
+  int* counts;                     // [experts]
+  int* offsets;                    // [experts + 1]
+  int* sorted_route;               // [routes] token * top_k + slot, stable by expert
+  int* route_pos;                  // [routes] inverse permutation
+  float* sorted_weight;            // [routes]
+  int* num_tiles; int* tile_expert; int* tile_row0; int* tile_rows;   // 128-route tiles
+  int max_tiles;
+  unsigned* status;
+};
+int launch_route_sort(const SortArgs& a, cudaStream_t stream);
+
+int launch_dense_tiles(int rows, int* num_tiles, int* tile_expert, int* tile_row0, int* tile_rows, cudaStream_t stream);
+
+// rows of x gathered into sorted order; `permute` writes each run of 8 as [0,4,1,5,2,6,3,7]
+int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_k, long long routes, int hidden,
+                       int permute, __nv_bfloat16* out, cudaStream_t stream);
+int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
+                   int top_k, int hidden, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
+                   const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream);
+
+}  // namespace umaq

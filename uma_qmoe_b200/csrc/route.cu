@@ -1,0 +1,303 @@
+// Routing side of the prefill path: the fused router, the stable expert sort that replaces the
+// reference's host-side argsort / bincount / cumsum (src/uma_qmoe/native_backend.py:531-543), the
+// row gather that feeds the grouped GEMM and the ordered top-k combine that replaces
+// reduce_topk_route_output_kernel (src/uma_qmoe/native/packed_q4_kernel.cu:1349-1365) with the
+// accumulation order of the reference's CPU path (src/uma_qmoe/custom_op.py:312-338).
+#include "grouped.cuh"
+
+#include "common.cuh"
+
+namespace umaq {
+namespace {
+
+// ---- router: logits = bf16(x . Wr^T), softmax in float32, top-k, optional renormalisation ----------
+// The arithmetic of the Hugging Face OlmoeTopKRouter / Qwen2MoeTopKRouter the reference calls at
+// src/uma_qmoe/compressed_loader.py:59 and src/uma_qmoe/qwen_compressed_loader.py:73.  One warp per
+// token; ties go to the lowest expert index.
+constexpr int kRouterWarps = 8;
+
+__global__ void __launch_bounds__(kRouterWarps * 32)
+router_topk_kernel(const RouterArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* probs = reinterpret_cast<float*>(smem) + (threadIdx.x >> 5) * a.experts;   // per-warp scratch
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * kRouterWarps + (threadIdx.x >> 5);
+  if (token >= a.tokens) return;
+  const int H = a.hidden, E = a.experts;
+  const __nv_bfloat16* xr = a.x + (size_t)token * H;
+  // logits: BF16 products are exact in float32; they are summed in float64 so that the BF16
+  // rounding of the logit matches an exactly rounded dot product (a float32 sum is off by one BF16
+  // ulp on ~0.2 % of the logits, which moves near-tied experts across the top-k boundary)
+  for (int e = 0; e < E; ++e) {
+    const __nv_bfloat16* wr = a.weight + (size_t)e * H;
+    double acc = 0.0;
+    for (int k = lane * 8; k < H; k += 256) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(xr + k);
+      const uint4 wv = *reinterpret_cast<const uint4*>(wr + k);
+      const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, ws[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc += (double)(__uint_as_float(xs[i] << 16) * __uint_as_float(ws[i] << 16));
+        acc += (double)(__uint_as_float(xs[i] & 0xffff0000u) * __uint_as_float(ws[i] & 0xffff0000u));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const float l = bf16_round((float)acc);       // F.linear output in BF16
+      probs[e] = l;
+      if (a.out_logits) a.out_logits[(size_t)token * E + e] = __float2bfloat16_rn(l);
+    }
+  }
+  __syncwarp();
+  // softmax over the experts in float32
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, probs[e]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(probs[e] - mx);
+    probs[e] = v;
+    sum += v;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
+  __syncwarp();
+  // top-k by repeated arg-max (value descending, index ascending)
+  float topsum = 0.f;
+  float myval = 0.f;
+  long long myidx = 0;
+  for (int j = 0; j < a.top_k; ++j) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = probs[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == j) { myval = best; myidx = bi; }
+    topsum += best;
+    if (lane == 0) probs[bi] = -2.f;
+    __syncwarp();
+  }
+  if (lane < a.top_k) {
+    a.out_weights[(size_t)token * a.top_k + lane] = a.renormalize ? myval / topsum : myval;
+    a.out_indices[(size_t)token * a.top_k + lane] = myidx;
+  }
+}
+
+// ---- stable expert sort of the routes, one CTA --------------------------------------------------------
+// Route i = token * top_k + slot.  Warp w owns a contiguous chunk of routes; a per-warp histogram and
+// a scan over (expert, warp) give every warp its first position inside each expert's run, and ranks
+// inside a 32-route batch come from __match_any_sync, so equal experts keep their route order.
+constexpr int kSortThreads = 1024;
+constexpr int kMaxSortExperts = 128;
+
+__device__ __forceinline__ int load_expert(const void* idx, int idx64, long long i) {
+  return idx64 ? (int)reinterpret_cast<const long long*>(idx)[i] : reinterpret_cast<const int*>(idx)[i];
+}
+
+__global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs a) {
+  __shared__ int hist[32][kMaxSortExperts];     // per-warp counts, then per-warp running positions
+  __shared__ int total[kMaxSortExperts + 1];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int E = a.experts;
+  const long long routes = (long long)a.tokens * a.top_k;
+  const long long chunk = ((routes + 31) / 32 + 31) / 32 * 32;     // routes per warp, multiple of 32
+  const long long begin = min(routes, warp * chunk), end = min(routes, begin + chunk);
+  for (int i = tid; i < 32 * kMaxSortExperts; i += kSortThreads) (&hist[0][0])[i] = 0;
+  __syncthreads();
+  bool bad = false;
+  for (long long i = begin + lane; i < end; i += 32) {
+    const int e = load_expert(a.indices, a.idx64, i);
+    if (e < 0 || e >= E) bad = true; else atomicAdd(&hist[warp][e], 1);
+  }
+  if (bad) atomicExch(a.status, (unsigned)ERR_BAD_ARGUMENT);
+  __syncthreads();
+  // per expert: exclusive scan over the warps; totals
+  if (tid < E) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) { const int c = hist[w][tid]; hist[w][tid] = run; run += c; }
+    total[tid] = run;
+    a.counts[tid] = run;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = total[e];
+      a.offsets[e] = run;
+      total[e] = run;
+      for (int r = 0; r < c && tiles < a.max_tiles; r += 128, ++tiles) {
+        a.tile_expert[tiles] = e; a.tile_row0[tiles] = run + r; a.tile_rows[tiles] = min(128, c - r);
+      }
+      run += c;
+    }
+    a.offsets[E] = run;
+    *a.num_tiles = tiles;
+  }
+  __syncthreads();
+  for (long long base = begin; base < end; base += 32) {
+    const long long i = base + lane;
+    const bool live = i < end;
+    int e = live ? load_expert(a.indices, a.idx64, i) : -1 - lane;     // distinct keys for idle lanes
+    if (live && (e < 0 || e >= E)) { e = -1 - lane; }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0) {
+      const int pos = total[e] + hist[warp][e] + rank;
+      a.sorted_route[pos] = (int)i;
+      a.route_pos[i] = pos;
+      a.sorted_weight[pos] = a.weights[i];
+    }
+    __syncwarp();
+    if (e >= 0 && rank == 0) hist[warp][e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+// ---- gather: sorted_x[i] = x[sorted_route[i] / top_k], optionally in the permuted K order ------------------
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route, int top_k,
+                                   long long routes, int hidden, int permute, __nv_bfloat16* __restrict__ out) {
+  const long long i = blockIdx.x;
+  if (i >= routes) return;
+  const int token = sorted_route ? sorted_route[i] / top_k : (int)i;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)token * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)i * hidden);
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+    uint4 w = src[v];
+    if (permute) {
+      // (e0,e1)(e2,e3)(e4,e5)(e6,e7) -> (e0,e4)(e1,e5)(e2,e6)(e3,e7)
+      const uint32_t a = w.x, b = w.y, c = w.z, d = w.w;
+      w.x = prmt(a, c, 0x5410); w.y = prmt(a, c, 0x7632);
+      w.z = prmt(b, d, 0x5410); w.w = prmt(b, d, 0x7632);
+    }
+    dst[v] = w;
+  }
+}
+
+// ---- combine: ordered BF16 running sum over a token's routes, then the Qwen shared branch -----------------
+// out[t] = (((0 + c_e1) + c_e2) + ...) with e1 < e2 < ... and every partial sum rounded to BF16; the
+// contributions are already BF16 (GEMM 2 epilogue).  With a shared expert: + bf16(sigmoid(bf16(x . wg))
+// * shared_out[t]), as QuantizedQwenMoEBlock does after the operator
+// (src/uma_qmoe/qwen_compressed_loader.py:82-85).
+__global__ void __launch_bounds__(256)
+combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restrict__ indices, int idx64,
+               const int* __restrict__ route_pos, int top_k, int hidden, const __nv_bfloat16* __restrict__ shared_out,
+               const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_vec,
+               __nv_bfloat16* __restrict__ out) {
+  __shared__ int order_pos[8];
+  __shared__ float red[8];
+  __shared__ float gate;
+  const int t = blockIdx.x, tid = threadIdx.x;
+  if (tid == 0) {
+    int ex[8], ps[8];
+    for (int s = 0; s < top_k; ++s) {
+      ex[s] = load_expert(indices, idx64, (long long)t * top_k + s);
+      ps[s] = route_pos[(long long)t * top_k + s];
+    }
+    for (int i = 1; i < top_k; ++i) {           // stable insertion sort by expert
+      const int e = ex[i], q = ps[i];
+      int j = i - 1;
+      while (j >= 0 && ex[j] > e) { ex[j + 1] = ex[j]; ps[j + 1] = ps[j]; --j; }
+      ex[j + 1] = e; ps[j + 1] = q;
+    }
+    for (int s = 0; s < top_k; ++s) order_pos[s] = ps[s];
+  }
+  if (shared_out) {
+    float acc = 0.f;
+    for (int k = tid; k < hidden; k += 256)
+      acc += __bfloat162float(x[(size_t)t * hidden + k]) * __bfloat162float(gate_vec[k]);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((tid & 31) == 0) red[tid >> 5] = acc;
+  }
+  __syncthreads();
+  if (shared_out && tid == 0) {
+    float s = 0.f;
+    for (int i = 0; i < 8; ++i) s += red[i];
+    s = bf16_round(s);
+    gate = bf16_round(1.f / (1.f + expf(-s)));
+  }
+  __syncthreads();
+  for (int c = tid * 2; c < hidden; c += 512) {
+    float r0 = 0.f, r1 = 0.f;
+    for (int s = 0; s < top_k; ++s) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(weighted + (size_t)order_pos[s] * hidden + c);
+      r0 = bf16_round(r0 + __low2float(v));
+      r1 = bf16_round(r1 + __high2float(v));
+    }
+    if (shared_out) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(shared_out + (size_t)t * hidden + c);
+      r0 = bf16_round(r0 + bf16_round(gate * __low2float(v)));
+      r1 = bf16_round(r1 + bf16_round(gate * __high2float(v)));
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * hidden + c) = __floats2bfloat162_rn(r0, r1);
+  }
+}
+
+// tile table of a dense [rows, k] matrix treated as one expert (the Qwen shared expert in prefill)
+__global__ void dense_tiles_kernel(int rows, int* num_tiles, int* tile_expert, int* tile_row0, int* tile_rows) {
+  const int tiles = (rows + 127) / 128;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    tile_expert[t] = 0; tile_row0[t] = t * 128; tile_rows[t] = min(128, rows - t * 128);
+  }
+  if (threadIdx.x == 0) *num_tiles = tiles;
+}
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("%s: launch failed: %s", what, cudaGetErrorString(e)); return ERR_LAUNCH; }
+  return ERR_NONE;
+}
+
+}  // namespace
+
+int launch_dense_tiles(int rows, int* num_tiles, int* tile_expert, int* tile_row0, int* tile_rows, cudaStream_t stream) {
+  dense_tiles_kernel<<<1, 256, 0, stream>>>(rows, num_tiles, tile_expert, tile_row0, tile_rows);
+  return check_launch("dense tiles");
+}
+
+int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
+  if (a.tokens <= 0 || a.hidden % 256 || a.experts < a.top_k || a.top_k < 1 || a.top_k > 32 || a.experts > 1024) {
+    set_error("router: unsupported shape (tokens %d, hidden %d, experts %d, top_k %d)", a.tokens, a.hidden, a.experts, a.top_k);
+    return ERR_BAD_ARGUMENT;
+  }
+  const int blocks = (a.tokens + kRouterWarps - 1) / kRouterWarps;
+  router_topk_kernel<<<blocks, kRouterWarps * 32, kRouterWarps * a.experts * sizeof(float), stream>>>(a);
+  return check_launch("router");
+}
+
+int launch_route_sort(const SortArgs& a, cudaStream_t stream) {
+  if (a.experts > kMaxSortExperts || a.tokens <= 0 || a.top_k < 1 || (long long)a.tokens * a.top_k > 0x7fffffffLL) {
+    set_error("route sort: unsupported shape (tokens %d, top_k %d, experts %d)", a.tokens, a.top_k, a.experts);
+    return ERR_BAD_ARGUMENT;
+  }
+  route_sort_kernel<<<1, kSortThreads, 0, stream>>>(a);
+  return check_launch("route sort");
+}
+
+int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_k, long long routes, int hidden,
+                       int permute, __nv_bfloat16* out, cudaStream_t stream) {
+  if (routes <= 0 || hidden % 8 || routes > 0x7fffffffLL) { set_error("gather: unsupported shape"); return ERR_BAD_ARGUMENT; }
+  gather_rows_kernel<<<(unsigned)routes, 128, 0, stream>>>(x, sorted_route, top_k, routes, hidden, permute, out);
+  return check_launch("gather");
+}
+
+int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
+                   int top_k, int hidden, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
+                   const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream) {
+  if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 2) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
+  combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, shared_out, x, gate_vec, out);
+  return check_launch("combine");
+}
+
+}  // namespace umaq

@@ -1,0 +1,257 @@
+"""The sm_100a performance backend behind ``uma_qmoe::moe_forward`` /
+``uma_qmoe::qwen_moe_forward``.
+
+Same public surface as the reference's ``src/uma_qmoe/native_backend.py``
+(``PackedQ4NativeBackend``, ``MixedTargetNativeBackend``,
+``install_packed_q4_backend``, ``install_mixed_target_backend``,
+``load_native_extension``, ``native_kernel_source_sha256``,
+``observed_native_platform``; ``cache_summary()`` keys ``:457-467``;
+``release_pack`` ``:469-480``), but the native side is ``libumaq_b200.so``
+called through its C ABI, one fused kernel per decode call and a tcgen05
+grouped-GEMM pipeline per prefill call, for every layer encoding.
+
+Staging (``_device_layer``, reference ``:374-455`` / ``:769-956``): the first
+call on a (pack handle, layer, device) copies every expert's canonical bytes,
+projection by projection, through a pinned host buffer into one device tensor
+per projection; nothing is dequantised, ``dequantized_weight_bytes`` stays 0.
+"""
+
+from __future__ import annotations
+
+import threading
+from pathlib import Path
+from typing import Any, Optional
+
+from . import _native, build as _build
+from .custom_op import PLATFORM, acquire_expert_pack, register_moe_forward, register_performance_backend
+from .formats import ContractError, row_bytes
+from .packs import expert_tensor_name
+
+_MODELS = {
+    # op name -> (layers, experts, top_k, hidden, intermediate)    src/uma_qmoe/fixed_models.py:32-55
+    "olmoe": (16, 64, 8, 2048, 1024),
+    "qwen": (24, 60, 4, 2048, 1408),
+}
+
+
+def native_kernel_source_sha256() -> str:
+    return _build.source_sha256()
+
+
+def observed_native_platform(torch: Any, device: Any = 0) -> str:
+    if not torch.cuda.is_available():
+        raise ContractError("the native backend requires a CUDA device")
+    capability = torch.cuda.get_device_capability(device)
+    if torch.version.hip or capability != (10, 0):
+        raise ContractError(f"the native backend requires SM100 (B200), got sm_{capability[0]}{capability[1]}")
+    return PLATFORM
+
+
+def load_native_extension(*, build_directory: str | Path | None = None, verbose: bool = False) -> tuple[str, Any]:
+    """Build (if stale) and load ``libumaq_b200.so``; returns (platform, library).
+
+    ``build_directory`` is accepted for signature compatibility; the library is
+    always built in-tree next to its sources."""
+    import torch
+
+    platform = observed_native_platform(torch)
+    _build.build(verbose=verbose)
+    return platform, _native.lib()
+
+
+class _LayerCache:
+    def __init__(self) -> None:
+        self.layers: dict[tuple[int, int, str], Any] = {}
+        self.lock = threading.Lock()
+
+
+class MixedTargetNativeBackend:
+    """Executes Q4, Q8 and BF16 layers of an ExpertPack or TargetPack."""
+
+    allowed_encodings = ("q4_group128", "q8_group128", "bf16_le")
+
+    def __init__(self, platform: str, extension: Any) -> None:
+        if platform != PLATFORM:
+            raise ContractError(f"unsupported native platform {platform!r}")
+        for name in _native.SIGNATURES:
+            if not hasattr(extension, name):
+                raise ContractError(f"native library does not export {name}")
+        self.platform = platform
+        self.extension = extension
+        self._cache = _LayerCache()
+        self._workspaces: dict[tuple, Any] = {}
+
+    # ---- construction ---------------------------------------------------------------------
+    @classmethod
+    def build_and_register(cls, *, build_directory: str | Path | None = None, verbose: bool = False):
+        platform, extension = load_native_extension(build_directory=build_directory, verbose=verbose)
+        backend = cls(platform, extension)
+        register_moe_forward()
+        register_performance_backend(platform, backend)
+        return backend
+
+    # ---- staging --------------------------------------------------------------------------
+    @staticmethod
+    def _encoding_of(reader: Any, layer_index: int) -> str:
+        if hasattr(reader, "layer_encoding"):
+            return reader.layer_encoding(layer_index)
+        group = int(reader.header["quantization"]["group_size"])
+        if group != 128:
+            raise RuntimeError(f"the native backend requires group size 128, got {group}")
+        return "q4_group128"
+
+    def _device_layer(self, pack_handle: int, layer_index: int, device: Any, reader: Any, model: str):
+        import torch
+
+        from .ops import DeviceLayer
+
+        key = (pack_handle, layer_index, str(device))
+        with self._cache.lock:
+            hit = self._cache.layers.get(key)
+        if hit is not None:
+            return hit
+        layers, experts, _k, hidden, inter = _MODELS[model]
+        if not 0 <= layer_index < layers:
+            name = "OLMoE" if model == "olmoe" else "Qwen"
+            raise RuntimeError(f"{name} layer_index must be in [0, {layers - 1}]")
+        encoding = self._encoding_of(reader, layer_index)
+        if encoding not in self.allowed_encodings:
+            raise RuntimeError(f"this backend cannot execute layer {layer_index} encoded as {encoding}; "
+                               "install the mixed backend")
+        quantised = encoding != "bf16_le"
+        staged = {}
+        for proj, (rows, k) in (("gate_proj", (inter, hidden)), ("up_proj", (inter, hidden)),
+                                ("down_proj", (hidden, inter))):
+            nbytes = rows * row_bytes(encoding, k)
+            host = torch.empty((experts, nbytes), dtype=torch.uint8).pin_memory()
+            host_s = torch.empty((experts, rows * k // 128), dtype=torch.float32).pin_memory() if quantised else None
+            for e in range(experts):
+                data, scales, meta = reader.tensor_views(expert_tensor_name(layer_index, e, proj))
+                try:
+                    if tuple(meta["shape"]) != (rows, k):
+                        raise RuntimeError(f"tensor {meta.get('name', proj)!r} has unexpected shape {tuple(meta['shape'])!r}")
+                    if meta.get("encoding", encoding) != encoding:
+                        raise RuntimeError(f"tensor of layer {layer_index} is not {encoding}")
+                    if len(data) != nbytes:
+                        raise RuntimeError("pack tensor byte count does not match its shape")
+                    host[e].copy_(torch.frombuffer(data, dtype=torch.uint8))
+                    if quantised:
+                        host_s[e].copy_(torch.frombuffer(scales, dtype=torch.float32))
+                finally:
+                    data.release()
+                    scales.release()
+            staged[proj] = (host.to(device, non_blocking=True),
+                            host_s.to(device, non_blocking=True) if quantised else None)
+        torch.cuda.current_stream(device).synchronize()      # the pinned buffers go away after this
+        layer = DeviceLayer(encoding, experts, hidden, inter, staged["gate_proj"][0], staged["up_proj"][0],
+                            staged["down_proj"][0], staged["gate_proj"][1], staged["up_proj"][1],
+                            staged["down_proj"][1])
+        with self._cache.lock:
+            return self._cache.layers.setdefault(key, layer)
+
+    def cache_summary(self) -> dict[str, int]:
+        with self._cache.lock:
+            layers = list(self._cache.layers.values())
+        return {
+            "tensor_count": sum(3 * layer.num_experts for layer in layers),
+            "device_storage_bytes": sum(layer.device_storage_bytes for layer in layers),
+            "dequantized_weight_bytes": 0,
+        }
+
+    def release_pack(self, pack_handle: int) -> None:
+        """Drop every device copy that belongs to a closed pack handle."""
+        with self._cache.lock:
+            for key in [k for k in self._cache.layers if k[0] == pack_handle]:
+                del self._cache.layers[key]
+
+    # ---- execution ------------------------------------------------------------------------
+    def _workspace(self, kind: str, layer: Any, tokens: int, top_k: int, shared: Any, device: Any):
+        from . import ops
+
+        key = (kind, str(device), layer.hidden, layer.intermediate, layer.num_experts, tokens, top_k,
+               0 if shared is None else int(shared.gate.shape[0]))
+        ws = self._workspaces.get(key)
+        if ws is None:
+            if kind == "decode":
+                ws = ops.decode_workspace(layer, top_k, shared, device)
+            else:
+                ws = ops.prefill_workspace(layer, tokens, top_k, shared, device)
+                # keep only the largest prefill workspace per shape family
+                for old in [k for k in self._workspaces if k[0] == "prefill" and k[1:5] == key[1:5] and k[6:] == key[6:]]:
+                    del self._workspaces[old]
+            self._workspaces[key] = ws
+        return ws
+
+    def _run(self, model: str, hidden_states: Any, expert_indices: Any, routing_weights: Any, layer_index: int,
+             pack_handle: int, shared: Optional[Any] = None):
+        import torch
+
+        from . import ops
+
+        _layers, _experts, top_k, hidden, _inter = _MODELS[model]
+        label = "OLMoE" if model == "olmoe" else "Qwen"
+        if hidden_states.dtype != torch.bfloat16:
+            raise RuntimeError(f"{label} native backend requires BF16 hidden states")
+        flat = hidden_states.reshape(-1, hidden_states.shape[-1])
+        if flat.shape[-1] != hidden:
+            raise RuntimeError(f"{label} native backend requires hidden size {hidden}")
+        if tuple(expert_indices.shape) != (flat.shape[0], top_k):
+            raise RuntimeError(f"{label} native backend requires [tokens, {top_k}] routes")
+        if expert_indices.dtype not in (torch.int32, torch.int64):
+            raise RuntimeError("expert_indices must use int32 or int64")
+        if tuple(routing_weights.shape) != tuple(expert_indices.shape):
+            raise RuntimeError("expert_indices and routing_weights shapes must match")
+        with acquire_expert_pack(pack_handle) as reader:
+            layer = self._device_layer(pack_handle, layer_index, hidden_states.device, reader, model)
+        stream = torch.cuda.current_stream(hidden_states.device)
+        for tensor in layer.tensors:
+            tensor.record_stream(stream)
+        flat = flat.contiguous()
+        indices = expert_indices.contiguous()
+        weights = routing_weights.to(dtype=torch.float32).contiguous()     # float32 routing weights, no BF16 rounding
+        tokens = flat.shape[0]
+        out = torch.empty_like(flat)
+        if tokens == 1:
+            ws = self._workspace("decode", layer, 1, top_k, shared, hidden_states.device)
+            ops.moe_decode(layer, flat, indices, weights, ws, shared, out=out)
+        else:
+            ws = self._workspace("prefill", layer, tokens, top_k, shared, hidden_states.device)
+            ops.moe_prefill(layer, flat, indices, weights, ws, shared, out=out)
+        return out.reshape(hidden_states.shape)
+
+    def __call__(self, hidden_states, expert_indices, routing_weights, layer_index: int, pack_handle: int):
+        return self._run("olmoe", hidden_states, expert_indices, routing_weights, layer_index, pack_handle)
+
+    def qwen_forward(self, hidden_states, expert_indices, routing_weights, layer_index: int, pack_handle: int):
+        return self._run("qwen", hidden_states, expert_indices, routing_weights, layer_index, pack_handle)
+
+    def qwen_block_forward(self, hidden_states, expert_indices, routing_weights, layer_index: int, pack_handle: int,
+                           shared: Any):
+        """Routed experts plus the shared expert and its sigmoid gate in the same kernels."""
+        return self._run("qwen", hidden_states, expert_indices, routing_weights, layer_index, pack_handle, shared)
+
+
+class PackedQ4NativeBackend(MixedTargetNativeBackend):
+    """The Q4-only backend of the reference's first milestone; other encodings are refused with the
+    reference's hint to install the mixed backend (``native_backend.py:421-427``)."""
+
+    allowed_encodings = ("q4_group128",)
+
+
+def install_packed_q4_backend(*, build_directory: str | Path | None = None, verbose: bool = False):
+    return PackedQ4NativeBackend.build_and_register(build_directory=build_directory, verbose=verbose)
+
+
+def install_mixed_target_backend(*, build_directory: str | Path | None = None, verbose: bool = False):
+    return MixedTargetNativeBackend.build_and_register(build_directory=build_directory, verbose=verbose)
+
+
+__all__ = [
+    "PackedQ4NativeBackend",
+    "MixedTargetNativeBackend",
+    "install_mixed_target_backend",
+    "install_packed_q4_backend",
+    "load_native_extension",
+    "native_kernel_source_sha256",
+    "observed_native_platform",
+]

@@ -104,6 +104,62 @@ def moe_decode(layer: DeviceLayer, hidden: torch.Tensor, indices: torch.Tensor, 
     return out
 
 
+def prefill_workspace(layer: DeviceLayer, tokens: int, top_k: int, shared: Optional[DeviceSharedExpert],
+                      device: torch.device) -> torch.Tensor:
+    s_inter = int(shared.gate.shape[0]) if shared is not None else 0
+    n = _native.lib().umaq_prefill_workspace_bytes(tokens, top_k, layer.num_experts, layer.hidden,
+                                                   layer.intermediate, s_inter)
+    ws = torch.empty((n + 255) // 256 * 256, dtype=torch.uint8, device=device)
+    ws[:256].zero_()
+    return ws
+
+
+def moe_prefill(layer: DeviceLayer, hidden: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                workspace: torch.Tensor, shared: Optional[DeviceSharedExpert] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[tokens, H] through the routed experts (and the Qwen shared expert) on the tensor cores."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    flat = hidden.reshape(-1, hidden.shape[-1])
+    tokens = flat.shape[0]
+    if flat.shape[1] != layer.hidden:
+        raise RuntimeError(f"hidden size must be {layer.hidden}")
+    if indices.dtype not in (torch.int32, torch.int64) or indices.ndim != 2 or indices.shape[0] != tokens:
+        raise RuntimeError("expert_indices must be [tokens, top_k] int32 or int64")
+    if weights.dtype != torch.float32 or weights.shape != indices.shape:
+        raise RuntimeError("routing_weights must be float32 with the shape of expert_indices")
+    if not (indices.is_contiguous() and weights.is_contiguous()):
+        raise RuntimeError("routes must be contiguous")
+    if out is None:
+        out = torch.empty_like(flat)
+    code = _native.lib().umaq_moe_prefill(
+        C.byref(layer.struct()), C.byref(shared.struct()) if shared is not None else None, flat.data_ptr(),
+        indices.data_ptr(), int(indices.dtype == torch.int64), weights.data_ptr(), tokens, indices.shape[1],
+        out.data_ptr(), workspace.data_ptr(), workspace.numel(), _stream(hidden.device))
+    _native.check(code, "umaq_moe_prefill")
+    return out.reshape(hidden.shape)
+
+
+def prefill_status(workspace: torch.Tensor) -> int:
+    return int(workspace[0:4].view(torch.int32).item())
+
+
+def route_topk(hidden: torch.Tensor, router_weight: torch.Tensor, top_k: int, renormalize: bool,
+               return_logits: bool = False):
+    """Fused router: (weights [T,k] f32, indices [T,k] i64[, logits [T,E] bf16])."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    _require_cuda_bf16(router_weight, "router weight")
+    flat = hidden.reshape(-1, hidden.shape[-1])
+    tokens, experts = flat.shape[0], router_weight.shape[0]
+    w = torch.empty((tokens, top_k), dtype=torch.float32, device=hidden.device)
+    idx = torch.empty((tokens, top_k), dtype=torch.int64, device=hidden.device)
+    logits = torch.empty((tokens, experts), dtype=torch.bfloat16, device=hidden.device) if return_logits else None
+    code = _native.lib().umaq_route_topk(flat.data_ptr(), router_weight.data_ptr(), tokens, flat.shape[1], experts,
+                                         top_k, int(renormalize), w.data_ptr(), idx.data_ptr(),
+                                         logits.data_ptr() if logits is not None else None, _stream(hidden.device))
+    _native.check(code, "umaq_route_topk")
+    return (w, idx, logits) if return_logits else (w, idx)
+
+
 def workspace_status(workspace: torch.Tensor) -> int:
     """Sticky device-side status word of a workspace (synchronises)."""
     return int(workspace[8:12].view(torch.int32).item())
