@@ -1,0 +1,313 @@
+"""Benchmark of the routed-expert MoE path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+
+Workload ("step"): one pass of 8192 BF16 N(0,1) tokens through an OLMoE-shaped stack of 16 MoE
+layers (hidden 2048, 64 experts, top-8 renormalised, intermediate 1024, W4A16 group-128): per layer
+the fused router, the expert-parallel dispatch (N > 1), the grouped-GEMM pipeline and the ordered
+combine; the output of a layer, renormalised to unit RMS, is the input of the next.  Weights are
+seeded synthetic (no checkpoint); the 3.4 GB of packed weights exceed L2, so every step streams them
+from HBM.  With N ranks the experts and the tokens are split N ways (strong scaling).
+
+One JSON line on rank 0.  `value` = tokens/s with inputs resident on the device; `e2e` = the same
+through torch.ops.uma_qmoe.moe_forward with the step's activations coming from pinned host memory
+and the result read back; `roofline` = the gate/up grouped GEMM alone (tensor-bound) and `decode`
+= the batch-1 fused decode kernel rotating over the 16 layers (HBM-bound); `cpu_baseline` = the CPU
+oracle (a port of the reference's correctness path) timed on a bounded sample on this host.
+`--impl reference` times that CPU path as the measured arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SEED = 20260917
+TOKENS, LAYERS = 8192, 16
+DECODE_BYTES = 8 * 3_342_336 + 8_192          # selected experts' codes + scales, x in, y out
+METRIC, UNIT = "prefill_tokens_per_s", "tokens/s"
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *_):
+        if self.proc:
+            self.proc.terminate()
+
+    def summary(self) -> dict:
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def timed(fn, steps: int, warmup: int, world: int) -> float:
+    """Milliseconds per step: CUDA events around `steps` calls, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([start.elapsed_time(stop) / steps], device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+    return float(ms.item())
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU oracle arm
+# ---------------------------------------------------------------------------------------------
+
+def cpu_sample(sample_tokens: int):
+    """A bounded sample of the workload for the CPU path: the first `sample_tokens` tokens through
+    layer 0 (its 64 experts quantised on the host with the oracle's packer)."""
+    from oracle import moe_oracle as orc
+    from uma_qmoe_b200 import synthetic as syn
+
+    shape = syn.OLMOE
+    x = syn.activations(SEED, sample_tokens)
+    wr = syn.router_weight(SEED, 0, shape, skew=1.0)
+    _p, w, idx = orc.router_topk(x, wr, shape.top_k, True)
+    cache: dict[int, tuple] = {}
+
+    def experts(e: int):
+        if e not in cache:
+            cache[e] = tuple(orc.encode_matrix(m, "q4_group128") for m in syn.expert_weights(SEED, 0, e, shape))
+        return cache[e]
+
+    for e in sorted(set(idx.reshape(-1).tolist())):
+        experts(e)                                  # packing is offline work, not part of the timed call
+
+    def call():
+        _pp, ww, ii = orc.router_topk(x, wr, shape.top_k, True)
+        return orc.moe_forward(x, ii, ww, experts, num_experts=64, top_k=8, qwen=False)
+
+    return call
+
+
+def run_cpu(sample_tokens: int, steps: int, warmup: int) -> dict:
+    call = cpu_sample(sample_tokens)
+    for _ in range(warmup):
+        call()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        call()
+    per_layer = (time.perf_counter() - t0) / steps
+    return {"value": sample_tokens / (per_layer * LAYERS), "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port", "seconds_per_layer_call": per_layer,
+            "sample": f"first {sample_tokens} of the {TOKENS} tokens through layer 0 of {LAYERS} "
+                      f"(router + CPU correctness path), time x {LAYERS} layers"}
+
+
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 64
+    probe = run_cpu(sample, 1, 0)
+    budget = 180.0
+    while sample > 8 and probe["seconds_per_layer_call"] * (args.steps + args.warmup) > budget:
+        sample //= 2
+        probe = run_cpu(sample, 1, 0)
+    res = run_cpu(sample, args.steps, args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res["seconds_per_layer_call"] * 1e3 * LAYERS * (TOKENS / sample),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_block(1), "cpu_baseline": res,
+            "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def config_block(world: int) -> dict:
+    return {"workload": "OLMoE-shaped MoE stack, 16 layers x 8192 tokens, hidden 2048, 64 experts top-8 renormalised, "
+                        "intermediate 1024, W4A16 group-128 (expert-parallel prefill)",
+            "tokens": TOKENS, "layers": LAYERS, "parallelism": f"ep{world}",
+            "l2": "inputs larger than L2 (3.4 GB of packed weights per step)"}
+
+
+# ---------------------------------------------------------------------------------------------
+# native arm
+# ---------------------------------------------------------------------------------------------
+
+def native_arm(args) -> None:
+    from uma_qmoe_b200 import custom_op, native_backend, ops, synthetic as syn
+    from uma_qmoe_b200.stack import MoEStack, rms_renorm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    shape = syn.OLMOE
+    per = shape.experts // world
+    mine = range(rank * per, (rank + 1) * per)
+    backend = native_backend.install_mixed_target_backend()
+    stack = MoEStack.build(shape, "q4_group128", LAYERS, SEED, dev, renormalize=True, skew=1.0, experts=mine)
+    share = TOKENS // world
+    x_host = syn.activations(SEED, TOKENS)[rank * share:(rank + 1) * share].contiguous().pin_memory()
+    x_dev = x_host.to(dev)
+    out_host = torch.empty_like(x_host).pin_memory()
+    launches = 0
+
+    if world == 1:
+        class _Stub:
+            mapping_count = 1
+        handle = custom_op.register_expert_pack(_Stub())
+        for l, layer in enumerate(stack.layers):
+            backend.preload_layer(handle, l, dev, layer)
+
+        def run_stack(x):
+            for l in range(LAYERS):
+                w, idx = stack.route(l, x)
+                x = rms_renorm(torch.ops.uma_qmoe.moe_forward(x, idx, w, l, handle, True))
+            return x
+        launches_per_step = LAYERS * 6          # router, sort, gather, 2 grouped GEMMs, combine
+    else:
+        from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE
+        eps = [ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k) for layer in stack.layers]
+
+        def run_stack(x):
+            for l in range(LAYERS):
+                w, idx = stack.route(l, x)
+                x = rms_renorm(eps[l].forward(x, idx, w))
+            return x
+        launches_per_step = LAYERS * 9          # router, sort, gather; on received rows sort, gather, 2 GEMMs, combine; combine
+
+    def step_resident():
+        run_stack(x_dev)
+
+    def step_e2e():
+        y = run_stack(x_host.to(dev, non_blocking=True))
+        out_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    with ClockSampler(local) as clocks:
+        ms = timed(step_resident, args.steps, args.warmup, world)
+        ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2), world)
+    launches = launches_per_step * args.steps
+    pk, pk_kind = peaks()
+
+    line = {"metric": METRIC, "value": TOKENS / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
+            "e2e": {"value": TOKENS / (ms_e2e / 1e3), "unit": UNIT, "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2 * world},
+            "gpu_launches": launches, "clocks": clocks.summary(),
+            "tflops_step": 65536 * 12_582_912 * LAYERS / (ms / 1e3) / 1e12 / world}
+
+    if rank == 0 and world == 1:
+        # ---- roofline of the dominant kernel: the gate/up grouped GEMM of layer 0 ------------------
+        w, idx = stack.route(0, x_dev)
+        routes = ops.route_sort(idx, w, shape.experts)
+        xs = ops.gather_rows(x_dev, routes.sorted_route, shape.top_k, permute=True)
+        inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        times = []
+        for i in range(3 + 10):
+            flush.zero_()                                            # weights leave L2 between launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter)
+            b.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        gemm_ms = statistics.mean(times)
+        flops = 2.0 * xs.shape[0] * shape.hidden * 2 * shape.intermediate
+        line["roofline"] = {"bound": "tensor", "kernel": "grouped_gemm_kernel<Q4, gate/up+SwiGLU>",
+                            "achieved": flops / (gemm_ms / 1e3) / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                            "frac": flops / (gemm_ms / 1e3) / 1e12 / pk["bf16_tflops"], "traffic": None,
+                            "peak_source": f"{pk_kind} (burst)", "ms_per_launch": gemm_ms,
+                            "flops_per_launch": flops}
+        # ---- batch-1 decode: the fused kernel over the 16 layers in rotation (428 MB > L2) -----------
+        xd = x_dev[:1].contiguous()
+        routes1 = [stack.route(l, xd) for l in range(LAYERS)]
+        wsd = ops.decode_workspace(stack.layers[0], shape.top_k, None, dev)
+        outd = torch.empty_like(xd)
+
+        def decode_pass():
+            for l in range(LAYERS):
+                ops.moe_decode(stack.layers[l], xd, routes1[l][1], routes1[l][0], wsd, out=outd)
+        dms = timed(decode_pass, 20, 3, 1) / LAYERS
+        line["decode"] = {"metric": "decode_hbm_gbs", "us_per_layer": dms * 1e3,
+                          "roofline": {"bound": "hbm", "kernel": "moe_decode_kernel", "achieved": DECODE_BYTES / (dms / 1e3) / 1e9,
+                                       "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                       "frac": DECODE_BYTES / (dms / 1e3) / 1e9 / pk["hbm_gbs"], "traffic": None,
+                                       "peak_source": pk_kind, "bytes_per_launch": DECODE_BYTES},
+                          "status": ops.workspace_status(wsd)}
+        line["gpu_launches"] += 13 + 20 * LAYERS + 3 * LAYERS
+        line["cpu_baseline"] = run_cpu(64, 1, 0)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("native", "reference"), default="native")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        native_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -125,6 +125,41 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared /
                      const float* routing_weights /* device [tokens, top_k] */, long long tokens, int top_k,
                      void* out_bf16 /* device [tokens, H] */, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- building blocks of the prefill path ---------------------------------------------
+ * The pieces umaq_moe_prefill chains, exported for hosts that place a collective
+ * between them (expert parallelism) and for per-kernel measurement.  They have no
+ * single counterpart in the reference; each cites what it replaces.
+ *
+ * umaq_route_sort: stable sort of the tokens*top_k routes by expert id, replacing
+ * torch.argsort(stable) / bincount / cumsum at src/uma_qmoe/native_backend.py:531-543.
+ * Route i = token * top_k + slot.  Outputs (all device): counts[E], offsets[E+1],
+ * sorted_route[routes] (route ids in expert order), route_pos[routes] (its inverse),
+ * sorted_weight[routes], and the 128-route tile list of the grouped GEMM:
+ * *num_tiles and tile_table = int[3 * max_tiles] holding expert, first row, row count.
+ * max_tiles >= ceil(routes / 128) + E.  *status: sticky error word, zero it first. */
+int umaq_route_sort(const void* expert_indices, int indices_are_int64, const float* routing_weights, int tokens,
+                    int top_k, int num_experts, int* counts, int* offsets, int* sorted_route, int* route_pos,
+                    float* sorted_weight, int* num_tiles, int* tile_table, int max_tiles, unsigned* status,
+                    void* stream);
+/* out[i] = hidden[sorted_route[i] / top_k] (sorted_route == NULL: out[i] = hidden[i]);
+ * permute != 0 writes every run of 8 elements as [0,4,1,5,2,6,3,7], the K order the
+ * quantised grouped GEMM expects of its activations. */
+int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k, long long routes, int hidden,
+                     int permute, void* out_bf16, void* stream);
+/* One grouped GEMM over the tile list.  mode 0: out[r, :I] = SiLU(act_r . Gate_e) * (act_r . Up_e)
+ * (permute_out != 0 writes the permuted K order for a quantised mode-1 GEMM); mode 1:
+ * out[r, :H] = route_weight[r] * (act_r . Down_e) (route_weight NULL = 1).  Replaces the
+ * tile kernels at src/uma_qmoe/native/packed_q4_kernel.cu:560-776 and :894-1099. */
+int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows,
+                      const int* num_tiles, const int* tile_table, int max_tiles, const float* route_weight,
+                      int permute_out, void* out_bf16, unsigned* status, void* stream);
+/* out[t] = BF16 running sum of weighted[route_pos[t*top_k+s]] over the token's routes in
+ * ascending expert order: the accumulation order of the reference's CPU path
+ * (src/uma_qmoe/custom_op.py:312-338), in place of
+ * reduce_topk_route_output_kernel (src/uma_qmoe/native/packed_q4_kernel.cu:1349-1365). */
+int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, int indices_are_int64,
+                        const int* route_pos, int tokens, int top_k, int hidden, void* out_bf16, void* stream);
+
 /* ---- device-side packer -------------------------------------------------------
  * Quantises `elements` (a multiple of 128) BF16 values, row-major, into the
  * canonical Q4 (elements/2 bytes) or Q8 (elements bytes) codes and elements/128

@@ -41,6 +41,15 @@ SIGNATURES = {
     "umaq_prefill_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "umaq_moe_prefill": (C.c_int, [C.POINTER(Layer), C.POINTER(SharedExpert), C.c_void_p, C.c_void_p, C.c_int,
                                    C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "umaq_route_sort": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
+                                  C.c_void_p]),
+    "umaq_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p,
+                                   C.c_void_p]),
+    "umaq_grouped_gemm": (C.c_int, [C.POINTER(Layer), C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p,
+                                    C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "umaq_combine_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                      C.c_void_p, C.c_void_p]),
     "umaq_quantize_groups": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 

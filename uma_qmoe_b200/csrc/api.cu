@@ -125,6 +125,63 @@ int umaq_route_topk(const void* hidden_bf16, const void* router_weight_bf16, int
   return launch_router_topk(a, static_cast<cudaStream_t>(stream));
 }
 
+int umaq_route_sort(const void* expert_indices, int indices_are_int64, const float* routing_weights, int tokens, int top_k,
+                    int num_experts, int* counts, int* offsets, int* sorted_route, int* route_pos, float* sorted_weight,
+                    int* num_tiles, int* tile_table, int max_tiles, unsigned* status, void* stream) {
+  if (!expert_indices || !routing_weights || !counts || !offsets || !sorted_route || !route_pos || !sorted_weight ||
+      !num_tiles || !tile_table || !status || max_tiles <= 0) {
+    set_error("umaq_route_sort: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  SortArgs a{};
+  a.indices = expert_indices; a.idx64 = indices_are_int64; a.weights = routing_weights;
+  a.tokens = tokens; a.top_k = top_k; a.experts = num_experts;
+  a.counts = counts; a.offsets = offsets; a.sorted_route = sorted_route; a.route_pos = route_pos;
+  a.sorted_weight = sorted_weight; a.num_tiles = num_tiles;
+  a.tile_expert = tile_table; a.tile_row0 = tile_table + max_tiles; a.tile_rows = tile_table + 2 * max_tiles;
+  a.max_tiles = max_tiles; a.status = status;
+  return launch_route_sort(a, static_cast<cudaStream_t>(stream));
+}
+
+int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k, long long routes, int hidden,
+                     int permute, void* out_bf16, void* stream) {
+  if (!hidden_bf16 || !out_bf16) { set_error("umaq_gather_rows: null argument"); return ERR_BAD_ARGUMENT; }
+  return launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sorted_route, top_k, routes, hidden, permute,
+                            static_cast<__nv_bfloat16*>(out_bf16), static_cast<cudaStream_t>(stream));
+}
+
+int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows, const int* num_tiles,
+                      const int* tile_table, int max_tiles, const float* route_weight, int permute_out, void* out_bf16,
+                      unsigned* status, void* stream) {
+  if (!layer || !act_bf16 || !num_tiles || !tile_table || !out_bf16 || !status || (mode != 0 && mode != 1)) {
+    set_error("umaq_grouped_gemm: bad argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  GroupedGemmArgs g{};
+  g.mode = mode; g.enc = layer->encoding; g.num_experts = layer->num_experts;
+  g.n_rows = mode == 0 ? layer->intermediate : layer->hidden;
+  g.k = mode == 0 ? layer->hidden : layer->intermediate;
+  g.act = act_bf16; g.total_rows = total_rows;
+  if (mode == 0) { g.w0 = layer->gate; g.s0 = layer->gate_scales; g.w1 = layer->up; g.s1 = layer->up_scales; }
+  else { g.w0 = layer->down; g.s0 = layer->down_scales; }
+  g.num_tiles = num_tiles; g.tile_expert = tile_table; g.tile_row0 = tile_table + max_tiles;
+  g.tile_rows = tile_table + 2 * max_tiles; g.max_tiles = max_tiles;
+  g.out = static_cast<__nv_bfloat16*>(out_bf16); g.out_stride = g.n_rows;
+  g.route_weight = route_weight; g.permute_out = permute_out; g.status = status;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, int indices_are_int64, const int* route_pos,
+                        int tokens, int top_k, int hidden, void* out_bf16, void* stream) {
+  if (!weighted_bf16 || !expert_indices || !route_pos || !out_bf16) {
+    set_error("umaq_combine_routes: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  return launch_combine(static_cast<const __nv_bfloat16*>(weighted_bf16), expert_indices, indices_are_int64, route_pos,
+                        tokens, top_k, hidden, nullptr, nullptr, nullptr, static_cast<__nv_bfloat16*>(out_bf16),
+                        static_cast<cudaStream_t>(stream));
+}
+
 namespace {
 struct PrefillPlan {
   size_t status, counts, offsets, num_tiles, tiles, sorted_route, route_pos, sorted_weight, xs, inter, yw;

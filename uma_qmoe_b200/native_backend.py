@@ -149,6 +149,12 @@ class MixedTargetNativeBackend:
         with self._cache.lock:
             return self._cache.layers.setdefault(key, layer)
 
+    def preload_layer(self, pack_handle: int, layer_index: int, device: Any, layer: Any) -> None:
+        """Adopt a layer that already sits on the device in the staged layout (synthetic weights
+        built with the device-side packer), instead of staging it from the pack's host bytes."""
+        with self._cache.lock:
+            self._cache.layers[(pack_handle, layer_index, str(device))] = layer
+
     def cache_summary(self) -> dict[str, int]:
         with self._cache.lock:
             layers = list(self._cache.layers.values())

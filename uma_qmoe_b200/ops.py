@@ -160,6 +160,85 @@ def route_topk(hidden: torch.Tensor, router_weight: torch.Tensor, top_k: int, re
     return (w, idx, logits) if return_logits else (w, idx)
 
 
+@dataclass
+class SortedRoutes:
+    """Device-side result of :func:`route_sort`."""
+
+    counts: torch.Tensor          # [E] int32
+    offsets: torch.Tensor         # [E + 1] int32
+    sorted_route: torch.Tensor    # [routes] int32: route ids (token * top_k + slot) in expert order
+    route_pos: torch.Tensor       # [routes] int32: position of each route in that order
+    sorted_weight: torch.Tensor   # [routes] float32
+    num_tiles: torch.Tensor       # [1] int32
+    tile_table: torch.Tensor      # [3 * max_tiles] int32
+    max_tiles: int
+    status: torch.Tensor          # [1] uint32 as int32
+
+
+def route_sort(indices: torch.Tensor, weights: torch.Tensor, num_experts: int) -> SortedRoutes:
+    """Stable sort of the routes by expert, with the grouped GEMM's tile list."""
+    if not indices.is_cuda or indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("expert_indices must be a CUDA int32 or int64 tensor")
+    if weights.dtype != torch.float32 or weights.shape != indices.shape:
+        raise RuntimeError("routing_weights must be float32 with the shape of expert_indices")
+    tokens, top_k = indices.shape
+    routes = tokens * top_k
+    dev = indices.device
+    i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
+    max_tiles = (routes + 127) // 128 + num_experts
+    r = SortedRoutes(i32(num_experts), i32(num_experts + 1), i32(routes), i32(routes),
+                     torch.empty(routes, dtype=torch.float32, device=dev), i32(1), i32(3 * max_tiles), max_tiles,
+                     torch.zeros(1, dtype=torch.int32, device=dev))
+    code = _native.lib().umaq_route_sort(
+        indices.contiguous().data_ptr(), int(indices.dtype == torch.int64), weights.contiguous().data_ptr(), tokens,
+        top_k, num_experts, r.counts.data_ptr(), r.offsets.data_ptr(), r.sorted_route.data_ptr(),
+        r.route_pos.data_ptr(), r.sorted_weight.data_ptr(), r.num_tiles.data_ptr(), r.tile_table.data_ptr(),
+        max_tiles, r.status.data_ptr(), _stream(dev))
+    _native.check(code, "umaq_route_sort")
+    return r
+
+
+def gather_rows(hidden: torch.Tensor, sorted_route: Optional[torch.Tensor], top_k: int, permute: bool) -> torch.Tensor:
+    _require_cuda_bf16(hidden, "hidden_states")
+    routes = sorted_route.numel() if sorted_route is not None else hidden.shape[0]
+    out = torch.empty((routes, hidden.shape[1]), dtype=torch.bfloat16, device=hidden.device)
+    code = _native.lib().umaq_gather_rows(hidden.data_ptr(), sorted_route.data_ptr() if sorted_route is not None else None,
+                                          top_k, routes, hidden.shape[1], int(permute), out.data_ptr(),
+                                          _stream(hidden.device))
+    _native.check(code, "umaq_gather_rows")
+    return out
+
+
+def grouped_gemm(layer: DeviceLayer, mode: int, act: torch.Tensor, routes: SortedRoutes,
+                 route_weight: Optional[torch.Tensor] = None, permute_out: bool = False,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One grouped GEMM launch (mode 0: gate/up + SwiGLU, mode 1: down * routing weight)."""
+    _require_cuda_bf16(act, "activations")
+    n = layer.intermediate if mode == 0 else layer.hidden
+    if out is None:
+        out = torch.empty((act.shape[0], n), dtype=torch.bfloat16, device=act.device)
+    code = _native.lib().umaq_grouped_gemm(
+        C.byref(layer.struct()), mode, act.data_ptr(), act.shape[0], routes.num_tiles.data_ptr(),
+        routes.tile_table.data_ptr(), routes.max_tiles, route_weight.data_ptr() if route_weight is not None else None,
+        int(permute_out), out.data_ptr(), routes.status.data_ptr(), _stream(act.device))
+    _native.check(code, "umaq_grouped_gemm")
+    return out
+
+
+def combine_routes(weighted: torch.Tensor, indices: torch.Tensor, route_pos: torch.Tensor,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Ordered BF16 top-k combine of per-route weighted outputs."""
+    _require_cuda_bf16(weighted, "weighted outputs")
+    tokens, top_k = indices.shape
+    if out is None:
+        out = torch.empty((tokens, weighted.shape[1]), dtype=torch.bfloat16, device=weighted.device)
+    code = _native.lib().umaq_combine_routes(weighted.data_ptr(), indices.contiguous().data_ptr(),
+                                             int(indices.dtype == torch.int64), route_pos.data_ptr(), tokens, top_k,
+                                             weighted.shape[1], out.data_ptr(), _stream(weighted.device))
+    _native.check(code, "umaq_combine_routes")
+    return out
+
+
 def workspace_status(workspace: torch.Tensor) -> int:
     """Sticky device-side status word of a workspace (synchronises)."""
     return int(workspace[8:12].view(torch.int32).item())

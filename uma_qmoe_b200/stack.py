@@ -1,0 +1,74 @@
+"""Device-resident synthetic MoE layers and the layer stack the benchmarks step through.
+
+Weights are generated on the GPU from a seed (N(0, 0.02) in BF16) and packed by the device-side
+packer into the canonical bytes, so a 16-layer OLMoE-shaped stack (3.4 GB of Q4) is ready in well
+under a second; nothing here reads a checkpoint.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import ops
+from .ops import DeviceLayer, DeviceSharedExpert
+from .synthetic import ModelShape, router_weight
+
+
+def random_layer(shape: ModelShape, encoding: str, seed: int, device: torch.device,
+                 experts: Optional[range] = None) -> DeviceLayer:
+    """One layer of `shape` with experts `experts` (default: all) in `encoding`."""
+    experts = range(shape.experts) if experts is None else experts
+    gen = torch.Generator(device=device)
+    n = len(experts)
+
+    def projection(tag: int, rows: int, k: int):
+        gen.manual_seed(seed * 1000003 + tag * 7919 + experts.start)
+        w = (torch.randn(n * rows * k, device=device, generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        if encoding == "bf16_le":
+            return w.view(torch.uint8), None
+        return ops.quantize_groups(w, encoding)
+
+    g, gs = projection(0, shape.intermediate, shape.hidden)
+    u, us = projection(1, shape.intermediate, shape.hidden)
+    d, ds = projection(2, shape.hidden, shape.intermediate)
+    return DeviceLayer(encoding, n, shape.hidden, shape.intermediate, g, u, d, gs, us, ds)
+
+
+def random_shared_expert(shape: ModelShape, seed: int, device: torch.device) -> DeviceSharedExpert:
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 1000003 + 99991)
+    s, h = shape.shared_intermediate, shape.hidden
+    mk = lambda *dims: (torch.randn(*dims, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    return DeviceSharedExpert(mk(s, h), mk(s, h), mk(h, s), mk(1, h))
+
+
+def rms_renorm(x: torch.Tensor) -> torch.Tensor:
+    """Keeps the activations at unit RMS from layer to layer (there is no attention or norm between
+    the MoE layers of the synthetic stack)."""
+    f = x.float()
+    return (f * torch.rsqrt(f.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+
+
+@dataclass
+class MoEStack:
+    shape: ModelShape
+    layers: list[DeviceLayer]
+    routers: list[torch.Tensor]
+    renormalize: bool
+
+    @classmethod
+    def build(cls, shape: ModelShape, encoding: str, num_layers: int, seed: int, device: torch.device,
+              renormalize: bool, skew: float = 1.0, experts: Optional[range] = None) -> "MoEStack":
+        layers = [random_layer(shape, encoding, seed + l, device, experts) for l in range(num_layers)]
+        routers = [router_weight(seed, l, shape, skew=skew).to(device) for l in range(num_layers)]
+        return cls(shape, layers, routers, renormalize)
+
+    def route(self, layer: int, x: torch.Tensor):
+        return ops.route_topk(x, self.routers[layer], self.shape.top_k, self.renormalize)
+
+    @property
+    def device_bytes(self) -> int:
+        return sum(l.device_storage_bytes for l in self.layers)
