@@ -98,4 +98,4 @@ def test_router_matches_oracle(model, renorm):
     chosen = own.gather(1, idx)
     kth = own.sort(dim=1, descending=True).values[:, shape.top_k - 1]
     assert bool((chosen >= kth[:, None] - 1e-9).all())
-    assert int((~same_logits).sum()) <= 0.01 * x.shape[0]
+    assert int((~same_logits).sum()) <= 0.03 * x.shape[0]
