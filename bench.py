@@ -296,14 +296,58 @@ def native_arm(args) -> None:
         torch.distributed.destroy_process_group()
 
 
+def kernel_case(args) -> None:
+    """A small case of one kernel, sized for a profiler capture: a few launches, < 1 GB on the device."""
+    from uma_qmoe_b200 import ops, synthetic as syn
+    from uma_qmoe_b200.stack import MoEStack
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = syn.OLMOE
+    stack = MoEStack.build(shape, "q4_group128", args.layers, SEED, dev, renormalize=True, skew=1.0)
+    if args.only == "decode":
+        x = syn.activations(SEED, 1).to(dev)
+        routes = [stack.route(l, x) for l in range(args.layers)]
+        ws = ops.decode_workspace(stack.layers[0], shape.top_k, None, dev)
+        out = torch.empty_like(x)
+
+        def run():
+            for l in range(args.layers):
+                ops.moe_decode(stack.layers[l], x, routes[l][1], routes[l][0], ws, out=out)
+        ms = timed(run, args.steps, args.warmup, 1) / args.layers
+        print(json.dumps({"case": "decode", "us_per_layer": ms * 1e3, "gbs": DECODE_BYTES / (ms / 1e3) / 1e9,
+                          "status": ops.workspace_status(ws)}))
+    else:
+        x = syn.activations(SEED, args.tokens).to(dev)
+        w, idx = stack.route(0, x)
+        routes = ops.route_sort(idx, w, shape.experts)
+        xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)
+        inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
+        yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
+
+        def run():
+            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter)
+            ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw)
+        ms = timed(run, args.steps, args.warmup, 1)
+        flops = 2.0 * xs.shape[0] * 3 * shape.hidden * shape.intermediate
+        print(json.dumps({"case": "gemm", "tokens": args.tokens, "ms_both_gemms": ms,
+                          "tflops": flops / (ms / 1e3) / 1e12, "status": int(routes.status.item())}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
+    ap.add_argument("--only", choices=("all", "decode", "gemm"), default="all",
+                    help="small single-kernel cases for profiler captures (not a bench line)")
+    ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
+    ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only != "all":
+        kernel_case(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         native_arm(args)
