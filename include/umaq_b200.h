@@ -93,6 +93,32 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /*
                     void* out_bf16 /* device [H] */, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* Decode for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Same computation and result as umaq_moe_decode, but the scratch the kernel
+ * needs (control words and the float32 intermediate of the selected experts) lives in a
+ * 64 KiB block built into the library instead of a caller workspace.  It is meant for
+ * hosts that are handed only their input and output buffers: code running inside another
+ * framework's stream callback or custom-call hook, or a plug-in whose memory is owned by
+ * the embedding runtime, where calling cudaMalloc (or any allocator) is not allowed or
+ * would serialise the device.  The call itself allocates nothing.
+ *
+ * Limits and rules:
+ *  - top_k * intermediate + shared intermediate must fit: at most 16128 float32 values
+ *    (OLMoE 8 x 1024 and Qwen 4 x 1408 + 5632 fit); larger shapes are refused with
+ *    UMAQ_ERR_WORKSPACE and a message, use umaq_moe_decode then.
+ *  - Every device that loads the library holds its own 64 KiB block until the process
+ *    exits.  The first call on a device looks up the block's device address; make that
+ *    first call outside any stream capture.
+ *  - All calls on a device share the block, and it keeps what the last call left; each
+ *    call clears the control words it needs on `stream` before it launches.  Two calls
+ *    that can overlap on the device (different streams without an ordering between
+ *    them) race on it: order them. */
+int umaq_moe_decode_static(const umaq_layer* layer, const umaq_shared_expert* shared /* may be NULL */,
+                           const void* hidden_bf16 /* device [H] */,
+                           const void* expert_indices /* device [top_k] */, int indices_are_int64,
+                           const float* routing_weights /* device [top_k] */, int top_k,
+                           void* out_bf16 /* device [H] */, void* stream);
+
 /* ---- router ---------------------------------------------------------------------
  * logits = bf16(x . Wr^T), softmax over the experts in float32, top-k (ties to the
  * lowest expert index), optional division by the top-k sum: the arithmetic of the

@@ -1,0 +1,66 @@
+"""The decode entry point that brings its own scratch (``umaq_moe_decode_static``).
+
+Some hosts of this library may not allocate device memory at the point where they call it -- a
+plug-in running inside another runtime's stream hook only gets its input and output buffers.  For
+them the library carries a fixed 64 KiB scratch block per device.  This test calls that entry point
+through the C ABI twice in a row and compares each result with the regular entry point (which works
+in a caller-provided workspace); both run the same kernel, so the outputs must agree bit for bit,
+and they must also meet the operator's tolerance against the CPU oracle.  The file sorts last so a
+run that stops at the first failure has already covered everything else.
+"""
+
+import ctypes as C
+
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+from tests.helpers import SEED, assert_parity, expert_source, stage_layer
+from uma_qmoe_b200 import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _call_static(layer, x, idx, w):
+    from uma_qmoe_b200 import _native
+    out = torch.empty_like(x)
+    stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    code = _native.lib().umaq_moe_decode_static(C.byref(layer.struct()), None, x.data_ptr(), idx.data_ptr(),
+                                                int(idx.dtype == torch.int64), w.data_ptr(), idx.numel(),
+                                                out.data_ptr(), stream)
+    _native.check(code, "umaq_moe_decode_static")
+    return out
+
+
+def test_static_scratch_decode_matches_workspace_decode_twice():
+    from uma_qmoe_b200 import ops
+    src = expert_source(SEED, 6, "olmoe", "q4_group128")
+    layer = stage_layer({e: src(e) for e in range(8)}, 8, 2048, 1024, "q4_group128", DEV)
+    ws = ops.decode_workspace(layer, 8, None, torch.device(DEV))
+    for call in range(2):                       # second call starts from the first call's leftovers
+        x = syn.activations(SEED + 40 + call, 1)
+        idx = torch.tensor([[3, 1, 0, 2, 5, 4, 7, 6]]).roll(call, dims=1).contiguous()
+        w = torch.full((1, 8), 0.125) + 0.01 * call
+        xd, idd, wd = x.to(DEV), idx.to(DEV), w.to(DEV)
+        got = _call_static(layer, xd, idd, wd)
+        ref = ops.moe_decode(layer, xd, idd, wd, ws)
+        torch.cuda.synchronize()
+        assert torch.equal(got, ref), f"call {call}: static-scratch result differs from the workspace result"
+        assert_parity(got.cpu(), orc.moe_forward(x, idx, w, src, num_experts=64, top_k=8, qwen=False))
+
+
+def test_static_scratch_rejects_shapes_beyond_its_block():
+    from uma_qmoe_b200 import _native
+    src = expert_source(SEED, 6, "olmoe", "q4_group128")
+    layer = stage_layer({0: src(0)}, 1, 2048, 1024, "q4_group128", DEV)
+    big = layer.struct()
+    big.intermediate = 4096                      # 8 x 4096 float32 values do not fit 64 KiB
+    x = syn.activations(1, 1).to(DEV)
+    idx = torch.zeros((1, 8), dtype=torch.int64, device=DEV)
+    w = torch.full((1, 8), 0.125, device=DEV)
+    out = torch.empty_like(x)
+    code = _native.lib().umaq_moe_decode_static(C.byref(big), None, x.data_ptr(), idx.data_ptr(), 1, w.data_ptr(), 8,
+                                                out.data_ptr(), None)
+    assert code == -2
+    assert b"64" in _native.lib().umaq_last_error() or b"65536" in _native.lib().umaq_last_error()

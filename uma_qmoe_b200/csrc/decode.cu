@@ -25,8 +25,11 @@
 // Latency discipline: a CTA runs each path once, so everything on the critical path is kept to a
 // handful of instructions: the stage list is computed once, in parallel, into shared memory; the
 // routes are fetched with one round of loads; partial sums are parked and reduced once per phase.
+#include "../../include/umaq_b200.h"
 #include "common.cuh"
 #include "decode.cuh"
+
+#include <mutex>
 
 #include <algorithm>
 
@@ -936,3 +939,98 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
 }
 
 }  // namespace umaq
+
+// ---- decode without a caller-provided workspace ---------------------------------------------------
+// Scratch of the entry point below: one fixed block per device that loads this library, held until
+// the process exits.  It has the layout of the decode workspace (control words, diagnostics, float32
+// intermediate) and therefore bounds the shapes the entry point accepts.
+namespace {
+constexpr size_t kStaticScratchBytes = 64 * 1024;
+}
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the scratch block on the current device.  The name of a __device__ array is only
+// a host-side stand-in for the symbol; the address a kernel can use has to be asked for, once per
+// device, with that device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    umaq::set_error("umaq_moe_decode_static: cannot identify the current device (%s)", cudaGetErrorString(e));
+    return umaq::ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      umaq::set_error("umaq_moe_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return umaq::ERR_LAUNCH;
+    }
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return umaq::ERR_NONE;
+}
+}  // namespace
+
+extern "C" int umaq_moe_decode_static(const umaq_layer* layer, const umaq_shared_expert* shared, const void* hidden_bf16,
+                                      const void* expert_indices, int indices_are_int64, const float* routing_weights,
+                                      int top_k, void* out_bf16, void* stream) {
+  using namespace umaq;
+  if (!layer || !hidden_bf16 || !expert_indices || !routing_weights || !out_bf16) {
+    set_error("umaq_moe_decode_static: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  const int s_inter = shared ? shared->intermediate : 0;
+  if (top_k < 1 || top_k > 8 || layer->intermediate < 1 || s_inter < 0) {
+    set_error("umaq_moe_decode_static: unsupported shape");
+    return ERR_BAD_ARGUMENT;
+  }
+  const size_t need = decode_workspace_bytes(top_k, layer->intermediate, s_inter);
+  if (need > kStaticScratchBytes) {
+    set_error("umaq_moe_decode_static: top_k * intermediate + shared intermediate = %lld float32 values need %zu bytes "
+              "of scratch, the built-in block holds %zu; use umaq_moe_decode with a caller workspace",
+              (long long)top_k * layer->intermediate + s_inter, need, kStaticScratchBytes);
+    return ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != ERR_NONE) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The block keeps whatever the previous call left.  The control words (status, barrier counter)
+  // must start from zero; the intermediate area is fully rewritten before it is read.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 64, st);
+  if (e != cudaSuccess) { set_error("umaq_moe_decode_static: cudaMemsetAsync: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+  DecodeParams p{};
+  p.gate = static_cast<const uint8_t*>(layer->gate);
+  p.up = static_cast<const uint8_t*>(layer->up);
+  p.down = static_cast<const uint8_t*>(layer->down);
+  p.gate_s = layer->gate_scales; p.up_s = layer->up_scales; p.down_s = layer->down_scales;
+  p.enc = layer->encoding; p.experts = layer->num_experts; p.hidden = layer->hidden; p.inter = layer->intermediate;
+  p.top_k = top_k;
+  p.x = static_cast<const __nv_bfloat16*>(hidden_bf16);
+  p.idx = expert_indices; p.idx64 = indices_are_int64; p.w = routing_weights;
+  if (shared) {
+    p.sh_gate = static_cast<const __nv_bfloat16*>(shared->gate);
+    p.sh_up = static_cast<const __nv_bfloat16*>(shared->up);
+    p.sh_down = static_cast<const __nv_bfloat16*>(shared->down);
+    p.sh_gatevec = static_cast<const __nv_bfloat16*>(shared->gate_vec);
+    p.shared_inter = shared->intermediate;
+    if (!p.sh_gate || !p.sh_up || !p.sh_down || !p.sh_gatevec) {
+      set_error("umaq_moe_decode_static: shared expert with a null tensor");
+      return ERR_BAD_ARGUMENT;
+    }
+  }
+  p.out = static_cast<__nv_bfloat16*>(out_bf16);
+  uint8_t* ws = static_cast<uint8_t*>(scratch);
+  p.sync = reinterpret_cast<unsigned*>(ws);
+  p.amax = reinterpret_cast<unsigned*>(ws + 64);
+  p.inter_buf = reinterpret_cast<float*>(ws + kDecodeWsHeader);
+  return launch_moe_decode(p, st);
+}
