@@ -160,7 +160,7 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared /
  * torch.argsort(stable) / bincount / cumsum at src/uma_qmoe/native_backend.py:531-543.
  * Route i = token * top_k + slot.  Outputs (all device): counts[E], offsets[E+1],
  * sorted_route[routes] (route ids in expert order), route_pos[routes] (its inverse),
- * sorted_weight[routes], and the 128-route tile list of the grouped GEMM:
+ * sorted_weight[routes], and the tile list of the grouped GEMM (up to 256 routes of one expert each):
  * *num_tiles and tile_table = int[3 * max_tiles] holding expert, first row, row count.
  * max_tiles >= ceil(routes / 128) + E.  *status: sticky error word, zero it first. */
 int umaq_route_sort(const void* expert_indices, int indices_are_int64, const float* routing_weights, int tokens,

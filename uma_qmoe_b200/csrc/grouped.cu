@@ -7,8 +7,10 @@
 // (src/uma_qmoe/native/packed_q4_kernel.cu:560-776 Q4, :894-1099 Q8, launched from :1535-1641 and
 // :1691-1762) and its torch._grouped_mm path for BF16 layers (src/uma_qmoe/native_backend.py:958-1005).
 //
-// One CTA computes one 128-route x 128-column tile.  Warp 0 drives TMA: activation tiles
-// (128 rows x 64 k, 128-byte swizzle) and the packed weight rows of the same k range.  Eight warps
+// One CTA computes one tile of up to 256 routes x 128 columns: two M = 128 accumulators that share
+// every converted weight tile, so the conversion work per route is halved.  Warp 0 drives TMA:
+// activation tiles (2 x 128 rows x 64 k, 128-byte swizzle) and the packed weight rows of the same k
+// range.  Eight warps
 // turn the packed codes into BF16 (code * scale) and write the canonical K-major 128-byte-swizzled
 // B tile the tensor core reads; warp 1 issues tcgen05.mma (M = 128, N = 128, K = 16) with the FP32
 // accumulator in tensor memory and signals buffers free with tcgen05.commit.  The same eight warps
@@ -33,7 +35,8 @@ constexpr int kInStages = 4;          // TMA ring: activation tile + packed weig
 constexpr int kBStages = 3;           // converted B tiles
 constexpr int kConvertWarps = 8;
 constexpr int kGemmThreads = (2 + kConvertWarps) * 32;
-constexpr int kTmemCols = 128;
+constexpr int kHalves = 2;            // M = 128 accumulators per tile
+constexpr int kTmemCols = 128 * kHalves;
 constexpr int kMaxGroups = 16;        // quantised K <= 2048
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------------------------
@@ -152,7 +155,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // layout: [A stages][packed stages][B stages][scales][control]
   constexpr int kPackedRow = ENC == ENC_Q4 ? BK / 2 : BK;               // bytes of codes per row and k chunk
   constexpr int kPackedBytes = ENC == ENC_BF16 ? 0 : BN * kPackedRow;
-  constexpr int kATile = BM * BK * 2, kBTile = BN * BK * 2;
+  constexpr int kAHalf = BM * BK * 2, kATile = kHalves * kAHalf, kBTile = BN * BK * 2;
   uint8_t* sA = smem_raw;
   uint8_t* sP = sA + kInStages * kATile;
   uint8_t* sB = sP + kInStages * kPackedBytes;
@@ -167,6 +170,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int K = p.k;
   const int nk = K / BK;
   const int groups = K >> 7;
+  const bool two = nrows > BM;             // the tile has a second 128-route half
   volatile int* abort_flag = &sh.abort_flag;
 
   if (tid == 0) {
@@ -207,9 +211,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (kc >= kInStages && !mbar_wait(&sh.in_empty[s], ((kc / kInStages) - 1) & 1)) {
           atomicExch(p.status, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; break;
         }
-        const uint32_t bytes = kATile + (ENC == ENC_BF16 ? kBTile : kPackedBytes);
+        const uint32_t bytes = (two ? kATile : kAHalf) + (ENC == ENC_BF16 ? kBTile : kPackedBytes);
         mbar_expect_tx(&sh.in_full[s], bytes);
         tma_load_2d(sA + s * kATile, &map_a, kc * BK, row0, &sh.in_full[s]);
+        if (two) tma_load_2d(sA + s * kATile + kAHalf, &map_a, kc * BK, row0 + BM, &sh.in_full[s]);
         if (ENC == ENC_BF16) {
           uint8_t* dst = sB + s * kBTile;
           if (MODE == 0) {
@@ -247,8 +252,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t a_addr = smem_u32(sA + s * kATile), b_addr = smem_u32(sB + sb * kBTile);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k) {
-          tc_mma_bf16(tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), kInstrDesc,
-                      (kc | k) ? 1u : 0u);
+          const uint64_t bdesc = smem_desc_sw128(b_addr + k * 32);
+          tc_mma_bf16(tmem, smem_desc_sw128(a_addr + k * 32), bdesc, kInstrDesc, (kc | k) ? 1u : 0u);
+          if (two) tc_mma_bf16(tmem + BN, smem_desc_sw128(a_addr + kAHalf + k * 32), bdesc, kInstrDesc, (kc | k) ? 1u : 0u);
         }
         tc_commit(&sh.in_empty[s]);                 // A tile (and a BF16 B tile) may be overwritten
         if (ENC != ENC_BF16) tc_commit(&sh.b_empty[sb]);
@@ -292,8 +298,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (ok) {
       tc_fence_after();
       const int quarter = warp & 3, ch = (warp - 2) >> 2;
-      const int row = quarter * 32 + lane;           // route row inside the tile
-      const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16);
+      for (int half = 0; half < (two ? 2 : 1); ++half) {
+      const int row = half * BM + quarter * 32 + lane;   // route row inside the tile
+      const uint32_t tbase = tmem + half * BN + ((uint32_t)(quarter * 32) << 16);
       const bool valid = row < nrows;
       const long long grow = (long long)row0 + row;
       if (MODE == 0) {
@@ -345,6 +352,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      }
       tc_fence_before();
     }
   }
@@ -359,7 +367,7 @@ template <int ENC>
 constexpr size_t gemm_smem_bytes() {
   constexpr int packed = ENC == ENC_BF16 ? 0 : BN * (ENC == ENC_Q4 ? BK / 2 : BK);
   constexpr int nb = ENC == ENC_BF16 ? kInStages : kBStages;
-  return (size_t)kInStages * (BM * BK * 2 + packed) + (size_t)nb * BN * BK * 2 + BN * kMaxGroups * 4 + sizeof(GemmShared) + 1024;
+  return (size_t)kInStages * (kHalves * BM * BK * 2 + packed) + (size_t)nb * BN * BK * 2 + BN * kMaxGroups * 4 + sizeof(GemmShared) + 1024;
 }
 
 // ---- tensor maps ----------------------------------------------------------------------------------

@@ -94,11 +94,144 @@ router_topk_kernel(const RouterArgs a) {
   }
 }
 
+// Softmax over the experts in float32, top-k by repeated arg-max (value descending, index ascending),
+// optional renormalisation; `probs` holds the BF16-rounded logits of one token on entry.  One warp.
+__device__ __forceinline__ void softmax_topk_warp(float* probs, int E, int top_k, int renormalize, int lane,
+                                                  float* out_w, long long* out_i) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, probs[e]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(probs[e] - mx);
+    probs[e] = v;
+    sum += v;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
+  __syncwarp();
+  float topsum = 0.f, myval = 0.f;
+  long long myidx = 0;
+  for (int j = 0; j < top_k; ++j) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = probs[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == j) { myval = best; myidx = bi; }
+    topsum += best;
+    if (lane == 0) probs[bi] = -2.f;
+    __syncwarp();
+  }
+  if (lane < top_k) {
+    out_w[lane] = renormalize ? myval / topsum : myval;
+    out_i[lane] = myidx;
+  }
+}
+
+// Tiled router for E <= 64: a CTA takes 32 tokens and all experts, stages 128-wide k chunks of x and
+// Wr in shared memory (rows padded by 16 bytes against bank conflicts); thread (ty, tx) accumulates
+// tokens {ty, ty+16} x experts {tx, tx+16, tx+32, tx+48}.  The BF16 products are exact in float32;
+// runs of 32 are summed in float32 and the runs in float64, which keeps the BF16 rounding of the
+// logit equal to that of an exactly rounded dot product in all but ~1 logit in 10^4.
+constexpr int kRtTokens = 32, kRtExperts = 64, kRtChunk = 128, kRtPitch = kRtChunk + 8;
+
+__global__ void __launch_bounds__(256) router_tiled_kernel(const RouterArgs a) {
+  __shared__ __align__(16) __nv_bfloat16 xs[kRtTokens][kRtPitch];
+  __shared__ __align__(16) __nv_bfloat16 ws[kRtExperts][kRtPitch];
+  __shared__ float logit[kRtTokens][kRtExperts];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int token0 = blockIdx.x * kRtTokens;
+  const int H = a.hidden, E = a.experts;
+  double acc[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+  for (int kc = 0; kc < H; kc += kRtChunk) {
+    __syncthreads();
+    for (int v = tid; v < kRtTokens * (kRtChunk / 8); v += 256) {
+      const int r = v >> 4, c = v & 15;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (token0 + r < a.tokens) w = *reinterpret_cast<const uint4*>(a.x + (size_t)(token0 + r) * H + kc + c * 8);
+      *reinterpret_cast<uint4*>(&xs[r][c * 8]) = w;
+    }
+    for (int v = tid; v < kRtExperts * (kRtChunk / 8); v += 256) {
+      const int r = v >> 4, c = v & 15;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (r < E) w = *reinterpret_cast<const uint4*>(a.weight + (size_t)r * H + kc + c * 8);
+      *reinterpret_cast<uint4*>(&ws[r][c * 8]) = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int run = 0; run < kRtChunk / 32; ++run) {
+      float part[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < 32; kk += 8) {
+        uint4 xv[2], wv[4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) xv[i] = *reinterpret_cast<const uint4*>(&xs[ty + 16 * i][run * 32 + kk]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wv[j] = *reinterpret_cast<const uint4*>(&ws[tx + 16 * j][run * 32 + kk]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint32_t xw[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t ww[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              part[i][j] = fmaf(__uint_as_float(xw[q] << 16), __uint_as_float(ww[q] << 16), part[i][j]);
+              part[i][j] = fmaf(__uint_as_float(xw[q] & 0xffff0000u), __uint_as_float(ww[q] & 0xffff0000u), part[i][j]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += (double)part[i][j];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float l = bf16_round((float)acc[i][j]);            // F.linear output in BF16
+      logit[ty + 16 * i][tx + 16 * j] = l;
+      const int t = token0 + ty + 16 * i, e = tx + 16 * j;
+      if (a.out_logits && t < a.tokens && e < E) a.out_logits[(size_t)t * E + e] = __float2bfloat16_rn(l);
+    }
+  __syncthreads();
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int r = warp; r < kRtTokens; r += 8) {
+    const int t = token0 + r;
+    if (t < a.tokens)
+      softmax_topk_warp(logit[r], E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)t * a.top_k,
+                        a.out_indices + (size_t)t * a.top_k);
+  }
+}
+
 // ---- stable expert sort of the routes, one CTA --------------------------------------------------------
 // Route i = token * top_k + slot.  Warp w owns a contiguous chunk of routes; a per-warp histogram and
 // a scan over (expert, warp) give every warp its first position inside each expert's run, and ranks
 // inside a 32-route batch come from __match_any_sync, so equal experts keep their route order.
 constexpr int kSortThreads = 1024;
+constexpr int kTileRows = 256;       // routes per grouped-GEMM tile (two M = 128 accumulators)
 constexpr int kMaxSortExperts = 128;
 
 __device__ __forceinline__ int load_expert(const void* idx, int idx64, long long i) {
@@ -136,8 +269,8 @@ __global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs
       const int c = total[e];
       a.offsets[e] = run;
       total[e] = run;
-      for (int r = 0; r < c && tiles < a.max_tiles; r += 128, ++tiles) {
-        a.tile_expert[tiles] = e; a.tile_row0[tiles] = run + r; a.tile_rows[tiles] = min(128, c - r);
+      for (int r = 0; r < c && tiles < a.max_tiles; r += kTileRows, ++tiles) {
+        a.tile_expert[tiles] = e; a.tile_row0[tiles] = run + r; a.tile_rows[tiles] = min(kTileRows, c - r);
       }
       run += c;
     }
@@ -246,9 +379,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
 
 // tile table of a dense [rows, k] matrix treated as one expert (the Qwen shared expert in prefill)
 __global__ void dense_tiles_kernel(int rows, int* num_tiles, int* tile_expert, int* tile_row0, int* tile_rows) {
-  const int tiles = (rows + 127) / 128;
+  const int tiles = (rows + 255) / 256;
   for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
-    tile_expert[t] = 0; tile_row0[t] = t * 128; tile_rows[t] = min(128, rows - t * 128);
+    tile_expert[t] = 0; tile_row0[t] = t * 256; tile_rows[t] = min(256, rows - t * 256);
   }
   if (threadIdx.x == 0) *num_tiles = tiles;
 }
@@ -270,6 +403,10 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
   if (a.tokens <= 0 || a.hidden % 256 || a.experts < a.top_k || a.top_k < 1 || a.top_k > 32 || a.experts > 1024) {
     set_error("router: unsupported shape (tokens %d, hidden %d, experts %d, top_k %d)", a.tokens, a.hidden, a.experts, a.top_k);
     return ERR_BAD_ARGUMENT;
+  }
+  if (a.experts <= kRtExperts && a.hidden % kRtChunk == 0 && a.top_k <= 32) {
+    router_tiled_kernel<<<(a.tokens + kRtTokens - 1) / kRtTokens, 256, 0, stream>>>(a);
+    return check_launch("router");
   }
   const int blocks = (a.tokens + kRouterWarps - 1) / kRouterWarps;
   router_topk_kernel<<<blocks, kRouterWarps * 32, kRouterWarps * a.experts * sizeof(float), stream>>>(a);
