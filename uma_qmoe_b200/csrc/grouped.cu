@@ -7,12 +7,14 @@
 // (src/uma_qmoe/native/packed_q4_kernel.cu:560-776 Q4, :894-1099 Q8, launched from :1535-1641 and
 // :1691-1762) and its torch._grouped_mm path for BF16 layers (src/uma_qmoe/native_backend.py:958-1005).
 //
-// One CTA computes one tile of up to 256 routes x 128 columns: two M = 128 accumulators that share
-// every converted weight tile, so the conversion work per route is halved.  Warp 0 drives TMA:
+// One CTA computes one tile of up to 256 routes x 256 columns: two M = 128, N = 256 accumulators
+// (all 512 tensor-memory columns) that share every converted weight tile.  The wide tile is what keeps
+// the activation traffic from L2 below the tensor rate: a 128-column tile re-reads the activations
+// 16 times per layer and is L2-bound at 40 % of the tensor peak.  Warp 0 drives TMA:
 // activation tiles (2 x 128 rows x 64 k, 128-byte swizzle) and the packed weight rows of the same k
 // range.  Eight warps
 // turn the packed codes into BF16 (code * scale) and write the canonical K-major 128-byte-swizzled
-// B tile the tensor core reads; warp 1 issues tcgen05.mma (M = 128, N = 128, K = 16) with the FP32
+// B tile the tensor core reads; warp 1 issues tcgen05.mma (M = 128, N = 256, K = 16) with the FP32
 // accumulator in tensor memory and signals buffers free with tcgen05.commit.  The same eight warps
 // then read the accumulator with tcgen05.ld and run the epilogue.  BF16 layers skip the conversion:
 // TMA writes the swizzled B tile directly.
@@ -30,13 +32,14 @@
 namespace umaq {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int kInStages = 4;          // TMA ring: activation tile + packed weight rows
-constexpr int kBStages = 3;           // converted B tiles
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kInStages = 3;          // TMA ring of activation tiles (2 x 128 rows x 64 k each)
+constexpr int kBStages = 2;           // converted B tiles (256 rows x 64 k)
 constexpr int kConvertWarps = 8;
-constexpr int kGemmThreads = (2 + kConvertWarps) * 32;
+constexpr int kGemmThreads = (3 + kConvertWarps) * 32;   // + activation TMA, MMA issuer, weight TMA
+constexpr int kWeightWarp = 2 + kConvertWarps;
 constexpr int kHalves = 2;            // M = 128 accumulators per tile
-constexpr int kTmemCols = 128 * kHalves;
+constexpr int kTmemCols = BN * kHalves;   // 512: the whole tensor memory of the SM
 constexpr int kMaxGroups = 16;        // quantised K <= 2048
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------------------------
@@ -97,9 +100,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 // kind::f16, BF16 x BF16 -> FP32, both operands K-major, M = 128, N = BN
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
+constexpr int kMaxPStages = 4;        // packed-weight ring (8 KiB stages for Q4)
 struct GemmShared {
   uint64_t in_full[kInStages];
   uint64_t in_empty[kInStages];
+  uint64_t p_full[kMaxPStages];
+  uint64_t p_empty[kMaxPStages];
   uint64_t b_full[kBStages];
   uint64_t b_empty[kBStages];
   uint64_t scales_full;
@@ -156,9 +162,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int kPackedRow = ENC == ENC_Q4 ? BK / 2 : BK;               // bytes of codes per row and k chunk
   constexpr int kPackedBytes = ENC == ENC_BF16 ? 0 : BN * kPackedRow;
   constexpr int kAHalf = BM * BK * 2, kATile = kHalves * kAHalf, kBTile = BN * BK * 2;
+  constexpr int kPStages = ENC == ENC_Q4 ? 4 : 2;
   uint8_t* sA = smem_raw;
   uint8_t* sP = sA + kInStages * kATile;
-  uint8_t* sB = sP + kInStages * kPackedBytes;
+  uint8_t* sB = sP + kPStages * kPackedBytes;
   constexpr int kNumB = ENC == ENC_BF16 ? kInStages : kBStages;
   float* sScales = reinterpret_cast<float*>(sB + kNumB * kBTile);
   GemmShared& sh = *reinterpret_cast<GemmShared*>(reinterpret_cast<uint8_t*>(sScales) + BN * kMaxGroups * 4);
@@ -174,7 +181,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   volatile int* abort_flag = &sh.abort_flag;
 
   if (tid == 0) {
-    for (int s = 0; s < kInStages; ++s) { mbar_init(&sh.in_full[s], 1); mbar_init(&sh.in_empty[s], 1 + (ENC == ENC_BF16 ? 0 : kConvertWarps)); }
+    for (int s = 0; s < kInStages; ++s) { mbar_init(&sh.in_full[s], 1); mbar_init(&sh.in_empty[s], 1); }
+    for (int s = 0; s < kMaxPStages; ++s) { mbar_init(&sh.p_full[s], 1); mbar_init(&sh.p_empty[s], kConvertWarps); }
     for (int s = 0; s < kBStages; ++s) { mbar_init(&sh.b_full[s], kConvertWarps); mbar_init(&sh.b_empty[s], 1); }
     mbar_init(&sh.scales_full, 1);
     mbar_init(&sh.acc_full, 1);
@@ -196,22 +204,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const long long wrow0 = (long long)expert * p.n_rows + f0;
 
   if (warp == 0) {
-    // ===================== TMA producer =========================================================
+    // ===================== TMA producer: activation tiles (and BF16 weight tiles) ==================
     if (lane == 0) {
-      if (ENC != ENC_BF16) {
-        // scales of the tile's rows: contiguous [rows, K/128] float32
-        const uint32_t half_bytes = (uint32_t)(MODE == 0 ? BN / 2 : BN) * groups * 4;
-        mbar_expect_tx(&sh.scales_full, MODE == 0 ? 2 * half_bytes : half_bytes);
-        bulk_g2s(sScales, p.scales0 + wrow0 * groups, half_bytes, &sh.scales_full);
-        if (MODE == 0) bulk_g2s(sScales + (BN / 2) * groups, p.scales1 + wrow0 * groups, half_bytes, &sh.scales_full);
-      }
       int issued = 0;
       for (int kc = 0; kc < nk && !*abort_flag; ++kc) {
         const int s = kc % kInStages;
         if (kc >= kInStages && !mbar_wait(&sh.in_empty[s], ((kc / kInStages) - 1) & 1)) {
           atomicExch(p.status, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; break;
         }
-        const uint32_t bytes = (two ? kATile : kAHalf) + (ENC == ENC_BF16 ? kBTile : kPackedBytes);
+        const uint32_t bytes = (two ? kATile : kAHalf) + (ENC == ENC_BF16 ? kBTile : 0);
         mbar_expect_tx(&sh.in_full[s], bytes);
         tma_load_2d(sA + s * kATile, &map_a, kc * BK, row0, &sh.in_full[s]);
         if (two) tma_load_2d(sA + s * kATile + kAHalf, &map_a, kc * BK, row0 + BM, &sh.in_full[s]);
@@ -223,14 +224,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           } else {
             tma_load_2d(dst, &map_b0, kc * BK, (int)wrow0, &sh.in_full[s]);
           }
-        } else {
-          uint8_t* dst = sP + s * kPackedBytes;
-          if (MODE == 0) {
-            tma_load_2d(dst, &map_b0, kc * kPackedRow, (int)wrow0, &sh.in_full[s]);
-            tma_load_2d(dst + (BN / 2) * kPackedRow, &map_b1, kc * kPackedRow, (int)wrow0, &sh.in_full[s]);
-          } else {
-            tma_load_2d(dst, &map_b0, kc * kPackedRow, (int)wrow0, &sh.in_full[s]);
-          }
         }
         issued = kc + 1;
       }
@@ -238,6 +231,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (*abort_flag)
         for (int kc = issued > kInStages ? issued - kInStages : 0; kc < issued; ++kc)
           mbar_wait(&sh.in_full[kc % kInStages], (kc / kInStages) & 1);
+    }
+  } else if (warp == kWeightWarp) {
+    // ===================== TMA producer: scales and packed weight rows, on their own deeper ring ====
+    if (lane == 0 && ENC != ENC_BF16) {
+      const uint32_t half_bytes = (uint32_t)(MODE == 0 ? BN / 2 : BN) * groups * 4;
+      mbar_expect_tx(&sh.scales_full, MODE == 0 ? 2 * half_bytes : half_bytes);
+      bulk_g2s(sScales, p.scales0 + wrow0 * groups, half_bytes, &sh.scales_full);
+      if (MODE == 0) bulk_g2s(sScales + (BN / 2) * groups, p.scales1 + wrow0 * groups, half_bytes, &sh.scales_full);
+      int issued = 0;
+      for (int kc = 0; kc < nk && !*abort_flag; ++kc) {
+        const int s = kc % kPStages;
+        if (kc >= kPStages && !mbar_wait(&sh.p_empty[s], ((kc / kPStages) - 1) & 1)) {
+          atomicExch(p.status, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; break;
+        }
+        mbar_expect_tx(&sh.p_full[s], kPackedBytes);
+        uint8_t* dst = sP + s * kPackedBytes;
+        if (MODE == 0) {
+          tma_load_2d(dst, &map_b0, kc * kPackedRow, (int)wrow0, &sh.p_full[s]);
+          tma_load_2d(dst + (BN / 2) * kPackedRow, &map_b1, kc * kPackedRow, (int)wrow0, &sh.p_full[s]);
+        } else {
+          tma_load_2d(dst, &map_b0, kc * kPackedRow, (int)wrow0, &sh.p_full[s]);
+        }
+        issued = kc + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait(&sh.scales_full, 0);
+        for (int kc = issued > kPStages ? issued - kPStages : 0; kc < issued; ++kc)
+          mbar_wait(&sh.p_full[kc % kPStages], (kc / kPStages) & 1);
+      }
     }
   } else if (warp == 1) {
     // ===================== MMA issuer ============================================================
@@ -261,35 +283,39 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_commit(&sh.acc_full);
     }
-  } else {
+  } else if (warp >= 2) {
     // ===================== conversion warps, then epilogue =======================================
     const int ct = tid - 64;                         // 0..255
     if (ENC != ENC_BF16) {
-      const int r = ct >> 1, h = ct & 1;             // B-tile row and 32-wide half of the k chunk
+      const int r = ct;                               // B-tile row of this thread (256 rows, 256 threads)
       bool ok = mbar_wait(&sh.scales_full, 0);
       if (!ok && lane == 0) { atomicExch(p.status, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; }
       for (int kc = 0; kc < nk && !*abort_flag; ++kc) {
-        const int s = kc % kInStages, sb = kc % kBStages;
-        ok = mbar_wait(&sh.in_full[s], (kc / kInStages) & 1);
+        const int s = kc % kPStages, sb = kc % kBStages;
+        ok = mbar_wait(&sh.p_full[s], (kc / kPStages) & 1);
         if (ok && kc >= kBStages) ok = mbar_wait(&sh.b_empty[sb], ((kc / kBStages) - 1) & 1);
         if (!ok) { if (lane == 0) { atomicExch(p.status, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; } break; }
         const float scale = sScales[r * groups + (kc >> 1)];
-        uint32_t out[16];
-        const uint8_t* src = sP + s * kPackedBytes + r * kPackedRow + h * (kPackedRow / 2);
-        if (ENC == ENC_Q4) {
-          convert_q4(*reinterpret_cast<const uint4*>(src), scale, out);
-        } else {
-          convert_q8(*reinterpret_cast<const uint4*>(src), *reinterpret_cast<const uint4*>(src + 16), scale, out);
-        }
+        const uint8_t* src = sP + s * kPackedBytes + r * kPackedRow;
         uint8_t* dstrow = sB + sb * kBTile + r * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int chunk = (h * 4 + i) ^ (r & 7);
-          *reinterpret_cast<uint4*>(dstrow + chunk * 16) = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+        for (int h = 0; h < 2; ++h) {                 // the two 32-wide halves of the k chunk
+          uint32_t out[16];
+          if (ENC == ENC_Q4) {
+            convert_q4(*reinterpret_cast<const uint4*>(src + h * 16), scale, out);
+          } else {
+            convert_q8(*reinterpret_cast<const uint4*>(src + h * 32), *reinterpret_cast<const uint4*>(src + h * 32 + 16),
+                       scale, out);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int chunk = (h * 4 + i) ^ (r & 7);
+            *reinterpret_cast<uint4*>(dstrow + chunk * 16) = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+          }
         }
         fence_proxy_async();                         // generic-proxy writes -> visible to the tensor core
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&sh.b_full[sb]); mbar_arrive(&sh.in_empty[s]); }
+        if (lane == 0) { mbar_arrive(&sh.b_full[sb]); mbar_arrive(&sh.p_empty[s]); }
       }
     }
     // ---- epilogue: warp quarter = warp % 4 (its 32 accumulator lanes), column half = (warp-2)/4 ---
@@ -304,42 +330,48 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const bool valid = row < nrows;
       const long long grow = (long long)row0 + row;
       if (MODE == 0) {
-        uint32_t g[32], u[32];
-        tmem_ld32(tbase + ch * 32, g);
-        tmem_ld32(tbase + BN / 2 + ch * 32, u);
-        tmem_ld_wait();
-        if (valid) {
-          __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + ch * 32;
-          uint32_t o[16];
+        // columns [0, BN/2) gate, [BN/2, BN) up; this warp: features ch*64 .. ch*64+63 in two parts
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float a = silu_f32(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-            const float b = silu_f32(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]);
-            const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-            o[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
-          }
-          if (p.permute_out) {
-            // natural pairs (f0,f1)(f2,f3)(f4,f5)(f6,f7) -> (f0,f4)(f1,f5)(f2,f6)(f3,f7) per run of 8
+        for (int part = 0; part < 2; ++part) {
+          uint32_t g[32], u[32];
+          const int c0 = ch * 64 + part * 32;
+          tmem_ld32(tbase + c0, g);
+          tmem_ld32(tbase + BN / 2 + c0, u);
+          tmem_ld_wait();
+          if (valid) {
+            __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + c0;
+            uint32_t o[16];
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {
-              const uint32_t a = o[4 * q8], b = o[4 * q8 + 1], c = o[4 * q8 + 2], d = o[4 * q8 + 3];
-              o[4 * q8] = prmt(a, c, 0x5410); o[4 * q8 + 1] = prmt(a, c, 0x7632);
-              o[4 * q8 + 2] = prmt(b, d, 0x5410); o[4 * q8 + 3] = prmt(b, d, 0x7632);
+            for (int j = 0; j < 32; j += 2) {
+              const float a = silu_f32(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+              const float b = silu_f32(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]);
+              const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+              o[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
             }
-          }
+            if (p.permute_out) {
+              // natural pairs (f0,f1)(f2,f3)(f4,f5)(f6,f7) -> (f0,f4)(f1,f5)(f2,f6)(f3,f7) per run of 8
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
-            reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              for (int q8 = 0; q8 < 4; ++q8) {
+                const uint32_t a = o[4 * q8], b = o[4 * q8 + 1], c = o[4 * q8 + 2], d = o[4 * q8 + 3];
+                o[4 * q8] = prmt(a, c, 0x5410); o[4 * q8 + 1] = prmt(a, c, 0x7632);
+                o[4 * q8 + 2] = prmt(b, d, 0x5410); o[4 * q8 + 3] = prmt(b, d, 0x7632);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
         }
       } else {
         const float wr = !valid ? 0.f : (p.route_weight ? p.route_weight[grow] : 1.f);
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
+        for (int part = 0; part < 4; ++part) {
           uint32_t a[32];
-          tmem_ld32(tbase + ch * 64 + part * 32, a);
+          const int c0 = ch * 128 + part * 32;
+          tmem_ld32(tbase + c0, a);
           tmem_ld_wait();
           if (valid) {
-            __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + ch * 64 + part * 32;
+            __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + c0;
             uint32_t o[16];
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
@@ -367,7 +399,8 @@ template <int ENC>
 constexpr size_t gemm_smem_bytes() {
   constexpr int packed = ENC == ENC_BF16 ? 0 : BN * (ENC == ENC_Q4 ? BK / 2 : BK);
   constexpr int nb = ENC == ENC_BF16 ? kInStages : kBStages;
-  return (size_t)kInStages * (kHalves * BM * BK * 2 + packed) + (size_t)nb * BN * BK * 2 + BN * kMaxGroups * 4 + sizeof(GemmShared) + 1024;
+  constexpr int np = ENC == ENC_Q4 ? 4 : 2;
+  return (size_t)kInStages * (kHalves * BM * BK * 2) + (size_t)np * packed + (size_t)nb * BN * BK * 2 + BN * kMaxGroups * 4 + sizeof(GemmShared) + 1024;
 }
 
 // ---- tensor maps ----------------------------------------------------------------------------------
@@ -424,7 +457,7 @@ int launch_one(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap&
 
 int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
   const int K = a.k;
-  if (K % 128 || a.n_rows % (a.mode == 0 ? 64 : 128) || a.total_rows <= 0 || a.max_tiles <= 0 ||
+  if (K % 128 || a.n_rows % (a.mode == 0 ? BN / 2 : BN) || a.total_rows <= 0 || a.max_tiles <= 0 ||
       (a.enc != ENC_BF16 && K > kMaxGroups * 128)) {
     set_error("grouped: unsupported shape (k %d, rows per expert %d)", K, a.n_rows);
     return ERR_BAD_ARGUMENT;
