@@ -1,4 +1,5 @@
-// Batch-1 decode: one persistent cooperative kernel per MoE layer call.
+// Batch-1 decode: two lean kernels, a thousand small CTAs each, chained by programmatic dependent
+// launch.
 //
 //   out = sum_slot w_slot * Down_e( SiLU(Gate_e x) * Up_e x )   (+ Qwen shared expert)
 //
@@ -9,437 +10,99 @@
 // correctness path (src/uma_qmoe/custom_op.py:301-340, :465-506): float32 intermediate, one BF16
 // rounding of every expert contribution and of the running sum, experts in ascending order.
 //
-// Shape of the work.  The layer is ~27 MB (OLMoE Q4) to ~105 MB (Qwen Q8 + BF16 shared expert) of
-// weights read exactly once, i.e. a pure HBM stream of a few microseconds.  One CTA per SM; every
-// CTA owns a byte-balanced, contiguous range of gate/up feature rows (phase A) and of output rows
-// (phase B).  A producer warp streams the CTA's rows with untiled bulk async copies into a ring of
-// shared-memory stages guarded by mbarriers; it never waits for the phase boundary, so the down
-// projection rows are already in flight or resident while phase A computes.  Eight consumer warps
-// dequantise 64-byte row blocks in registers into exact integer-valued fp16
-// (nibble | 0x6400 = 1024 + code, no per-weight arithmetic) and feed m16n8k16 warp MMAs whose B
-// operand is the activation vector; the group scale and the constant code bias are applied once
-// per 128-wide group in float32.  On B200 the HBM-to-issue-rate ratio leaves < 3 instructions per
-// 4-bit weight, which rules out per-weight FMA on the CUDA cores; the warp MMA does the multiply-add
-// and the CUDA cores only unpack.  The two phases are separated by one bounded grid barrier.
+// The layer is ~27 MB (OLMoE Q4) to ~105 MB (Qwen Q8 + BF16 shared expert) of weights read exactly
+// once: a pure HBM stream of a few microseconds, during which nothing may serialise.  Kernel A
+// (gate/up + SwiGLU) gives every 16-row warp-MMA tile (8 features: 8 gate rows + 8 up rows, all of K)
+// its own 128-thread CTA; kernel B (down + ordered combine) gives every 8 output rows a CTA that
+// walks the selected experts in pairs.  Each thread issues all its 16-byte weight loads up front, so
+// with ~7 resident CTAs per SM well over 100 KB are in flight per SM and latency is hidden by
+// parallelism, not by a software pipeline; no CTA waits for another.  Kernel B is launched with
+// programmatic stream serialisation: its CTAs start while kernel A drains, issue their weight loads,
+// and only then wait for A's intermediate.
 //
-// Latency discipline: a CTA runs each path once, so everything on the critical path is kept to a
-// handful of instructions: the stage list is computed once, in parallel, into shared memory; the
-// routes are fetched with one round of loads; partial sums are parked and reduced once per phase.
+// Dequantisation is free of per-weight arithmetic: nibbles become exact integer-valued fp16
+// ((w ^ 8) & 0xF | 0x6400 = 1024 + code + 8, one LOP3 per two weights) and go straight into
+// m16n8k16 warp MMAs whose B operand is the activation vector; the group scale and the constant
+// bias (1032 * sum x etc.) are applied once per 128-wide group in float32.  On B200 the
+// HBM-to-issue-rate ratio leaves < 3 instructions per 4-bit weight, which rules out per-weight FMA
+// on the CUDA cores; the warp MMA does the multiply-add and the CUDA cores only unpack.
 #include "../../include/umaq_b200.h"
 #include "common.cuh"
 #include "decode.cuh"
 
-#include <mutex>
-
 #include <algorithm>
+#include <mutex>
 
 namespace umaq {
 namespace {
 
-constexpr int kGroupWarps = 8;                  // warps that split the K blocks of one stage
-constexpr int kConsumerWarps = 16;              // two groups: consecutive tiles go to alternate groups
-constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = kConsumers + 32;       // + one producer warp
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
 constexpr int kMaxSlots = 9;                    // top-k <= 8 routed + 1 shared
-constexpr int kScaleArea = 1152;                // bytes of scale staging per ring stage
-constexpr int kMaxRing = 16;                    // ring stages
-constexpr int kMaxList = 128;                   // stages one CTA may have to process
-constexpr int kRedTiles = 24;                   // tiles parked before a cross-warp reduction
-constexpr int kMaxUnitsX = 32;                  // hidden size <= 32 * 128
-constexpr int kMaxUnitsB = 96;                  // sum of intermediate sizes <= 96 * 128
 
-struct Slot {
-  const uint8_t* gate;
-  const uint8_t* up;
-  const uint8_t* down;
-  const float* gate_s;
-  const float* up_s;
-  const float* down_s;
-  float weight;
-  int expert;         // sort key (shared expert: INT_MAX)
-  int bad;            // expert index out of range
-};
-
-// One ring stage: 16 tile rows x nkb 64-byte blocks.
-//  kind 0: features [r0, r0+nr) of a slot: gate rows in tile rows 0..7, up rows in 8..15 (nr <= 8)
-//  kind 1: output rows [r0, r0+nr) of a slot's down projection (nr <= 16)
-struct alignas(16) Stage {
-  int flags;     // bit0 kind, bit1 last slice of its tile, bit2 owned by one warp pair, bit3 warp group,
-                 // bits 4-7 slot position (phase A: slot; phase B: index into order[]), bits 8-12 nr,
-                 // bits 16-19 owner pair (warps 2*owner and 2*owner+1)
-  int r0;
-  int kb0;       // first 64-byte block of the row covered by this stage
-  int nkb;       // blocks covered
-  __device__ int kind() const { return flags & 1; }
-  __device__ int last() const { return (flags >> 1) & 1; }
-  __device__ int owned() const { return (flags >> 2) & 1; }
-  __device__ int group() const { return (flags >> 3) & 1; }
-  __device__ int pos() const { return (flags >> 4) & 15; }
-  __device__ int nr() const { return (flags >> 8) & 31; }
-  __device__ int owner() const { return (flags >> 16) & 15; }
-};
-
-struct Shared {
-  Slot slots[kMaxSlots];
-  int order[kMaxSlots];        // phase-B slot order: ascending expert, shared last
-  int nlist;                   // stages in list[]
-  int first_b;                 // index of the first phase-B stage (== nlist if none)
-  int abort_flag;
-  float scale_x_inv;           // undoes the power-of-two prescale of x
-  float scaleB;                // prescale of the quantised slots' intermediate vectors, and its inverse
-  float scaleB_inv;
-  float contrib[kMaxSlots][16];
-  float sig_gate;              // bf16(sigmoid(bf16(x . wg)))
-  float wred[kConsumerWarps];
-  float wred2[kConsumerWarps];
-  unsigned long long bar_target;   // grid barrier: counter value that releases this launch
-  unsigned amaxB;              // max |intermediate| over the quantised slots (float bits)
-  float red[kRedTiles][kGroupWarps][16];      // parked partial sums: [tile][warp of the group][tile row]
-  Stage tdesc[kRedTiles];
-  Stage list[kMaxList];
-  uint64_t full[kMaxRing];
-  uint64_t empty[kMaxRing];
-};
-
-// ---- per-slot shape: depends on the launch parameters only, not on the routes --------------------
-struct Shape {
-  int H, top_k, enc, inter, shared_inter, nslots, max_kb;
-  __device__ int enc_of(int slot) const { return slot < top_k ? enc : ENC_BF16; }
-  __device__ int inter_of(int slot) const { return slot < top_k ? inter : shared_inter; }
-  __device__ int inter_off(int slot) const { return slot < top_k ? slot * inter : top_k * inter; }
-  __device__ int bias_off(int slot) const { return slot * ((row_bytes(enc, inter) >> 6) + 1); }
-  __device__ int kbA(int slot) const { return row_bytes(enc_of(slot), H) >> 6; }               // blocks per gate/up row
-  __device__ int kbB(int slot) const { return row_bytes(enc_of(slot), inter_of(slot)) >> 6; }  // per down row
-  __device__ int slices(int kb) const { return (kb + max_kb - 1) / max_kb; }
-};
-
-// Builds the CTA's stage list, one lane per stage.  Phase A: the CTA's byte-balanced range of
-// (slot, feature) pairs in tiles of 8 features; phase B: its range of output rows in groups of 16,
-// every slot (in order[] position; position s has slot s's shape since the shared expert is last
-// in both) per group.
-__device__ void build_stage_list(Shared& sh, const Shape& S, int G, int cta, int lane) {
-  const unsigned long long costR = 2ull * row_bytes(S.enc, S.H), costS = 4ull * S.H;
-  const unsigned long long bytesR = costR * S.inter * S.top_k;
-  const unsigned long long total = bytesR + (S.nslots > S.top_k ? costS * S.shared_inter : 0ull);
-  auto locate = [&](unsigned long long pos, int& si, int& fi) {
-    if (pos >= total) { si = S.nslots; fi = 0; return; }
-    if (pos < bytesR) {
-      const unsigned long long f = pos / costR;
-      si = (int)(f / S.inter); fi = (int)(f % S.inter);
-    } else { si = S.top_k; fi = (int)((pos - bytesR) / costS); }
-  };
-  int s0, f0, s1, f1;
-  locate(total * (unsigned long long)cta / G, s0, f0);
-  locate(total * (unsigned long long)(cta + 1) / G, s1, f1);
-  int startA[kMaxSlots];       // first stage index of each slot's segment
-  int totalA = 0;
-#pragma unroll
-  for (int s = 0; s < kMaxSlots; ++s) {
-    int n = 0;
-    if (s < S.nslots && s >= s0 && s <= s1) {
-      const int lo = s == s0 ? f0 : 0, hi = s == s1 ? f1 : S.inter_of(s);
-      if (hi > lo) n = ((hi - lo + 7) >> 3) * S.slices(S.kbA(s));
-    }
-    startA[s] = totalA;
-    totalA += n;
-  }
-  const int n0 = (int)((long long)S.H * cta / G), n1 = (int)((long long)S.H * (cta + 1) / G);
-  const int groups = (n1 - n0 + 15) >> 4;
-  int startB[kMaxSlots];
-  int perGroup = 0;
-#pragma unroll
-  for (int s = 0; s < kMaxSlots; ++s) {
-    startB[s] = perGroup;
-    if (s < S.nslots) perGroup += S.slices(S.kbB(s));
-  }
-  const int total_stages = totalA + groups * perGroup;
-  if (lane == 0) {
-    sh.nlist = total_stages;
-    sh.first_b = totalA;
-  }
-  for (int j = lane; j < total_stages && j < kMaxList; j += 32) {
-    Stage st;
-    if (j < totalA) {
-      int s = 0, base = 0;
-#pragma unroll
-      for (int t = 1; t < kMaxSlots; ++t)
-        if (j >= startA[t]) { s = t; base = startA[t]; }
-      const int rem = j - base;
-      const int nsl = S.slices(S.kbA(s));
-      const int tile = rem / nsl, slice = rem - tile * nsl;
-      const int lo = s == s0 ? f0 : 0, hi = s == s1 ? f1 : S.inter_of(s);
-      const int r0 = lo + tile * 8;
-      const int nr = min(8, hi - r0);
-      st.kb0 = slice * S.max_kb;
-      st.nkb = min(S.max_kb, S.kbA(s) - st.kb0);
-      const int tile_id = (base / nsl) + tile + s;      // any numbering that alternates along the list
-      st.flags = 0 | ((slice == nsl - 1) << 1) | ((tile_id & 1) << 3) | (s << 4) | (nr << 8);
-      st.r0 = r0;
-    } else {
-      const int jb = j - totalA;
-      const int g = jb / perGroup, rem = jb - g * perGroup;
-      int pos = 0, base = 0;
-#pragma unroll
-      for (int t = 1; t < kMaxSlots; ++t)
-        if (t < S.nslots && rem >= startB[t]) { pos = t; base = startB[t]; }
-      const int slice = rem - base;
-      const int nsl = S.slices(S.kbB(pos));
-      const int r0 = n0 + g * 16;
-      const int nr = min(16, n1 - r0);
-      st.kb0 = slice * S.max_kb;
-      st.nkb = min(S.max_kb, S.kbB(pos) - st.kb0);
-      // an unsliced tile is computed by one warp on its own (all slots of a group in parallel)
-      const int own = nsl == 1;
-      st.flags = 1 | ((slice == nsl - 1) << 1) | (own << 2) | (((g + pos) & 1) << 3) | (pos << 4) | (nr << 8) |
-                 ((pos & 7) << 16);
-      st.r0 = r0;
-    }
-    sh.list[j] = st;
-  }
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
 }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// ---- producer ------------------------------------------------------------------------------------
-__device__ __forceinline__ void scale_span(int r0, int nr, int K, int& first_byte, int& bytes) {
-  // contiguous rows [r0, r0+nr) x (K/128) floats, widened to 16-byte boundaries
-  const int gk4 = (K >> 7) * 4;
-  const int b0 = r0 * gk4, b1 = (r0 + nr) * gk4;
-  first_byte = b0 & ~15;
-  bytes = ((b1 + 15) & ~15) - first_byte;
-}
-
-__device__ void issue_stage(const Shared& sh, const Shape& S, const Stage& st, uint8_t* buf, uint64_t* bar, int lane) {
-  const int kind = st.kind();
-  const int slot = kind ? sh.order[st.pos()] : st.pos();
-  const Slot& sl = sh.slots[slot];
-  const int enc = S.enc_of(slot);
-  const int K = kind == 0 ? S.H : S.inter_of(slot);
-  const int rb = row_bytes(enc, K);
-  const int sb = st.nkb << 6;
-  const int nr = st.nr();
-  const bool whole = (sb == rb);
-  const bool has_scales = enc != ENC_BF16 && st.kb0 == 0;
-  const int gk4 = (K >> 7) * 4;
-  uint32_t tx;
-  int fb = 0, nb = 0;
-  if (kind == 0) {
-    tx = 2u * nr * sb + (has_scales ? 2u * nr * gk4 : 0u);
-  } else {
-    scale_span(st.r0, nr, K, fb, nb);
-    tx = (uint32_t)nr * sb + (has_scales ? (uint32_t)nb : 0u);
-  }
-  if (lane == 0) mbar_expect_tx(bar, tx);
-  __syncwarp();
-  uint8_t* sc = buf + 16 * sb;   // scale staging follows the 16 row slots
-  const size_t base = (size_t)st.r0 * rb + ((size_t)st.kb0 << 6);
-  if (kind == 0) {
-    if (whole) {
-      if (lane == 0) bulk_g2s(buf, sl.gate + base, (uint32_t)nr * rb, bar);
-      if (lane == 1) bulk_g2s(buf + 8 * sb, sl.up + base, (uint32_t)nr * rb, bar);
-    } else if (lane < 16) {
-      const int i = lane & 7;
-      if (i < nr) bulk_g2s(buf + (lane < 8 ? i : 8 + i) * sb, (lane < 8 ? sl.gate : sl.up) + base + (size_t)i * rb,
-                           (uint32_t)sb, bar);
-    }
-    if (has_scales) {
-      if (lane == 2) bulk_g2s(sc, sl.gate_s + (size_t)st.r0 * (K >> 7), (uint32_t)nr * gk4, bar);
-      if (lane == 3) bulk_g2s(sc + 8 * gk4, sl.up_s + (size_t)st.r0 * (K >> 7), (uint32_t)nr * gk4, bar);
-    }
-  } else {
-    if (whole) {
-      if (lane == 0) bulk_g2s(buf, sl.down + base, (uint32_t)nr * rb, bar);
-    } else if (lane < nr) {
-      bulk_g2s(buf + lane * sb, sl.down + base + (size_t)lane * rb, (uint32_t)sb, bar);
-    }
-    if (has_scales && lane == 16) bulk_g2s(sc, reinterpret_cast<const uint8_t*>(sl.down_s) + fb, (uint32_t)nb, bar);
-  }
-}
-
-// ---- block processors: 16 tile rows x 64-byte blocks of each row ---------------------------------
-// lane = 4*q + c supplies tile rows q and q+8; the raw dot products come back in element 0 (row q)
-// and element 2 (row q+8) of the accumulators -- every MMA column carries the same activation
-// vector.  Each block feeds two independent accumulator chains so that consecutive warp MMAs do
-// not wait on each other.
-
-// Q4: a[] / b[] = 16 bytes (32 codes) of rows q / q+8, x[] = 64 bytes of fragments (8 MMAs).
+// ---- block arithmetic: 16 tile rows x one 64-byte block of each row ---------------------------------
+// lane = 4*q + c supplies tile rows q and q+8.  Every block runs two accumulator chains; d[] returns
+// the four accumulator elements of the lane summed over the chains: d[0], d[1] = row q, MMA columns
+// 2c, 2c+1; d[2], d[3] = row q+8.
 #define UMAQ_Q4_LO(w) lop3<0x6A>((w), 0x000F000Fu, 0x64086408u)   /* fp16 1024 + (code + 8)      */
 #define UMAQ_Q4_HI(w) lop3<0x6A>((w), 0x00F000F0u, 0x64806480u)   /* fp16 1024 + 16 * (code + 8) */
-__device__ __forceinline__ void mma_block_q4(const uint32_t (&a)[4], const uint32_t (&b)[4], const uint4 (&x)[4],
-                                             float (&d0)[4], float (&d1)[4]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t ah = a[j] >> 8, bh = b[j] >> 8;
-    mma_f16_16816(d0, UMAQ_Q4_LO(a[j]), UMAQ_Q4_LO(b[j]), UMAQ_Q4_HI(a[j]), UMAQ_Q4_HI(b[j]), x[j].x, x[j].y);
-    mma_f16_16816(d1, UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x[j].z, x[j].w);
-  }
-}
 
-// Two Q4 blocks at once, sixteen MMAs over eight accumulator chains issued round-robin, so that
-// no MMA has to wait for the one before it; sums come back in s0 (first block) and s1 (second).
-__device__ __forceinline__ void mma_pair_q4(const uint32_t (&a0)[4], const uint32_t (&b0)[4], const uint4 (&x0)[4],
-                                            const uint32_t (&a1)[4], const uint32_t (&b1)[4], const uint4 (&x1)[4],
-                                            float (&s0)[2], float (&s1)[2]) {
-  float d[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) d[i][0] = d[i][1] = d[i][2] = d[i][3] = 0.f;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int ch = (j & 1) * 4;
-    const uint32_t ah = a0[j] >> 8, bh = b0[j] >> 8, ch1 = a1[j] >> 8, dh = b1[j] >> 8;
-    mma_f16_16816(d[ch + 0], UMAQ_Q4_LO(a0[j]), UMAQ_Q4_LO(b0[j]), UMAQ_Q4_HI(a0[j]), UMAQ_Q4_HI(b0[j]), x0[j].x, x0[j].y);
-    mma_f16_16816(d[ch + 1], UMAQ_Q4_LO(a1[j]), UMAQ_Q4_LO(b1[j]), UMAQ_Q4_HI(a1[j]), UMAQ_Q4_HI(b1[j]), x1[j].x, x1[j].y);
-    mma_f16_16816(d[ch + 2], UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x0[j].z, x0[j].w);
-    mma_f16_16816(d[ch + 3], UMAQ_Q4_LO(ch1), UMAQ_Q4_LO(dh), UMAQ_Q4_HI(ch1), UMAQ_Q4_HI(dh), x1[j].z, x1[j].w);
-  }
-  s0[0] = (d[0][0] + d[2][0]) + (d[4][0] + d[6][0]);
-  s0[1] = (d[0][2] + d[2][2]) + (d[4][2] + d[6][2]);
-  s1[0] = (d[1][0] + d[3][0]) + (d[5][0] + d[7][0]);
-  s1[1] = (d[1][2] + d[3][2]) + (d[5][2] + d[7][2]);
-}
-
-// Q8: 16 codes of rows q / q+8, x[] = 32 bytes of fragments (4 MMAs).
-__device__ __forceinline__ void mma_block_q8(const uint32_t (&a)[4], const uint32_t (&b)[4], const uint4 (&x)[2],
-                                             float (&d0)[4], float (&d1)[4]) {
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const uint32_t a0 = a[2 * j] ^ 0x80808080u, a1 = a[2 * j + 1] ^ 0x80808080u;
-    const uint32_t b0 = b[2 * j] ^ 0x80808080u, b1 = b[2 * j + 1] ^ 0x80808080u;
-    // byte | 0x6400 -> fp16 1024 + (code + 128)
-    mma_f16_16816(d0, prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
-                  prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x[j].x, x[j].y);
-    mma_f16_16816(d1, prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
-                  prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x[j].z, x[j].w);
-  }
-}
-
-__device__ __forceinline__ void mma_block_bf16(const uint32_t (&a)[4], const uint32_t (&b)[4], const uint4& x,
-                                               float (&d0)[4], float (&d1)[4]) {
-  mma_bf16_16816(d0, a[0], b[0], a[1], b[1], x.x, x.y);
-  mma_bf16_16816(d1, a[2], b[2], a[3], b[3], x.z, x.w);
-}
-
-__device__ __forceinline__ void lds16(const uint8_t* p, uint32_t (&r)[4]) {
-  const uint4 v = *reinterpret_cast<const uint4*>(p);
-  r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
-}
-
-// What one warp needs to know about a stage to process blocks of it.
-struct StageView {
-  const uint8_t* buf;   // 16 row slots of `sb` bytes
-  int sb;
-  int nkb, kb0;
-  int enc;
-  const uint8_t* xf;    // fragments of the activation vector, block 0 of the row
-  const float* bias;    // bias sums per block (Q4 / Q8)
-  const float* sc;      // staged scales
-  int sc_lo, sc_hi;     // element offsets of rows q / q+8 (group 0)
-};
-
-// One block (local index blk); fragments, bias and scales come from shared memory and are fetched
-// before the MMA chain starts.
-__device__ __forceinline__ void block_from_smem(const StageView& v, int blk, int q, int c, float& acc_lo, float& acc_hi) {
-  uint32_t a[4], b[4];
-  lds16(v.buf + q * v.sb + (blk << 6) + (c << 4), a);
-  lds16(v.buf + (q + 8) * v.sb + (blk << 6) + (c << 4), b);
-  const int kb = v.kb0 + blk;
+__device__ __forceinline__ void mma_block(int enc, const uint4& ra, const uint4& rb, const uint8_t* xf_lane, bool xvalid,
+                                          float (&d)[4]) {
   float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-  if (v.enc == ENC_Q4) {
-    const uint4* xp = reinterpret_cast<const uint4*>(v.xf + ((size_t)kb << 8) + (c << 6));
-    const uint4 x[4] = {xp[0], xp[1], xp[2], xp[3]};
-    const float bs = v.bias[kb], s_lo = v.sc[v.sc_lo + kb], s_hi = v.sc[v.sc_hi + kb];
-    mma_block_q4(a, b, x, d0, d1);
-    acc_lo = fmaf(s_lo, d0[0] + d1[0] - bs, acc_lo);
-    acc_hi = fmaf(s_hi, d0[2] + d1[2] - bs, acc_hi);
-  } else if (v.enc == ENC_Q8) {
-    const uint4* xp = reinterpret_cast<const uint4*>(v.xf + ((size_t)kb << 7) + (c << 5));
-    const uint4 x[2] = {xp[0], xp[1]};
-    const float bs = v.bias[kb], s_lo = v.sc[v.sc_lo + (kb >> 1)], s_hi = v.sc[v.sc_hi + (kb >> 1)];
-    mma_block_q8(a, b, x, d0, d1);
-    acc_lo = fmaf(s_lo, d0[0] + d1[0] - bs, acc_lo);
-    acc_hi = fmaf(s_hi, d0[2] + d1[2] - bs, acc_hi);
-  } else {
-    const uint4 x = *reinterpret_cast<const uint4*>(v.xf + ((size_t)kb << 6) + (c << 4));
-    mma_block_bf16(a, b, x, d0, d1);
-    acc_lo += d0[0] + d1[0];
-    acc_hi += d0[2] + d1[2];
-  }
-}
-
-// Two adjacent blocks (pb, pb+1).  With row strides that are a multiple of 128 bytes, rows q and q+1
-// of a quarter-warp hit the same banks; odd rows therefore read the pair in the opposite order,
-// which makes both 16-byte loads conflict-free.  XREG: the Q4 fragments of the pair are passed in
-// registers (they do not change while a warp keeps the same pair of a 2048-wide row).
-template <bool XREG>
-__device__ __forceinline__ void pair_from_smem(const StageView& v, int pb, int q, int c, const uint4 (&xr)[8],
-                                               float& acc_lo, float& acc_hi) {
-  const bool swap = ((v.sb >> 6) & 1) == 0 && (q & 1);
-  const int first = swap ? pb + 1 : pb, second = swap ? pb : pb + 1;
-  uint32_t r1a[4], r1b[4], r2a[4], r2b[4];
-  lds16(v.buf + q * v.sb + (first << 6) + (c << 4), r1a);
-  lds16(v.buf + (q + 8) * v.sb + (first << 6) + (c << 4), r1b);
-  lds16(v.buf + q * v.sb + (second << 6) + (c << 4), r2a);
-  lds16(v.buf + (q + 8) * v.sb + (second << 6) + (c << 4), r2b);
-  const int kb = v.kb0 + pb;
-  float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-  float e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
-  uint32_t a0[4], b0[4], a1[4], b1[4];
+  const uint32_t a[4] = {ra.x, ra.y, ra.z, ra.w}, b[4] = {rb.x, rb.y, rb.z, rb.w};
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  if (enc == ENC_Q4) {
+    const uint4* xp = reinterpret_cast<const uint4*>(xf_lane);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    a0[i] = swap ? r2a[i] : r1a[i]; b0[i] = swap ? r2b[i] : r1b[i];
-    a1[i] = swap ? r1a[i] : r2a[i]; b1[i] = swap ? r1b[i] : r2b[i];
-  }
-  if (XREG || v.enc == ENC_Q4) {
-    const float bs0 = v.bias[kb], bs1 = v.bias[kb + 1];
-    const float sl0 = v.sc[v.sc_lo + kb], sh0 = v.sc[v.sc_hi + kb];
-    const float sl1 = v.sc[v.sc_lo + kb + 1], sh1 = v.sc[v.sc_hi + kb + 1];
-    float s0[2], s1[2];
-    if (XREG) {
-      const uint4 x0[4] = {xr[0], xr[1], xr[2], xr[3]};
-      const uint4 x1[4] = {xr[4], xr[5], xr[6], xr[7]};
-      mma_pair_q4(a0, b0, x0, a1, b1, x1, s0, s1);
-    } else {
-      const uint4* xp = reinterpret_cast<const uint4*>(v.xf + ((size_t)kb << 8) + (c << 6));
-      const uint4 x0[4] = {xp[0], xp[1], xp[2], xp[3]};
-      const uint4 x1[4] = {xp[16], xp[17], xp[18], xp[19]};
-      mma_pair_q4(a0, b0, x0, a1, b1, x1, s0, s1);
+    for (int j = 0; j < 4; ++j) {
+      const uint4 x = xvalid ? xp[j] : zero;
+      const uint32_t ah = a[j] >> 8, bh = b[j] >> 8;
+      mma_f16_16816(d0, UMAQ_Q4_LO(a[j]), UMAQ_Q4_LO(b[j]), UMAQ_Q4_HI(a[j]), UMAQ_Q4_HI(b[j]), x.x, x.y);
+      mma_f16_16816(d1, UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x.z, x.w);
     }
-    acc_lo = fmaf(sl0, s0[0] - bs0, acc_lo);
-    acc_hi = fmaf(sh0, s0[1] - bs0, acc_hi);
-    acc_lo = fmaf(sl1, s1[0] - bs1, acc_lo);
-    acc_hi = fmaf(sh1, s1[1] - bs1, acc_hi);
-  } else if (v.enc == ENC_Q8) {
-    const float bs0 = v.bias[kb], bs1 = v.bias[kb + 1];
-    const float sl0 = v.sc[v.sc_lo + (kb >> 1)], sh0 = v.sc[v.sc_hi + (kb >> 1)];   // kb is even: one group
-    const uint4* xp = reinterpret_cast<const uint4*>(v.xf + ((size_t)kb << 7) + (c << 5));
-    const uint4 x0[2] = {xp[0], xp[1]};
-    const uint4 x1[2] = {xp[8], xp[9]};
-    mma_block_q8(a0, b0, x0, d0, d1);
-    mma_block_q8(a1, b1, x1, e0, e1);
-    acc_lo = fmaf(sl0, (d0[0] + d1[0] - bs0) + (e0[0] + e1[0] - bs1), acc_lo);
-    acc_hi = fmaf(sh0, (d0[2] + d1[2] - bs0) + (e0[2] + e1[2] - bs1), acc_hi);
+  } else if (enc == ENC_Q8) {
+    const uint4* xp = reinterpret_cast<const uint4*>(xf_lane);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint4 x = xvalid ? xp[j] : zero;
+      const uint32_t a0 = a[2 * j] ^ 0x80808080u, a1 = a[2 * j + 1] ^ 0x80808080u;
+      const uint32_t b0 = b[2 * j] ^ 0x80808080u, b1 = b[2 * j + 1] ^ 0x80808080u;
+      // byte | 0x6400 -> fp16 1024 + (code + 128)
+      mma_f16_16816(d0, prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
+                    prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x.x, x.y);
+      mma_f16_16816(d1, prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
+                    prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x.z, x.w);
+    }
   } else {
-    const uint4* xp = reinterpret_cast<const uint4*>(v.xf + ((size_t)kb << 6) + (c << 4));
-    mma_block_bf16(a0, b0, xp[0], d0, d1);
-    mma_block_bf16(a1, b1, xp[4], e0, e1);
-    acc_lo += (d0[0] + d1[0]) + (e0[0] + e1[0]);
-    acc_hi += (d0[2] + d1[2]) + (e0[2] + e1[2]);
+    const uint4 x = xvalid ? *reinterpret_cast<const uint4*>(xf_lane) : zero;
+    mma_bf16_16816(d0, a[0], b[0], a[1], b[1], x.x, x.y);
+    mma_bf16_16816(d1, a[2], b[2], a[3], b[3], x.z, x.w);
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) d[i] = d0[i] + d1[i];
 }
 
-// ---- activation fragments --------------------------------------------------------------------
+// bytes of activation fragments per 64-byte weight block: Q4 128 k, Q8 64 k, BF16 32 k, 2 bytes each
+__device__ __forceinline__ int frag_block_bytes(int enc) { return enc == ENC_Q4 ? 256 : (enc == ENC_Q8 ? 128 : 64); }
+
+// ---- activation fragments in shared memory -------------------------------------------------------------
 // fp16 fragments for Q4 rows: each run of 8 activations k0..k7 is stored as
 // [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16] (the nibble pairs one LOP3 extracts and the 1/16 that
-// undoes the in-place high nibble).  Q8 and BF16 rows use natural order.
-//
-// store_unit() stores the fragments of one 128-activation unit (lane owns k = 128*unit + 4*lane +
-// 0..3, values already multiplied by the prescale) and, for Q4/Q8, the bias sums of its 64-byte
-// weight blocks: sum of 1032*x (even k) + 72*x (odd k) for Q4, 1152*x for Q8, taken from the
-// rounded fp16 values.
-__device__ __forceinline__ void store_unit(int enc, uint8_t* xf, int unit, const float (&v)[4], int lane) {
-  const int k0 = unit * 128 + lane * 4;
+// undoes the in-place high nibble).  Q8 and BF16 rows use natural order.  v[] = four consecutive
+// activations starting at k0 (a multiple of 4), already multiplied by the prescale.
+__device__ __forceinline__ void store_frag4(int enc, uint8_t* xf, int k0, const float (&v)[4]) {
   if (enc == ENC_Q4) {
-    // the lane's activations k0..k0+3 are elements 0..3 (even lane) or 4..7 (odd lane) of an 8-run:
-    // run positions 0,2,4,6 resp. 1,3,5,7
-    __half* o = reinterpret_cast<__half*>(xf) + (k0 & ~7) + (lane & 1);
+    __half* o = reinterpret_cast<__half*>(xf) + (k0 & ~7) + ((k0 >> 2) & 1);
     o[0] = __float2half_rn(v[0]); o[2] = __float2half_rn(v[1] * 0.0625f);
     o[4] = __float2half_rn(v[2]); o[6] = __float2half_rn(v[3] * 0.0625f);
     return;
@@ -459,10 +122,11 @@ __device__ __forceinline__ void store_unit(int enc, uint8_t* xf, int unit, const
 
 // Bias sums of the 64-byte weight blocks of an n-activation fragment vector, read back from shared
 // memory: every thread sums 32 stored halves with their coefficients, 4 (Q4) or 2 (Q8) neighbouring
-// lanes combine.  Q4: run positions 0,1,4,5 hold x (coefficient 1032), 2,3,6,7 hold x/16 (72 * 16).
+// lanes combine.  Q4: run positions 0,1,4,5 hold x (coefficient 1032), 2,3,6,7 hold x/16 (72 * 16);
+// Q8: every position holds x (1152).
 __device__ __forceinline__ void build_bias(int enc, const uint8_t* xf, float* bias, int n, int tid) {
   const int chunks = n >> 5;
-  for (int ch = tid; ch < ((chunks + 31) & ~31); ch += kConsumers) {
+  for (int ch = tid; ch < ((chunks + 31) & ~31); ch += kThreads) {
     float sum = 0.f;
     if (ch < chunks) {
       const uint4* src = reinterpret_cast<const uint4*>(xf + (size_t)ch * 64);
@@ -495,401 +159,515 @@ __device__ __forceinline__ float prescale_for(float amax) {
   return __uint_as_float((unsigned)(267 - eb) << 23);        // 2^(14 - (eb - 126))
 }
 
-__global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const DecodeParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  Shared& sh = *reinterpret_cast<Shared*>(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int H = p.hidden;
-  const int G = gridDim.x;
-  Shape S;
-  S.H = H; S.top_k = p.top_k; S.enc = p.enc; S.inter = p.inter; S.shared_inter = p.shared_inter;
-  S.nslots = p.top_k + (p.sh_gate ? 1 : 0);
-  S.max_kb = p.stage_bytes >> 10;          // a stage holds 16 rows x (max_kb * 64) bytes
-
-  // ---- carve shared memory (same arithmetic as decode_smem_layout() on the host) --------------
-  uint8_t* cur = smem_raw + ((sizeof(Shared) + 127) & ~127);
-  uint8_t* xfA = cur;                 cur += H * 2;           // routed-encoding fragments of x
-  uint8_t* xfA_bf = cur;              cur += H * 2;           // bf16 x (shared expert / bf16 layers)
-  float* biasA = reinterpret_cast<float*>(cur); cur += (H >> 6) * 4;
-  uint8_t* xfB = cur;                 cur += p.inter_total * 2;
-  float* biasB = reinterpret_cast<float*>(cur); cur += ((p.inter_total >> 6) + kMaxSlots) * 4;
-  uint8_t* ring = smem_raw + (((cur - smem_raw) + 1023) & ~1023);
-  const int stage_bytes = p.stage_bytes + kScaleArea;
-  const int nstages = p.nstages;
-  volatile int* abort_flag = &sh.abort_flag;
-  // CTA 0 leaves cycle stamps of its phases in the diagnostic area of the workspace
-  long long* stamps = (blockIdx.x == 0 && tid == 0) ? reinterpret_cast<long long*>(p.sync) + 24 : nullptr;
-  const long long t_start = clock64();
-#define UMAQ_STAMP(i) do { if (stamps) stamps[i] = clock64() - t_start; } while (0)
-
-  // The activation vector is needed first and is a cold read: every consumer warp fetches its
-  // 128-activation units before anything else so the latency overlaps the set-up.
-  constexpr int kMaxUX = kMaxUnitsX / kConsumerWarps;
-  float xv[kMaxUX][4];
-  float gdot = 0.f;
+// max over the CTA; `red` has kWarps floats
+__device__ __forceinline__ float block_max(float v, float* red, int tid) {
 #pragma unroll
-  for (int j = 0; j < kMaxUX; ++j) {
-    const int u = warp + j * kConsumerWarps;
-    xv[j][0] = xv[j][1] = xv[j][2] = xv[j][3] = 0.f;
-    if (warp < kConsumerWarps && u * 128 < H) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(p.x + u * 128 + lane * 4);
-      xv[j][0] = __uint_as_float(raw.x << 16); xv[j][1] = __uint_as_float(raw.x & 0xffff0000u);
-      xv[j][2] = __uint_as_float(raw.y << 16); xv[j][3] = __uint_as_float(raw.y & 0xffff0000u);
-      if (p.sh_gatevec) {
-        const uint2 g = *reinterpret_cast<const uint2*>(p.sh_gatevec + u * 128 + lane * 4);
-        gdot += xv[j][0] * __uint_as_float(g.x << 16) + xv[j][1] * __uint_as_float(g.x & 0xffff0000u) +
-                xv[j][2] * __uint_as_float(g.y << 16) + xv[j][3] * __uint_as_float(g.y & 0xffff0000u);
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int i = 1; i < kWarps; ++i) m = fmaxf(m, red[i]);
+  __syncthreads();
+  return m;
+}
+
+__device__ __forceinline__ long long load_index(const void* idx, int idx64, int i) {
+  return idx64 ? reinterpret_cast<const long long*>(idx)[i] : (long long)reinterpret_cast<const int*>(idx)[i];
+}
+
+// Four blocks at once: eight accumulator chains issued round-robin, so no MMA waits for the one
+// before it (a dependent warp MMA on this architecture takes ~130 cycles to issue).  n = valid blocks;
+// d[i] as in mma_block().
+// XG: the fragments are in global memory and were written by the preceding kernel of the chain:
+// they are read through L2 (ld.global.cg), never through a cache that may predate that kernel.
+template <bool XG>
+__device__ __forceinline__ uint4 load_frag(const uint8_t* p) {
+  return XG ? __ldcg(reinterpret_cast<const uint4*>(p)) : *reinterpret_cast<const uint4*>(p);
+}
+template <bool XG>
+__device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4], const uint4 (&rb)[4],
+                                            const uint8_t* const (&xf_lane)[4], bool xvalid, float (&d)[4][4]) {
+  float d0[4][4], d1[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d0[i][e] = d1[i][e] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  if (enc == ENC_Q4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (i < n) {
+          const uint4 x = xvalid ? load_frag<XG>(xf_lane[i] + 16 * j) : zero;
+          const uint32_t a = j == 0 ? ra[i].x : j == 1 ? ra[i].y : j == 2 ? ra[i].z : ra[i].w;
+          const uint32_t b = j == 0 ? rb[i].x : j == 1 ? rb[i].y : j == 2 ? rb[i].z : rb[i].w;
+          const uint32_t ah = a >> 8, bh = b >> 8;
+          mma_f16_16816(d0[i], UMAQ_Q4_LO(a), UMAQ_Q4_LO(b), UMAQ_Q4_HI(a), UMAQ_Q4_HI(b), x.x, x.y);
+          mma_f16_16816(d1[i], UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x.z, x.w);
+        }
+      }
+    }
+  } else if (enc == ENC_Q8) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (i < n) {
+          const uint4 x = xvalid ? load_frag<XG>(xf_lane[i] + 16 * j) : zero;
+          const uint32_t a0 = (j == 0 ? ra[i].x : ra[i].z) ^ 0x80808080u, a1 = (j == 0 ? ra[i].y : ra[i].w) ^ 0x80808080u;
+          const uint32_t b0 = (j == 0 ? rb[i].x : rb[i].z) ^ 0x80808080u, b1 = (j == 0 ? rb[i].y : rb[i].w) ^ 0x80808080u;
+          mma_f16_16816(d0[i], prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
+                        prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x.x, x.y);
+          mma_f16_16816(d1[i], prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
+                        prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x.z, x.w);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i < n) {
+        const uint4 x = xvalid ? load_frag<XG>(xf_lane[i]) : zero;
+        mma_bf16_16816(d0[i], ra[i].x, rb[i].x, ra[i].y, rb[i].y, x.x, x.y);
+        mma_bf16_16816(d1[i], ra[i].z, rb[i].z, ra[i].w, rb[i].w, x.z, x.w);
       }
     }
   }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d[i][e] = d0[i][e] + d1[i][e];
+}
 
-  // ---- set-up: routes (one round of global loads), stage list, barriers --------------------------
-  if (warp == 0) {
-    if (lane == 30) sh.abort_flag = 0;
-    if (lane < p.top_k) {
-      long long e = p.idx64 ? reinterpret_cast<const long long*>(p.idx)[lane]
-                            : (long long)reinterpret_cast<const int*>(p.idx)[lane];
-      const float wt = p.w[lane];
-      Slot& sl = sh.slots[lane];
-      sl.bad = (e < 0 || e >= p.experts);
-      if (sl.bad) e = 0;
-      const size_t wgu = (size_t)p.inter * row_bytes(p.enc, H), wd = (size_t)H * row_bytes(p.enc, p.inter);
-      sl.gate = p.gate + e * wgu; sl.up = p.up + e * wgu; sl.down = p.down + e * wd;
-      sl.gate_s = p.gate_s ? p.gate_s + e * (size_t)p.inter * (H >> 7) : nullptr;
-      sl.up_s = p.up_s ? p.up_s + e * (size_t)p.inter * (H >> 7) : nullptr;
-      sl.down_s = p.down_s ? p.down_s + e * (size_t)H * (p.inter >> 7) : nullptr;
-      sl.expert = (int)e; sl.weight = wt;
-    } else if (lane == p.top_k && p.sh_gate) {
-      Slot& sl = sh.slots[lane];
-      sl.gate = reinterpret_cast<const uint8_t*>(p.sh_gate); sl.up = reinterpret_cast<const uint8_t*>(p.sh_up);
-      sl.down = reinterpret_cast<const uint8_t*>(p.sh_down);
-      sl.gate_s = sl.up_s = sl.down_s = nullptr;
-      sl.expert = 0x7fffffff; sl.weight = 1.f; sl.bad = 0;
-    }
-    __syncwarp();
-    // phase-B order: ascending expert number, stable in slot order (rank by counting); shared last
-    if (lane < S.nslots) {
-      const int mine = sh.slots[lane].expert;
-      int rank = 0;
-      for (int j = 0; j < S.nslots; ++j) {
-        const int other = sh.slots[j].expert;
-        rank += (other < mine) || (other == mine && j < lane);
-      }
-      sh.order[rank] = lane;
-      if (sh.slots[lane].bad) {          // every CTA sees the same routes and takes the same exit
-        atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);
-        sh.abort_flag = 1;
-      }
-    }
-  } else if (warp == 1) {
-    build_stage_list(sh, S, G, blockIdx.x, lane);
-  } else if (warp == 2) {
-    if (lane < nstages) { mbar_init(&sh.full[lane], 1); mbar_init(&sh.empty[lane], kGroupWarps); }
-    __syncwarp();
-    if (lane == 0) fence_barrier_init();
-  } else if (warp == 3) {
-    // grid barrier: the counter only ever grows by G per launch; whatever has arrived already,
-    // this launch is released at the next multiple of G above the value seen now
-    if (lane == 0) {
-      const unsigned long long seen = ld_acquire_u64(reinterpret_cast<const unsigned long long*>(p.sync + 4));
-      sh.bar_target = (seen / G + 1) * G;
+// ---- fragment records in global memory ------------------------------------------------------------------
+// A vector of n activations that quantised rows will multiply is published once as: n fp16 fragments
+// (2n bytes), then the bias sums of its 64-byte weight blocks (n/64 floats, padded to a multiple of
+// four), then the inverse of its power-of-two prescale in a 16-byte slot.  Every part starts on a
+// 16-byte boundary.  BF16 rows read the BF16 vector itself.
+__host__ __device__ __forceinline__ int frag_body_bytes(int n) { return n * 2 + (((n >> 6) + 3) & ~3) * 4; }
+__host__ __device__ __forceinline__ size_t frag_record_bytes(int n) { return (size_t)frag_body_bytes(n) + 16; }
+
+// Publishes the record of `n` float values held as vals[j] = value at index tid*4 + j*kThreads*4 + 0..3
+// (a CTA-wide layout); all threads of the CTA call it.  `stage` is frag_body_bytes(n) bytes of shared memory.
+template <int MAXV>
+__device__ __forceinline__ void publish_record(int enc, int n, const float (&vals)[MAXV][4], uint8_t* stage,
+                                               float* red, uint8_t* dst, int tid) {
+  float am = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j)
+    if (tid * 4 + j * kThreads * 4 < n)
+      am = fmaxf(am, fmaxf(fmaxf(fabsf(vals[j][0]), fabsf(vals[j][1])), fmaxf(fabsf(vals[j][2]), fabsf(vals[j][3]))));
+  const float m = block_max(am < 3.0e38f ? am : 0.f, red, tid);
+  const float sc = prescale_for(m);
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int k0 = tid * 4 + j * kThreads * 4;
+    if (k0 < n) {
+      const float v[4] = {vals[j][0] * sc, vals[j][1] * sc, vals[j][2] * sc, vals[j][3] * sc};
+      store_frag4(enc, stage, k0, v);
     }
   }
   __syncthreads();
-  UMAQ_STAMP(0);
-  const int nlist = min(sh.nlist, kMaxList);
-  const int first_b = min(sh.first_b, nlist);
-  if (sh.nlist > kMaxList && tid == 0) { atomicExch(p.sync + 2, (unsigned)ERR_UNSUPPORTED); *abort_flag = 1; }
-
-  if (warp == kConsumerWarps) {
-    // ======================= producer warp ===================================================
-    int n = 0;
-    for (; n < nlist && !*abort_flag; ++n) {
-      const int s = n % nstages;
-      if (n >= nstages && !mbar_wait(&sh.empty[s], ((n / nstages) - 1) & 1)) {
-        if (lane == 0) { atomicExch(p.sync + 2, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; }
-        __syncwarp();
-        break;
-      }
-      if (*abort_flag) break;
-      issue_stage(sh, S, sh.list[n], ring + (size_t)s * stage_bytes, &sh.full[s], lane);
-    }
-    // After an abort the consumers skip their waits: drain what was issued so that no copy is
-    // still writing this CTA's shared memory when it retires.
-    if (*abort_flag) {
-      const int first = n > nstages ? n - nstages : 0;
-      for (int i = first; i < n; ++i) mbar_wait(&sh.full[i % nstages], (i / nstages) & 1);
-    }
-    return;
-  }
-
-  // ========================= consumer warps =====================================================
-  const int q = lane >> 2, c = lane & 3;
-  const int grp = warp >> 3, w8 = warp & 7;     // K-split group and position inside it
-
-  // x -> fragments (routed encoding: prescaled fp16; bf16 copy), sigmoid gate of the shared expert.
-  // Warp w owns the 128-activation units w, w+16, ... (loaded at kernel entry).
-  {
-    float am = 0.f;
-#pragma unroll
-    for (int j = 0; j < kMaxUX; ++j)
-      am = fmaxf(am, fmaxf(fmaxf(fabsf(xv[j][0]), fabsf(xv[j][1])), fmaxf(fabsf(xv[j][2]), fabsf(xv[j][3]))));
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-      gdot += __shfl_xor_sync(0xffffffffu, gdot, o);
-    }
-    if (lane == 0) { sh.wred[warp] = am; sh.wred2[warp] = gdot; }
-    named_bar_sync(1, kConsumers);
-    float m = 0.f, t = 0.f;
-#pragma unroll
-    for (int i = 0; i < kConsumerWarps; ++i) { m = fmaxf(m, sh.wred[i]); t += sh.wred2[i]; }
-    const float sx = prescale_for(m);
-    if (tid == 0) {
-      sh.scale_x_inv = 1.f / sx;
-      t = bf16_round(t);                                   // nn.Linear output in BF16
-      sh.sig_gate = bf16_round(1.f / (1.f + expf(-t)));    // sigmoid of a BF16 tensor
-    }
-#pragma unroll
-    for (int j = 0; j < kMaxUX; ++j) {
-      const int u = warp + j * kConsumerWarps;
-      if (u * 128 < H) {
-        store_unit(ENC_BF16, xfA_bf, u, xv[j], lane);
-        if (p.enc != ENC_BF16) {
-          const float sv[4] = {xv[j][0] * sx, xv[j][1] * sx, xv[j][2] * sx, xv[j][3] * sx};
-          store_unit(p.enc, xfA, u, sv, lane);
-        }
-      }
-    }
-    named_bar_sync(1, kConsumers);
-    if (p.enc != ENC_BF16) build_bias(p.enc, xfA, biasA, H, tid);
-    named_bar_sync(1, kConsumers);
-  }
-  UMAQ_STAMP(1);
-
-  // Q4 rows of 16 blocks: this warp's two blocks of x stay in registers during phase A.
-  const bool xreg = p.enc == ENC_Q4 && (H >> 7) == 16;
-  uint4 xr[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) xr[i] = make_uint4(0, 0, 0, 0);
-  if (xreg) {
-    const uint4* xp = reinterpret_cast<const uint4*>(xfA + ((size_t)(2 * w8) << 8) + (c << 6));
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { xr[i] = xp[i]; xr[4 + i] = xp[16 + i]; }
-  }
-
-  int pend = 0;                  // tiles whose partial sums sit in sh.red, not yet reduced
-  float acc_lo = 0.f, acc_hi = 0.f;
-
-  // Reduces the parked tiles and finishes them.  Phase A: sum of the eight K-slices, SwiGLU, float32
-  // intermediate.  Phase B: the ordered BF16 running sum over the slots of one 16-row group.
-  auto flush = [&]() {
-    named_bar_sync(1, kConsumers);
-    // `go` only guards work; the barriers below are reached by every thread whatever it reads
-    const bool go = !*abort_flag;
-    if (pend && sh.tdesc[0].kind() == 0) {
-      for (int i = tid; go && i < pend * 8; i += kConsumers) {
-        const int t = i >> 3, f = i & 7;
-        const Stage td = sh.tdesc[t];
-        if (f < td.nr()) {
-          const int slot = td.pos();
-          float g = 0.f, u = 0.f;
-#pragma unroll
-          for (int w = 0; w < kGroupWarps; ++w) { g += sh.red[t][w][f]; u += sh.red[t][w][8 + f]; }
-          float v;
-          if (slot >= S.top_k) {      // Qwen2MoeMLP in BF16: every linear / activation output is rounded
-            g = bf16_round(g); u = bf16_round(u);
-            v = bf16_round(bf16_round(silu_f32(g)) * u);
-          } else {
-            if (S.enc != ENC_BF16) { g *= sh.scale_x_inv; u *= sh.scale_x_inv; }
-            v = silu_f32(g) * u;
-          }
-          p.inter_buf[S.inter_off(slot) + td.r0 + f] = v;
-        }
-      }
-    } else if (pend) {
-      // the parked tiles are the slots of one row group in phase-B order: every (slot, row)
-      // contribution in parallel, then the ordered BF16 running sum per row
-      const int nr = sh.tdesc[0].nr();
-      for (int i = tid; go && i < pend * 16; i += kConsumers) {
-        const int t = i >> 4, r = i & 15;
-        const Stage td = sh.tdesc[t];
-        const int slot = sh.order[td.pos()];
-        float y = 0.f;
-        if (td.owned()) {
-          y = sh.red[t][0][r] + sh.red[t][1][r];
-        } else {
-#pragma unroll
-          for (int w = 0; w < kGroupWarps; ++w) y += sh.red[t][w][r];
-        }
-        if (S.enc_of(slot) != ENC_BF16) y *= sh.scaleB_inv;
-        sh.contrib[t][r] = slot >= S.top_k ? bf16_round(sh.sig_gate * bf16_round(y))
-                                           : bf16_round(y * sh.slots[slot].weight);
-      }
-      named_bar_sync(1, kConsumers);
-      if (go && tid < nr) {
-        float run = 0.f;
-        for (int t = 0; t < pend; ++t) run = bf16_round(run + sh.contrib[t][tid]);
-        p.out[sh.tdesc[0].r0 + tid] = __float2bfloat16_rn(run);
-      }
-    }
-    pend = 0;
-    named_bar_sync(1, kConsumers);
-  };
-
-  for (int n = 0;; ++n) {
-    if (n == first_b) {
-      // ---- phase boundary: grid barrier, then phase-B fragments from the float32 intermediates --
-      UMAQ_STAMP(2);
-      flush();
-      if (tid == 0) {
-        sh.amaxB = 0u;
-        // one monotonic counter; this launch is released at the next multiple of G
-        __threadfence();
-        red_release_add_u64(reinterpret_cast<unsigned long long*>(p.sync + 4), 1ull);
-        if (!*abort_flag) {
-          const unsigned long long target = sh.bar_target;
-          const uint64_t t0 = global_ns();
-          while (ld_acquire_u64(reinterpret_cast<const unsigned long long*>(p.sync + 4)) < target) {
-            if (global_ns() - t0 > kWaitBudgetNs) {
-              atomicExch(p.sync + 2, (unsigned)ERR_DEVICE_TIMEOUT);
-              *abort_flag = 1;
-              break;
-            }
-          }
-        }
-        __threadfence();
-      }
-      named_bar_sync(1, kConsumers);
-      UMAQ_STAMP(3);
-      if (n < nlist && !*abort_flag) {
-        // every CTA needs every slot's whole intermediate vector: one batch of L2 loads per warp
-        constexpr int kMaxU = kMaxUnitsB / kConsumerWarps;
-        float iv[kMaxU][4];
-        const int nunits = p.inter_total >> 7;
-        const int qunits = S.enc == ENC_BF16 ? 0 : (S.top_k * p.inter) >> 7;   // units that get the prescale
-        float a = 0.f;
-#pragma unroll
-        for (int j = 0; j < kMaxU; ++j) {
-          const int u = warp + j * kConsumerWarps;
-          iv[j][0] = iv[j][1] = iv[j][2] = iv[j][3] = 0.f;
-          if (u < nunits) {
-            const float4 f = __ldcg(reinterpret_cast<const float4*>(p.inter_buf + u * 128 + lane * 4));
-            iv[j][0] = f.x; iv[j][1] = f.y; iv[j][2] = f.z; iv[j][3] = f.w;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < kMaxU; ++j)
-          if (warp + j * kConsumerWarps < qunits)
-            a = fmaxf(a, fmaxf(fmaxf(fabsf(iv[j][0]), fabsf(iv[j][1])), fmaxf(fabsf(iv[j][2]), fabsf(iv[j][3]))));
-#pragma unroll
-        for (int o = 16; o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-        if (lane == 0 && a < 3.0e38f) atomicMax(&sh.amaxB, __float_as_uint(a));
-        named_bar_sync(1, kConsumers);
-        const float sc = prescale_for(__uint_as_float(sh.amaxB));
-        if (tid == 0) { sh.scaleB = sc; sh.scaleB_inv = 1.f / sc; }
-#pragma unroll
-        for (int j = 0; j < kMaxU; ++j) {
-          const int u = warp + j * kConsumerWarps;
-          if (u < nunits) {
-            if (u < qunits) {
-              const float sv[4] = {iv[j][0] * sc, iv[j][1] * sc, iv[j][2] * sc, iv[j][3] * sc};
-              store_unit(S.enc, xfB, u, sv, lane);
-            } else {
-              store_unit(ENC_BF16, xfB, u, iv[j], lane);
-            }
-          }
-        }
-        named_bar_sync(1, kConsumers);
-        // bias sums of the quantised slots: slot s's blocks start at bias_off(s)
-        if (qunits) {
-          const int per = row_bytes(S.enc, p.inter) >> 6;       // 64-byte weight blocks per down row
-          for (int sl = 0; sl < S.top_k; ++sl)
-            build_bias(S.enc, xfB + (size_t)S.inter_off(sl) * 2, biasB + S.bias_off(sl), p.inter, tid);
-          (void)per;
-        }
-      }
-      named_bar_sync(1, kConsumers);
-      UMAQ_STAMP(4);
-    }
-    if (n >= nlist) break;
-
-    const Stage st = sh.list[n];
-    const int s = n % nstages;
-    const int half = warp & 1;
-    const bool mine = st.owned() ? ((warp >> 1) == st.owner()) : (grp == st.group());
-    if (mine) {
-      const bool live = !*abort_flag && mbar_wait(&sh.full[s], (n / nstages) & 1);
-      if (!live && !*abort_flag && lane == 0) { atomicExch(p.sync + 2, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; }
-      if (live) {
-        const int kind = st.kind();
-        const int slot = kind ? sh.order[st.pos()] : st.pos();
-        StageView v;
-        v.buf = ring + (size_t)s * stage_bytes;
-        v.sb = st.nkb << 6;
-        v.nkb = st.nkb; v.kb0 = st.kb0; v.enc = S.enc_of(slot);
-        const int gk = (kind == 0 ? H : S.inter_of(slot)) >> 7;
-        v.sc = reinterpret_cast<const float*>(v.buf + 16 * v.sb);
-        if (kind == 0) {
-          v.sc_lo = q * gk; v.sc_hi = (8 + q) * gk;
-          v.xf = v.enc == ENC_BF16 ? xfA_bf : xfA; v.bias = biasA;
-        } else {
-          const int off = ((st.r0 * gk * 4) & 15) >> 2;
-          v.sc_lo = off + q * gk; v.sc_hi = off + (q + 8) * gk;
-          v.xf = xfB + (size_t)S.inter_off(slot) * 2; v.bias = biasB + S.bias_off(slot);
-        }
-        if (xreg && kind == 0 && v.enc == ENC_Q4) {
-          pair_from_smem<true>(v, 2 * w8, q, c, xr, acc_lo, acc_hi);
-        } else {
-          // owned tile: the two warps of the pair take alternate block pairs; K-split stage: the
-          // group's eight warps take block pairs (rows of >= 16 blocks) or single blocks
-          const bool pairs = st.owned() || v.nkb >= 16;
-          const int step = st.owned() ? 4 : (pairs ? 2 * kGroupWarps : kGroupWarps);
-          for (int b = st.owned() ? 2 * half : (pairs ? 2 * w8 : w8); b < v.nkb; b += step) {
-            if (pairs && b + 1 < v.nkb) pair_from_smem<false>(v, b, q, c, xr, acc_lo, acc_hi);
-            else block_from_smem(v, b, q, c, acc_lo, acc_hi);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive_n(&sh.empty[s], st.owned() ? kGroupWarps / 2 : 1);
-      }
-    }
-    if (!st.last()) continue;
-
-    // ---- tile done: park this warp's partial sums; reduce them in batches ------------------------
-    if (mine && c == 0) {
-      const int wslot = st.owned() ? half : w8;
-      sh.red[pend][wslot][q] = acc_lo; sh.red[pend][wslot][q + 8] = acc_hi;
-    }
-    if (tid == 0) sh.tdesc[pend] = st;
-    if (mine) acc_lo = acc_hi = 0.f;
-    ++pend;
-    // phase B: a row group is complete once its last slot is parked; phase A: when the buffer is full
-    if (st.kind() ? (st.pos() == S.nslots - 1) : (pend == kRedTiles)) flush();
-  }
-  UMAQ_STAMP(5);
-#undef UMAQ_STAMP
+  float* bias = reinterpret_cast<float*>(stage + (size_t)n * 2);
+  build_bias(enc, stage, bias, n, tid);
+  __syncthreads();
+  const int words = frag_body_bytes(n) >> 4;                // 16-byte words of fragments + padded bias
+  for (int i = tid; i < words; i += kThreads) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(stage)[i];
+  if (tid == 0) *reinterpret_cast<float*>(dst + frag_body_bytes(n)) = 1.f / sc;
 }
 
-struct SmemPlan { size_t fixed; int stage_bytes; int nstages; size_t total; };
+// =====================================================================================================
+// Kernel A: one CTA = 8 features of one slot: tile rows 0..7 gate rows, 8..15 up rows, all of K = H.
+// The four warps split the 64-byte blocks of the rows; SwiGLU after the cross-warp sum.  The CTA that
+// completes a slot publishes the fragment record of that slot's intermediate vector in place.
+// =====================================================================================================
+__global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float red[kWarps * 16];
+  __shared__ float red2[kWarps];
+  __shared__ int s_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
+  const int H = p.hidden;
+  pdl_launch_dependents();
 
-SmemPlan decode_smem_layout(const DecodeParams& p) {
-  SmemPlan s{};
-  size_t cur = (sizeof(Shared) + 127) & ~size_t(127);
-  cur += (size_t)p.hidden * 2 * 2 + (size_t)(p.hidden >> 6) * 4;
-  cur += (size_t)p.inter_total * 2 + ((size_t)(p.inter_total >> 6) + kMaxSlots) * 4;
-  s.fixed = (cur + 1023) & ~size_t(1023);
-  int kb = 16;   // BF16 rows are sliced to 1 KiB; quantised rows are staged whole
-  if (p.enc != ENC_BF16) {
-    kb = std::max(kb, row_bytes(p.enc, p.hidden) >> 6);
-    kb = std::max(kb, (row_bytes(p.enc, p.inter) + 63) >> 6);
+  const int tiles_r = p.inter >> 3, routed = p.top_k * tiles_r;
+  const bool shared_tile = (int)blockIdx.x >= routed;
+  const int slot = shared_tile ? p.top_k : (int)blockIdx.x / tiles_r;
+  const int f0 = (shared_tile ? (int)blockIdx.x - routed : (int)blockIdx.x % tiles_r) * 8;
+  const int enc = shared_tile ? ENC_BF16 : p.enc;
+  const int rb = row_bytes(enc, H), nblk = rb >> 6, gk = H >> 7;
+  const uint8_t *gate, *up;
+  const float *gate_s = nullptr, *up_s = nullptr;
+  if (shared_tile) {
+    gate = reinterpret_cast<const uint8_t*>(p.sh_gate) + (size_t)f0 * rb;
+    up = reinterpret_cast<const uint8_t*>(p.sh_up) + (size_t)f0 * rb;
+  } else {
+    long long e = load_index(p.idx, p.idx64, slot);
+    if (e < 0 || e >= p.experts) {
+      if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);
+      return;
+    }
+    const size_t row = (size_t)e * p.inter + f0;
+    gate = p.gate + row * rb; up = p.up + row * rb;
+    if (enc != ENC_BF16) { gate_s = p.gate_s + row * gk; up_s = p.up_s + row * gk; }
   }
-  s.stage_bytes = kb << 10;
-  const size_t limit = 227 * 1024;
-  const size_t per = (size_t)s.stage_bytes + kScaleArea;
-  s.nstages = s.fixed + per > limit ? 0 : (int)std::min<size_t>(kMaxRing, (limit - s.fixed) / per);
-  s.total = s.fixed + per * s.nstages;
-  return s;
+
+  // this warp's blocks: warp, warp+4, ...; groups of four are loaded, then multiplied
+  const int bpw = (nblk - warp + kWarps - 1) / kWarps;
+  uint4 wa[4], wb[4];
+  float sa[4], sb[4];
+  auto issue = [&](int first) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int kb = warp + (first + i) * kWarps;
+      if (first + i < bpw) {
+        wa[i] = ldg_stream(gate + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
+        wb[i] = ldg_stream(up + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
+        if (enc != ENC_BF16) {
+          const int g = enc == ENC_Q4 ? kb : (kb >> 1);
+          sa[i] = gate_s[q * gk + g];
+          sb[i] = up_s[q * gk + g];
+        }
+      }
+    }
+  };
+  issue(0);                             // weights are in flight while the activation fragments are built
+
+  // ---- x -> fragments in shared memory (quantised rows: prescaled fp16 + bias sums; BF16 rows: x as is) ---
+  uint8_t* xf = smem;
+  float* bias = reinterpret_cast<float*>(smem + (size_t)H * 2);
+  float x_inv = 1.f;
+  {
+    constexpr int kMaxV = 4;                                 // hidden <= 4 * 512 * ... handled in passes
+    for (int base = 0; base < H; base += kMaxV * kThreads * 4) {
+      float vals[kMaxV][4];
+      float am = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxV; ++j) {
+        const int k0 = base + tid * 4 + j * kThreads * 4;
+        vals[j][0] = vals[j][1] = vals[j][2] = vals[j][3] = 0.f;
+        if (k0 < H) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(p.x + k0);
+          vals[j][0] = __uint_as_float(raw.x << 16); vals[j][1] = __uint_as_float(raw.x & 0xffff0000u);
+          vals[j][2] = __uint_as_float(raw.y << 16); vals[j][3] = __uint_as_float(raw.y & 0xffff0000u);
+          am = fmaxf(am, fmaxf(fmaxf(fabsf(vals[j][0]), fabsf(vals[j][1])), fmaxf(fabsf(vals[j][2]), fabsf(vals[j][3]))));
+        }
+      }
+      float sx = 1.f;
+      if (enc != ENC_BF16) {
+        // hidden sizes up to 2048 are one pass, so the block maximum is the vector maximum; wider
+        // vectors would need the maximum over all passes first
+        sx = prescale_for(block_max(am < 3.0e38f ? am : 0.f, red2, tid));
+        x_inv = 1.f / sx;
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxV; ++j) {
+        const int k0 = base + tid * 4 + j * kThreads * 4;
+        if (k0 < H) {
+          const float v[4] = {vals[j][0] * sx, vals[j][1] * sx, vals[j][2] * sx, vals[j][3] * sx};
+          store_frag4(enc, xf, k0, v);
+        }
+      }
+    }
+    __syncthreads();
+    if (enc != ENC_BF16) { build_bias(enc, xf, bias, H, tid); __syncthreads(); }
+  }
+  const int fb = frag_block_bytes(enc);
+  float acc_lo = 0.f, acc_hi = 0.f;
+  for (int first = 0; first < bpw; first += 4) {
+    if (first) issue(first);
+    const int n = min(4, bpw - first);
+    const uint8_t* xp[4];
+    float bs[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int kb = warp + (first + min(i, n - 1)) * kWarps;
+      xp[i] = xf + (size_t)kb * fb + c * (fb >> 2);
+      bs[i] = enc == ENC_BF16 ? 0.f : bias[kb];
+    }
+    float d[4][4];
+    mma_blocks4<false>(enc, n, wa, wb, xp, true, d);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i < n) {
+        if (enc == ENC_BF16) { acc_lo += d[i][0]; acc_hi += d[i][2]; }
+        else { acc_lo = fmaf(sa[i], d[i][0] - bs[i], acc_lo); acc_hi = fmaf(sb[i], d[i][2] - bs[i], acc_hi); }
+      }
+    }
+  }
+  if (c == 0) { red[warp * 16 + q] = acc_lo; red[warp * 16 + 8 + q] = acc_hi; }
+  __syncthreads();
+  const int islot = shared_tile ? p.shared_inter : p.inter;
+  const int ioff = shared_tile ? p.top_k * p.inter : slot * p.inter;
+  if (tid < 8) {
+    float g = 0.f, u = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) { g += red[w * 16 + tid]; u += red[w * 16 + 8 + tid]; }
+    float v;
+    if (shared_tile) {                  // Qwen2MoeMLP in BF16: every linear / activation output is rounded
+      g = bf16_round(g); u = bf16_round(u);
+      v = bf16_round(bf16_round(silu_f32(g)) * u);
+    } else {
+      g *= x_inv; u *= x_inv;
+      v = silu_f32(g) * u;
+    }
+    p.inter_buf[ioff + f0 + tid] = v;
+  }
+  (void)x_inv;
+  // ---- the last CTA of the slot turns the slot's float32 intermediate into its fragment record, in place ---
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned done = atomicAdd(p.amax + slot, 1u);
+    const unsigned tiles = (unsigned)(islot >> 3);
+    s_last = (done == tiles - 1);
+    if (s_last) { atomicExch(p.amax + slot, 0u); __threadfence(); }
+  }
+  __syncthreads();
+  if (!s_last) return;
+  const int enc_b = shared_tile ? ENC_BF16 : p.enc;          // encoding of the down rows that read it
+  constexpr int kMaxV = 12;                                  // intermediate size <= 12 * 512
+  float vals[kMaxV][4];
+#pragma unroll
+  for (int j = 0; j < kMaxV; ++j) {
+    const int k0 = tid * 4 + j * kThreads * 4;
+    vals[j][0] = vals[j][1] = vals[j][2] = vals[j][3] = 0.f;
+    if (k0 < islot) {
+      const float4 f = __ldcg(reinterpret_cast<const float4*>(p.inter_buf + ioff + k0));
+      vals[j][0] = f.x; vals[j][1] = f.y; vals[j][2] = f.z; vals[j][3] = f.w;
+    }
+  }
+  __syncthreads();                       // every value is in registers before the region is overwritten
+  uint8_t* dst = reinterpret_cast<uint8_t*>(p.inter_buf + ioff);
+  if (enc_b == ENC_BF16) {
+#pragma unroll
+    for (int j = 0; j < kMaxV; ++j) {
+      const int k0 = tid * 4 + j * kThreads * 4;
+      if (k0 < islot) store_frag4(ENC_BF16, dst, k0, vals[j]);
+    }
+  } else {
+    publish_record<kMaxV>(enc_b, islot, vals, smem, red2, dst, tid);
+  }
+}
+
+// =====================================================================================================
+// Kernel B: one CTA = 8 output rows.  Slots are walked in ascending expert order, two per MMA tile
+// (tile rows 0..7: row n0+q of the first slot, rows 8..15: the same row of the second; the slots'
+// intermediate vectors are MMA columns 0 and 1).  The Qwen shared expert is a last, half-filled tile.
+// =====================================================================================================
+__global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ int s_order[kMaxSlots];
+  __shared__ int s_expert[kMaxSlots];
+  __shared__ float s_weight[kMaxSlots];
+  __shared__ float s_inv[kMaxSlots];
+  __shared__ float s_red[5][kWarps][16];
+  __shared__ float s_tmp[kWarps];
+  __shared__ float s_gate;
+  __shared__ int s_bad;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
+  const int H = p.hidden, I = p.inter, S = p.sh_gate ? p.shared_inter : 0;
+  const int n0 = blockIdx.x * 8;
+  // shared memory: the published records of the routed slots (fragments + bias), then the shared
+  // expert's BF16 vector
+  const int enc = p.enc;
+  const int rec = enc == ENC_BF16 ? I * 2 : frag_body_bytes(I);        // bytes copied per routed slot
+  uint8_t* recs = smem;
+  uint8_t* xs = smem + (size_t)p.top_k * rec;
+
+  // ---- routes: order by expert (stable), shared expert last ----------------------------------------------
+  if (tid == 0) s_bad = 0;
+  __syncthreads();
+  if (tid < p.top_k) {
+    const long long e = load_index(p.idx, p.idx64, tid);
+    if (e < 0 || e >= p.experts) s_bad = 1;
+    s_expert[tid] = (int)e;
+    s_weight[tid] = p.w[tid];
+  }
+  __syncthreads();
+  if (s_bad) {
+    if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);
+    return;
+  }
+  if (tid < p.top_k) {
+    int rank = 0;
+    for (int j = 0; j < p.top_k; ++j) rank += (s_expert[j] < s_expert[tid]) || (s_expert[j] == s_expert[tid] && j < tid);
+    s_order[rank] = tid;
+  }
+  __syncthreads();
+
+  const int rb = row_bytes(enc, I), nblk = rb >> 6, gk = I >> 7;
+  const int rtiles = (p.top_k + 1) >> 1;
+  const int bpw = (nblk - warp + kWarps - 1) / kWarps;           // blocks of a routed tile this warp owns
+  const int items = rtiles * bpw;                                // (tile, block) items of this warp
+  constexpr int kUp = 8;                                         // items whose loads go out before the wait
+  uint4 wa[kUp], wb[kUp];
+  float sa[kUp], sb[kUp];
+  auto issue_routed = [&](int first) {
+#pragma unroll
+    for (int i = 0; i < kUp; ++i) {
+      const int it = first + i;
+      if (it < items) {
+        const int t = it / bpw, kb = warp + (it - t * bpw) * kWarps;
+        const int a = s_order[2 * t], b = 2 * t + 1 < p.top_k ? s_order[2 * t + 1] : -1;
+        const size_t ra = ((size_t)s_expert[a] * H + n0 + q);
+        wa[i] = ldg_stream(p.down + ra * rb + ((size_t)kb << 6) + (c << 4));
+        const int g = enc == ENC_Q4 ? kb : (kb >> 1);
+        if (enc != ENC_BF16) sa[i] = p.down_s[ra * gk + g];
+        if (b >= 0) {
+          const size_t rbw = ((size_t)s_expert[b] * H + n0 + q);
+          wb[i] = ldg_stream(p.down + rbw * rb + ((size_t)kb << 6) + (c << 4));
+          if (enc != ENC_BF16) sb[i] = p.down_s[rbw * gk + g];
+        } else { wb[i] = make_uint4(0, 0, 0, 0); sb[i] = 0.f; }
+      }
+    }
+  };
+  issue_routed(0);                      // weights do not depend on kernel A: in flight before the wait
+
+  // sigmoid gate of the shared expert: bf16(sigmoid(bf16(x . wg)))
+  if (S) {
+    float acc = 0.f;
+    for (int k = tid * 2; k < H; k += kThreads * 2) {
+      const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(p.x + k);
+      const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.sh_gatevec + k);
+      acc += __low2float(xv) * __low2float(gv) + __high2float(xv) * __high2float(gv);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_tmp[warp] = acc;
+    __syncthreads();
+    if (tid == 0) {
+      float t = 0.f;
+      for (int i = 0; i < kWarps; ++i) t += s_tmp[i];
+      t = bf16_round(t);
+      s_gate = bf16_round(1.f / (1.f + expf(-t)));
+    }
+    __syncthreads();
+  }
+
+  pdl_wait();                           // kernel A's records are complete and visible from here on
+
+  // ---- copy the records into shared memory (straight 16-byte copies, no arithmetic) ------------------------
+  for (int s = 0; s < p.top_k; ++s) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I);
+    uint4* dst = reinterpret_cast<uint4*>(recs + (size_t)s * rec);
+    for (int i = tid; i < (rec >> 4); i += kThreads) dst[i] = __ldcg(src + i);
+    if (tid == 0 && enc != ENC_BF16) s_inv[s] = __ldcg(reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(src) + rec));
+  }
+  if (S) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)p.top_k * I);
+    uint4* dst = reinterpret_cast<uint4*>(xs);
+    for (int i = tid; i < (S * 2) >> 4; i += kThreads) dst[i] = __ldcg(src + i);
+  }
+  __syncthreads();
+
+  // ---- routed tiles: groups of four (tile, block) items, eight MMA chains in flight ------------------------
+  const int fb = frag_block_bytes(enc);
+  float acc_lo = 0.f, acc_hi = 0.f;
+  for (int first = 0; first < items; first += kUp) {
+    if (first) issue_routed(first);
+#pragma unroll
+    for (int g4 = 0; g4 < kUp; g4 += 4) {
+      if (first + g4 < items) {
+        const int n = min(4, items - first - g4);
+        const uint8_t* xp[4];
+        float bsa[4], bsb[4];
+        int tl[4], jl[4];
+        uint4 ga[4], gb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int it = first + g4 + min(i, n - 1);
+          const int t = it / bpw, j = it - t * bpw, kb = warp + j * kWarps;
+          const int a = s_order[2 * t], b = 2 * t + 1 < p.top_k ? s_order[2 * t + 1] : a;
+          // MMA column 0 <- first slot's vector (lanes of quad 0), column 1 <- second slot's (quad 1)
+          const uint8_t* base = recs + (size_t)(q == 0 ? a : b) * rec;
+          xp[i] = base + (size_t)kb * fb + c * (fb >> 2);
+          if (enc != ENC_BF16) {
+            bsa[i] = reinterpret_cast<const float*>(recs + (size_t)a * rec + (size_t)I * 2)[kb];
+            bsb[i] = reinterpret_cast<const float*>(recs + (size_t)b * rec + (size_t)I * 2)[kb];
+          } else { bsa[i] = bsb[i] = 0.f; }
+          tl[i] = t; jl[i] = j;
+          ga[i] = wa[g4 + i]; gb[i] = wb[g4 + i];
+        }
+        float d[4][4];
+        mma_blocks4<false>(enc, n, ga, gb, xp, q < 2, d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (i < n) {
+            if (enc == ENC_BF16) { acc_lo += d[i][0]; acc_hi += d[i][3]; }
+            else {
+              acc_lo = fmaf(sa[g4 + i], d[i][0] - bsa[i], acc_lo);
+              acc_hi = fmaf(sb[g4 + i], d[i][3] - bsb[i], acc_hi);
+            }
+            if (jl[i] == bpw - 1) {        // last block of the tile for this warp: park the partial sums
+              if (c == 0) { s_red[tl[i]][warp][q] = acc_lo; s_red[tl[i]][warp][8 + q] = acc_hi; }
+              acc_lo = acc_hi = 0.f;
+            }
+          }
+        }
+      }
+    }
+  }
+  if (bpw == 0 && c == 0)
+    for (int t = 0; t < rtiles; ++t) { s_red[t][warp][q] = 0.f; s_red[t][warp][8 + q] = 0.f; }
+
+  // ---- shared expert: one half-filled BF16 tile, K = S, blocks split over the warps in groups of four ------
+  if (S) {
+    const int rbs = 2 * S, nb = rbs >> 6;
+    const uint8_t* rowp = reinterpret_cast<const uint8_t*>(p.sh_down) + (size_t)(n0 + q) * rbs;
+    const uint4 zero4[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    float acc = 0.f;
+    for (int first = warp; first < nb; first += kWarps * 4) {
+      uint4 w[4];
+      const uint8_t* xp[4];
+      int n = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int kb = first + i * kWarps;
+        if (kb < nb) { w[i] = ldg_stream(rowp + ((size_t)kb << 6) + (c << 4)); n = i + 1; }
+        else w[i] = make_uint4(0, 0, 0, 0);
+        xp[i] = xs + (size_t)min(kb, nb - 1) * 64 + c * 16;
+      }
+      float d[4][4];
+      mma_blocks4<false>(ENC_BF16, n, w, zero4, xp, true, d);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (i < n) acc += d[i][0];
+    }
+    if (c == 0) { s_red[4][warp][q] = acc; s_red[4][warp][8 + q] = 0.f; }
+  }
+  __syncthreads();
+
+  // ---- ordered combine: ascending expert, BF16 rounding of every contribution and partial sum --------------
+  if (tid < 8 && n0 + tid < H) {
+    float run = 0.f;
+    for (int r = 0; r < p.top_k; ++r) {
+      const int t = r >> 1, half = r & 1, slot = s_order[r];
+      float y = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) y += s_red[t][w][half * 8 + tid];
+      if (enc != ENC_BF16) y *= s_inv[slot];
+      run = bf16_round(run + bf16_round(y * s_weight[slot]));
+    }
+    if (S) {
+      float y = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) y += s_red[4][w][tid];
+      run = bf16_round(run + bf16_round(s_gate * bf16_round(y)));
+    }
+    p.out[n0 + tid] = __float2bfloat16_rn(run);
+  }
+}
+
+size_t gateup_smem(const DecodeParams& p) {
+  const int big = std::max(p.hidden, std::max(p.inter, p.sh_gate ? p.shared_inter : 0));
+  return (size_t)frag_body_bytes(big) + 64;                      // x fragments, later staging of a record
+}
+size_t down_smem(const DecodeParams& p) {
+  const size_t rec = p.enc == ENC_BF16 ? (size_t)p.inter * 2 : (size_t)frag_body_bytes(p.inter);
+  return (size_t)p.top_k * rec + (p.sh_gate ? (size_t)p.shared_inter * 2 : 0) + 64;
 }
 
 }  // namespace
@@ -899,8 +677,9 @@ size_t decode_workspace_bytes(int top_k, int inter, int shared_inter) {
 }
 
 int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
-  if (p.top_k < 1 || p.top_k > 8 || p.hidden % 128 || p.inter % 128 || p.hidden < 128 || p.inter < 128 ||
-      (p.sh_gate && (p.shared_inter % 128 || p.shared_inter < 128)) || p.enc < 0 || p.enc > 2) {
+  if (p.top_k < 1 || p.top_k > 8 || p.hidden % 512 || p.inter % 128 || p.hidden < 512 || p.inter < 128 ||
+      p.hidden > 2048 || p.inter > 6144 || (p.sh_gate && (p.shared_inter % 128 || p.shared_inter < 128 || p.shared_inter > 6144)) ||
+      p.enc < 0 || p.enc > 2) {
     set_error("decode: unsupported shape (hidden %d, intermediate %d, top_k %d, shared %d, encoding %d)", p.hidden,
               p.inter, p.top_k, p.shared_inter, p.enc);
     return ERR_BAD_ARGUMENT;
@@ -910,31 +689,37 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
     return ERR_BAD_ARGUMENT;
   }
   p.inter_total = p.top_k * p.inter + (p.sh_gate ? p.shared_inter : 0);
-  if (p.hidden > kMaxUnitsX * 128 || p.inter_total > kMaxUnitsB * 128) {
-    set_error("decode: hidden size %d or summed intermediate size %d beyond the register plan", p.hidden, p.inter_total);
-    return ERR_UNSUPPORTED;
-  }
-  const SmemPlan plan = decode_smem_layout(p);
-  const int grid = sm_count();
-  if (plan.nstages < 2 || grid < 1) {
-    set_error("decode: shape does not fit the shared-memory plan (fixed %zu B, stage %d B)", plan.fixed,
-              plan.stage_bytes);
-    return ERR_UNSUPPORTED;
-  }
-  p.stage_bytes = plan.stage_bytes;
-  p.nstages = plan.nstages;
+  const size_t smem_a = gateup_smem(p), smem_b = down_smem(p);
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     if (e != cudaSuccess) { set_error("decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
     configured_device = dev;
   }
-  void* args[] = {&p};
-  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(moe_decode_kernel), dim3(grid), dim3(kThreads),
-                                              args, plan.total, stream);
-  if (e != cudaSuccess) { set_error("decode: launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+  if (smem_b > 100 * 1024 || smem_a > 48 * 1024) {
+    set_error("decode: shape needs more shared memory than planned");
+    return ERR_UNSUPPORTED;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = stream;
+  cfg.gridDim = dim3(p.top_k * (p.inter / 8) + (p.sh_gate ? p.shared_inter / 8 : 0));
+  cfg.dynamicSmemBytes = smem_a;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gateup_kernel, p);
+  if (e != cudaSuccess) { set_error("decode: gate/up launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+  // The down kernel is chained by programmatic stream serialisation: its CTAs may start while the
+  // gate/up kernel drains, issue their weight loads, and wait on-device before reading its records.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3((p.hidden + 7) / 8);
+  cfg.dynamicSmemBytes = smem_b;
+  e = cudaLaunchKernelEx(&cfg, decode_down_kernel, p);
+  if (e != cudaSuccess) { set_error("decode: down launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
   return ERR_NONE;
 }
 

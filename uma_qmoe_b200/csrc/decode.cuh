@@ -8,10 +8,11 @@
 
 namespace umaq {
 
-// Workspace layout (bytes): [0,64) control words {arrive count, generation, error, ...},
-// [192,1024) cycle stamps CTA 0 leaves for diagnosis (6 phase stamps, then wait-done / compute-done
-// per ring stage), [1024,...) float32 intermediate, one run per slot.  Must be zero before its
-// first use.
+// Workspace layout (bytes): [0,1024) header -- the uint32 at byte 8 is the sticky status word, the
+// uint32 words from byte 64 count finished gate/up tiles per slot (self-resetting); [1024,...) one run
+// per slot (routed slots in route order, then the shared expert) that first holds the float32
+// intermediate and then, in place, its fragment record.
+// Must be zero before its first use.
 constexpr size_t kDecodeWsHeader = 1024;
 
 struct DecodeParams {
