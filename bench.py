@@ -231,7 +231,7 @@ def native_arm(args) -> None:
                 w, idx = stack.route(l, x)
                 x = rms_renorm(torch.ops.uma_qmoe.moe_forward(x, idx, w, l, handle, True))
             return x
-        launches_per_step = LAYERS * 6          # router, sort, gather, 2 grouped GEMMs, combine
+        launches_per_step = LAYERS * 7          # router, sort (2 kernels), gather, 2 grouped GEMMs, combine
     else:
         from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE
         eps = [ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k) for layer in stack.layers]
@@ -241,7 +241,7 @@ def native_arm(args) -> None:
                 w, idx = stack.route(l, x)
                 x = rms_renorm(eps[l].forward(x, idx, w))
             return x
-        launches_per_step = LAYERS * 9          # router, sort, gather; on received rows sort, gather, 2 GEMMs, combine; combine
+        launches_per_step = LAYERS * 11         # router, sort, gather; on received rows sort, gather, 2 GEMMs, combine; combine
 
     def step_resident():
         run_stack(x_dev)
@@ -347,9 +347,14 @@ def kernel_case(args) -> None:
             ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter)
             ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw)
         ms = timed(run, args.steps, args.warmup, 1)
+        ms1 = timed(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter),
+                    args.steps, args.warmup, 1)
+        ms2 = timed(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight,
+                                             out=yw), args.steps, args.warmup, 1)
         flops = 2.0 * xs.shape[0] * 3 * shape.hidden * shape.intermediate
-        print(json.dumps({"case": "gemm", "tokens": args.tokens, "ms_both_gemms": ms,
-                          "tflops": flops / (ms / 1e3) / 1e12, "status": int(routes.status.item())}))
+        print(json.dumps({"case": "gemm", "tokens": args.tokens, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
+                          "tflops": flops / (ms / 1e3) / 1e12, "tflops_gate_up": flops * 2 / 3 / (ms1 / 1e3) / 1e12,
+                          "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
 
 
 def main() -> None:

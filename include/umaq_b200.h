@@ -162,11 +162,12 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared /
  * sorted_route[routes] (route ids in expert order), route_pos[routes] (its inverse),
  * sorted_weight[routes], and the tile list of the grouped GEMM (up to 256 routes of one expert each):
  * *num_tiles and tile_table = int[3 * max_tiles] holding expert, first row, row count.
- * max_tiles >= ceil(routes / 128) + E.  *status: sticky error word, zero it first. */
+ * max_tiles >= ceil(routes / 128) + E.  *status: sticky error word, zero it first.
+ * scratch (device, may be NULL): ceil(routes / 2048) * E ints let large sorts run on many CTAs. */
 int umaq_route_sort(const void* expert_indices, int indices_are_int64, const float* routing_weights, int tokens,
                     int top_k, int num_experts, int* counts, int* offsets, int* sorted_route, int* route_pos,
                     float* sorted_weight, int* num_tiles, int* tile_table, int max_tiles, unsigned* status,
-                    void* stream);
+                    int* scratch, long long scratch_ints, void* stream);
 /* out[i] = hidden[sorted_route[i] / top_k] (sorted_route == NULL: out[i] = hidden[i]);
  * permute != 0 writes every run of 8 elements as [0,4,1,5,2,6,3,7], the K order the
  * quantised grouped GEMM expects of its activations. */

@@ -99,3 +99,32 @@ def test_router_matches_oracle(model, renorm):
     kth = own.sort(dim=1, descending=True).values[:, shape.top_k - 1]
     assert bool((chosen >= kth[:, None] - 1e-9).all())
     assert int((~same_logits).sum()) <= 0.03 * x.shape[0]
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,dtype", [(8192, 8, 64, torch.int64), (5000, 4, 60, torch.int32),
+                                                        (3, 8, 64, torch.int64)])
+def test_route_sort_is_the_stable_sort_by_expert(tokens, top_k, experts, dtype):
+    """Single-CTA and many-CTA sorts both equal a stable argsort; the tile list covers every route once."""
+    from uma_qmoe_b200 import ops
+    gen = torch.Generator().manual_seed(SEED + tokens)
+    popularity = 1.0 / torch.arange(1, experts + 1, dtype=torch.float64) ** 1.2
+    idx = torch.multinomial(popularity.expand(tokens, experts), top_k, replacement=False, generator=gen).to(dtype)
+    w = torch.rand((tokens, top_k), generator=gen, dtype=torch.float32)
+    r = ops.route_sort(idx.to(DEV), w.to(DEV), experts)
+    torch.cuda.synchronize()
+    assert int(r.status.item()) == 0
+    flat = idx.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=experts)
+    assert torch.equal(r.sorted_route.cpu().long(), order)
+    assert torch.equal(r.counts.cpu().long(), counts)
+    assert torch.equal(r.offsets.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]))
+    assert torch.equal(r.route_pos.cpu().long()[order], torch.arange(flat.numel()))
+    assert torch.equal(r.sorted_weight.cpu(), w.reshape(-1)[order])
+    tiles = int(r.num_tiles.item())
+    table = r.tile_table.cpu().view(3, r.max_tiles)[:, :tiles]
+    covered = torch.zeros(flat.numel(), dtype=torch.int32)
+    for e, row0, rows in table.t().tolist():
+        assert (flat[order[row0:row0 + rows]] == e).all()
+        covered[row0:row0 + rows] += 1
+    assert (covered == 1).all()

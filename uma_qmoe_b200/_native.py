@@ -45,7 +45,7 @@ SIGNATURES = {
                                    C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "umaq_route_sort": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
-                                  C.c_void_p]),
+                                  C.c_void_p, C.c_longlong, C.c_void_p]),
     "umaq_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p,
                                    C.c_void_p]),
     "umaq_grouped_gemm": (C.c_int, [C.POINTER(Layer), C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p,

@@ -127,7 +127,8 @@ int umaq_route_topk(const void* hidden_bf16, const void* router_weight_bf16, int
 
 int umaq_route_sort(const void* expert_indices, int indices_are_int64, const float* routing_weights, int tokens, int top_k,
                     int num_experts, int* counts, int* offsets, int* sorted_route, int* route_pos, float* sorted_weight,
-                    int* num_tiles, int* tile_table, int max_tiles, unsigned* status, void* stream) {
+                    int* num_tiles, int* tile_table, int max_tiles, unsigned* status, int* scratch, long long scratch_ints,
+                    void* stream) {
   if (!expert_indices || !routing_weights || !counts || !offsets || !sorted_route || !route_pos || !sorted_weight ||
       !num_tiles || !tile_table || !status || max_tiles <= 0) {
     set_error("umaq_route_sort: null argument");
@@ -140,6 +141,7 @@ int umaq_route_sort(const void* expert_indices, int indices_are_int64, const flo
   a.sorted_weight = sorted_weight; a.num_tiles = num_tiles;
   a.tile_expert = tile_table; a.tile_row0 = tile_table + max_tiles; a.tile_rows = tile_table + 2 * max_tiles;
   a.max_tiles = max_tiles; a.status = status;
+  a.scratch = scratch; a.scratch_ints = scratch ? scratch_ints : 0;
   return launch_route_sort(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -184,7 +186,8 @@ int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, i
 
 namespace {
 struct PrefillPlan {
-  size_t status, counts, offsets, num_tiles, tiles, sorted_route, route_pos, sorted_weight, xs, inter, yw;
+  size_t status, counts, offsets, num_tiles, tiles, sort_scratch, sorted_route, route_pos, sorted_weight, xs, inter, yw;
+  long long sort_ints;
   size_t s_num_tiles, s_tiles, s_inter, s_out, total;
   int max_tiles, s_max_tiles;
 };
@@ -201,6 +204,8 @@ PrefillPlan prefill_plan(long long tokens, int top_k, int experts, int hidden, i
   p.offsets = take((size_t)(experts + 1) * 4);
   p.num_tiles = take(4);
   p.tiles = take((size_t)p.max_tiles * 12);
+  p.sort_ints = (long long)((routes + 2047) / 2048) * experts;
+  p.sort_scratch = take((size_t)p.sort_ints * 4);
   p.sorted_route = take(routes * 4);
   p.route_pos = take(routes * 4);
   p.sorted_weight = take(routes * 4);
@@ -258,6 +263,7 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, 
   sa.num_tiles = reinterpret_cast<int*>(at(pl.num_tiles));
   sa.tile_expert = tiles; sa.tile_row0 = tiles + pl.max_tiles; sa.tile_rows = tiles + 2 * pl.max_tiles;
   sa.max_tiles = pl.max_tiles; sa.status = status;
+  sa.scratch = reinterpret_cast<int*>(at(pl.sort_scratch)); sa.scratch_ints = pl.sort_ints;
   int rc = launch_route_sort(sa, stream);
   if (rc) return rc;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(at(pl.xs));

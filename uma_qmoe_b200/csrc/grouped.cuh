@@ -68,6 +68,8 @@ struct SortArgs {
   int* num_tiles; int* tile_expert; int* tile_row0; int* tile_rows;   // 128-route tiles
   int max_tiles;
   unsigned* status;
+  int* scratch;                    // optional: ceil(routes / 2048) * experts ints let the sort use many CTAs
+  long long scratch_ints;
 };
 int launch_route_sort(const SortArgs& a, cudaStream_t stream);
 

@@ -297,6 +297,98 @@ __global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs
   }
 }
 
+// ---- the same sort over several CTAs (large route counts) ------------------------------------------------
+// Pass 1: every CTA histograms its contiguous chunk of kChunk routes.  Pass 2: every CTA rebuilds the
+// per-expert totals and its own starting positions from the chunk histograms (a few thousand loads),
+// then places its routes exactly like the single-CTA kernel.  CTA 0 also writes counts, offsets and
+// the tile list.
+constexpr int kChunk = 2048;
+
+__global__ void __launch_bounds__(kSortThreads) route_hist_kernel(const SortArgs a, int* __restrict__ chunk_hist) {
+  __shared__ int hist[kMaxSortExperts];
+  const int tid = threadIdx.x, E = a.experts;
+  const long long routes = (long long)a.tokens * a.top_k;
+  const long long begin = (long long)blockIdx.x * kChunk, end = min(routes, begin + kChunk);
+  if (tid < kMaxSortExperts) hist[tid] = 0;
+  __syncthreads();
+  bool bad = false;
+  for (long long i = begin + tid; i < end; i += kSortThreads) {
+    const int e = load_expert(a.indices, a.idx64, i);
+    if (e < 0 || e >= E) bad = true; else atomicAdd(&hist[e], 1);
+  }
+  if (bad) atomicExch(a.status, (unsigned)ERR_BAD_ARGUMENT);
+  __syncthreads();
+  if (tid < E) chunk_hist[(size_t)blockIdx.x * E + tid] = hist[tid];
+}
+
+__global__ void __launch_bounds__(kSortThreads) route_place_kernel(const SortArgs a, const int* __restrict__ chunk_hist,
+                                                                   int chunks) {
+  __shared__ int hist[32][kMaxSortExperts];     // per-warp counts of this chunk, then running positions
+  __shared__ int total[kMaxSortExperts + 1];    // per-expert totals, then first position of this chunk
+  __shared__ int before[kMaxSortExperts];       // routes of the expert in earlier chunks
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, E = a.experts;
+  const long long routes = (long long)a.tokens * a.top_k;
+  const long long cbegin = (long long)blockIdx.x * kChunk, cend = min(routes, cbegin + kChunk);
+  const long long per_warp = kChunk / 32;
+  const long long begin = min(cend, cbegin + warp * per_warp), end = min(cend, begin + per_warp);
+  for (int i = tid; i < 32 * kMaxSortExperts; i += kSortThreads) (&hist[0][0])[i] = 0;
+  if (tid < E) {
+    int all = 0, prev = 0;
+    for (int c2 = 0; c2 < chunks; ++c2) {
+      const int v = chunk_hist[(size_t)c2 * E + tid];
+      if (c2 < (int)blockIdx.x) prev += v;
+      all += v;
+    }
+    total[tid] = all;
+    before[tid] = prev;
+    if (blockIdx.x == 0) a.counts[tid] = all;
+  }
+  __syncthreads();
+  for (long long i = begin + lane; i < end; i += 32) {
+    const int e = load_expert(a.indices, a.idx64, i);
+    if (e >= 0 && e < E) atomicAdd(&hist[warp][e], 1);
+  }
+  __syncthreads();
+  if (tid < E) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) { const int c2 = hist[w][tid]; hist[w][tid] = run; run += c2; }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c2 = total[e];
+      if (blockIdx.x == 0) {
+        a.offsets[e] = run;
+        for (int r = 0; r < c2 && tiles < a.max_tiles; r += kTileRows, ++tiles) {
+          a.tile_expert[tiles] = e; a.tile_row0[tiles] = run + r; a.tile_rows[tiles] = min(kTileRows, c2 - r);
+        }
+      }
+      total[e] = run + before[e];
+      run += c2;
+    }
+    if (blockIdx.x == 0) { a.offsets[E] = run; *a.num_tiles = tiles; }
+  }
+  __syncthreads();
+  for (long long base = begin; base < end; base += 32) {
+    const long long i = base + lane;
+    const bool live = i < end;
+    int e = live ? load_expert(a.indices, a.idx64, i) : -1 - lane;
+    if (live && (e < 0 || e >= E)) e = -1 - lane;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0) {
+      const int pos = total[e] + hist[warp][e] + rank;
+      a.sorted_route[pos] = (int)i;
+      a.route_pos[i] = pos;
+      a.sorted_weight[pos] = a.weights[i];
+    }
+    __syncwarp();
+    if (e >= 0 && rank == 0) hist[warp][e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
 // ---- gather: sorted_x[i] = x[sorted_route[i] / top_k], optionally in the permuted K order ------------------
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route, int top_k,
                                    long long routes, int hidden, int permute, __nv_bfloat16* __restrict__ out) {
@@ -418,7 +510,14 @@ int launch_route_sort(const SortArgs& a, cudaStream_t stream) {
     set_error("route sort: unsupported shape (tokens %d, top_k %d, experts %d)", a.tokens, a.top_k, a.experts);
     return ERR_BAD_ARGUMENT;
   }
-  route_sort_kernel<<<1, kSortThreads, 0, stream>>>(a);
+  const long long routes = (long long)a.tokens * a.top_k;
+  const int chunks = (int)((routes + kChunk - 1) / kChunk);
+  if (chunks <= 2 || !a.scratch || a.scratch_ints < (long long)chunks * a.experts) {
+    route_sort_kernel<<<1, kSortThreads, 0, stream>>>(a);
+    return check_launch("route sort");
+  }
+  route_hist_kernel<<<chunks, kSortThreads, 0, stream>>>(a, a.scratch);
+  route_place_kernel<<<chunks, kSortThreads, 0, stream>>>(a, a.scratch, chunks);
   return check_launch("route sort");
 }
 

@@ -186,6 +186,7 @@ def route_sort(indices: torch.Tensor, weights: torch.Tensor, num_experts: int) -
     dev = indices.device
     i32 = lambda n: torch.empty(n, dtype=torch.int32, device=dev)
     max_tiles = (routes + 127) // 128 + num_experts
+    scratch = i32(((routes + 2047) // 2048) * num_experts)
     r = SortedRoutes(i32(num_experts), i32(num_experts + 1), i32(routes), i32(routes),
                      torch.empty(routes, dtype=torch.float32, device=dev), i32(1), i32(3 * max_tiles), max_tiles,
                      torch.zeros(1, dtype=torch.int32, device=dev))
@@ -193,7 +194,7 @@ def route_sort(indices: torch.Tensor, weights: torch.Tensor, num_experts: int) -
         indices.contiguous().data_ptr(), int(indices.dtype == torch.int64), weights.contiguous().data_ptr(), tokens,
         top_k, num_experts, r.counts.data_ptr(), r.offsets.data_ptr(), r.sorted_route.data_ptr(),
         r.route_pos.data_ptr(), r.sorted_weight.data_ptr(), r.num_tiles.data_ptr(), r.tile_table.data_ptr(),
-        max_tiles, r.status.data_ptr(), _stream(dev))
+        max_tiles, r.status.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream(dev))
     _native.check(code, "umaq_route_sort")
     return r
 

@@ -48,8 +48,7 @@ def random_shared_expert(shape: ModelShape, seed: int, device: torch.device) -> 
 def rms_renorm(x: torch.Tensor) -> torch.Tensor:
     """Keeps the activations at unit RMS from layer to layer (there is no attention or norm between
     the MoE layers of the synthetic stack)."""
-    f = x.float()
-    return (f * torch.rsqrt(f.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).to(torch.bfloat16)
+    return torch.nn.functional.rms_norm(x, (x.shape[-1],), None, 1e-6)
 
 
 @dataclass
