@@ -344,15 +344,16 @@ def kernel_case(args) -> None:
         yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
 
         def run():
-            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter)
-            ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw)
+            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter, variant=args.variant)
+            ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw,
+                             variant=args.variant)
         ms = timed(run, args.steps, args.warmup, 1)
-        ms1 = timed(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter),
-                    args.steps, args.warmup, 1)
+        ms1 = timed(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter,
+                                             variant=args.variant), args.steps, args.warmup, 1)
         ms2 = timed(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight,
-                                             out=yw), args.steps, args.warmup, 1)
+                                             out=yw, variant=args.variant), args.steps, args.warmup, 1)
         flops = 2.0 * xs.shape[0] * 3 * shape.hidden * shape.intermediate
-        print(json.dumps({"case": "gemm", "tokens": args.tokens, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
+        print(json.dumps({"case": "gemm", "tokens": args.tokens, "variant": args.variant, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
                           "tflops": flops / (ms / 1e3) / 1e12, "tflops_gate_up": flops * 2 / 3 / (ms1 / 1e3) / 1e12,
                           "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
 
@@ -367,6 +368,8 @@ def main() -> None:
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")
+    ap.add_argument("--variant", type=int, default=0, choices=(0, 1, 2),
+                    help="grouped GEMM kernel of the --only gemm case: 0/1 one CTA per tile (default), 2 CTA pairs")
     args = ap.parse_args()
     if args.only != "all":
         kernel_case(args)

@@ -67,12 +67,13 @@ def test_prefill_many_tokens_few_experts_matches_oracle():
     assert_parity(_run_prefill(layer, x, idx, w), want)
 
 
+@pytest.mark.parametrize("tokens", [500, 40])      # tensor-core kernel (ragged last CTA) / tiled kernel
 @pytest.mark.parametrize("model,renorm", [("olmoe", True), ("olmoe", False), ("qwen", False)])
-def test_router_matches_oracle(model, renorm):
+def test_router_matches_oracle(model, renorm, tokens):
     from uma_qmoe_b200 import ops
     shape = syn.OLMOE if model == "olmoe" else syn.QWEN
     wr = syn.router_weight(SEED, 1, shape, skew=1.5)
-    x = syn.activations(SEED + 31, 512)
+    x = syn.activations(SEED + 31, tokens)
     probs, w_ref, idx_ref = orc.router_topk(x, wr, shape.top_k, renorm)
     w, idx, logits = ops.route_topk(x.to(DEV), wr.to(DEV), shape.top_k, renorm, return_logits=True)
     w, idx, logits = w.cpu(), idx.cpu(), logits.cpu()
@@ -87,7 +88,7 @@ def test_router_matches_oracle(model, renorm):
     all_clear = same_logits & (srt[:, : k + 1].diff(dim=1) != 0).all(dim=1)
     # the kernel rounds an exactly summed dot product; the CPU GEMM of the oracle is off by one BF16 ulp on
     # about 1 logit in 5000, i.e. on 1-2 % of the rows
-    assert same_logits.float().mean() >= 0.97 and boundary_clear.float().mean() > 0.9 and all_clear.any()
+    assert same_logits.float().mean() >= 0.95 and boundary_clear.float().mean() > 0.85 and all_clear.any()
     assert torch.equal(idx[boundary_clear].sort(dim=1).values, idx_ref[boundary_clear].sort(dim=1).values)
     assert torch.allclose(w[boundary_clear].sort(dim=1).values, w_ref[boundary_clear].sort(dim=1).values,
                           rtol=2e-5, atol=1e-8)
@@ -98,7 +99,7 @@ def test_router_matches_oracle(model, renorm):
     chosen = own.gather(1, idx)
     kth = own.sort(dim=1, descending=True).values[:, shape.top_k - 1]
     assert bool((chosen >= kth[:, None] - 1e-9).all())
-    assert int((~same_logits).sum()) <= 0.03 * x.shape[0]
+    assert int((~same_logits).sum()) <= 0.05 * x.shape[0]
 
 
 @pytest.mark.parametrize("tokens,top_k,experts,dtype", [(8192, 8, 64, torch.int64), (5000, 4, 60, torch.int32),
@@ -128,3 +129,62 @@ def test_route_sort_is_the_stable_sort_by_expert(tokens, top_k, experts, dtype):
         assert (flat[order[row0:row0 + rows]] == e).all()
         covered[row0:row0 + rows] += 1
     assert (covered == 1).all()
+
+
+def _stagewise(layer, x, idx, w, variant):
+    """Prefill assembled from the exported stages, with the grouped GEMM kernel chosen explicitly."""
+    from uma_qmoe_b200 import ops
+    quant = layer.encoding != "bf16_le"
+    r = ops.route_sort(idx, w, layer.num_experts)
+    xs = ops.gather_rows(x, r.sorted_route, idx.shape[1], permute=quant)
+    inter = ops.grouped_gemm(layer, 0, xs, r, permute_out=quant, variant=variant)
+    yw = ops.grouped_gemm(layer, 1, inter, r, route_weight=r.sorted_weight, variant=variant)
+    y = ops.combine_routes(yw, idx, r.route_pos)
+    torch.cuda.synchronize()
+    assert int(r.status.item()) == 0
+    return inter, y
+
+
+@pytest.mark.parametrize("encoding", ["q4_group128", "q8_group128", "bf16_le"])
+def test_pair_kernel_matches_single_cta_kernel_and_oracle(encoding):
+    """The persistent CTA-pair GEMM (cta_group::2) against the one-CTA-per-tile GEMM and the oracle: 700 tokens
+    over 5 experts give full 256-route tiles, ragged tiles above and below 128 routes, and enough (tile, column)
+    items that every cluster walks several of them with both accumulators in use."""
+    src = expert_source(SEED, 3, "olmoe", encoding)
+    tokens = 700
+    rng = np.random.default_rng(11)
+    pool = np.array([0, 2, 3, 5, 9])
+    prob = np.array([0.45, 0.3, 0.15, 0.07, 0.03])
+    idx = torch.from_numpy(np.stack([rng.choice(pool, size=2, replace=False, p=prob) for _ in range(tokens)]).astype(np.int64))
+    w = torch.from_numpy(rng.random((tokens, 2), dtype=np.float32) / 2)
+    layer = stage_layer({int(e): src(int(e)) for e in pool}, 16, 2048, 1024, encoding, DEV)
+    x = syn.activations(SEED + 33, tokens)
+    args = (layer, x.to(DEV), idx.to(DEV), w.to(DEV))
+    inter1, y1 = _stagewise(*args, variant=1)
+    inter2, y2 = _stagewise(*args, variant=2)
+    inter2b, y2b = _stagewise(*args, variant=2)
+    assert torch.equal(y2, y2b) and torch.equal(inter2, inter2b), "two calls must give identical bits"
+    assert_parity(y2.cpu(), y1.cpu(), max_abs=4e-3)
+    mismatch = (inter1 != inter2).float().mean().item()
+    assert mismatch < 1e-3, f"intermediates differ in {mismatch:.2%} of the elements"
+    want = orc.moe_forward(x, idx, w, src, num_experts=64, top_k=2, qwen=False)
+    assert_parity(y2.cpu(), want)
+
+
+def test_large_batch_prefill_matches_the_pair_kernel_and_the_oracle():
+    """4096 tokens x top-8 (32768 routes: every persistent CTA walks many tiles) through umaq_moe_prefill vs the
+    stages run on the CTA-pair kernel; a sample of tokens is checked against the oracle."""
+    src = expert_source(SEED, 5, "olmoe", "q4_group128")
+    tokens, experts = 4096, 16
+    gen = torch.Generator().manual_seed(SEED + 77)
+    popularity = 1.0 / torch.arange(1, experts + 1, dtype=torch.float64) ** 1.1
+    idx = torch.multinomial(popularity.expand(tokens, experts), 8, replacement=False, generator=gen)
+    w = torch.rand((tokens, 8), generator=gen, dtype=torch.float32) / 8
+    layer = stage_layer({e: src(e) for e in range(experts)}, experts, 2048, 1024, "q4_group128", DEV)
+    x = syn.activations(SEED + 34, tokens)
+    y = _run_prefill(layer, x, idx, w)
+    _, y2 = _stagewise(layer, x.to(DEV), idx.to(DEV), w.to(DEV), variant=2)
+    assert_parity(y, y2.cpu(), max_abs=4e-3)
+    sample = torch.arange(0, tokens, 512)
+    want = orc.moe_forward(x[sample], idx[sample], w[sample], src, num_experts=experts, top_k=8, qwen=False)
+    assert_parity(y[sample], want)

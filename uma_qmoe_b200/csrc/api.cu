@@ -154,8 +154,9 @@ int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k
 
 int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows, const int* num_tiles,
                       const int* tile_table, int max_tiles, const float* route_weight, int permute_out, void* out_bf16,
-                      unsigned* status, void* stream) {
-  if (!layer || !act_bf16 || !num_tiles || !tile_table || !out_bf16 || !status || (mode != 0 && mode != 1)) {
+                      unsigned* status, int variant, void* stream) {
+  if (!layer || !act_bf16 || !num_tiles || !tile_table || !out_bf16 || !status || (mode != 0 && mode != 1) ||
+      variant < 0 || variant > 2) {
     set_error("umaq_grouped_gemm: bad argument");
     return ERR_BAD_ARGUMENT;
   }
@@ -169,7 +170,7 @@ int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, l
   g.num_tiles = num_tiles; g.tile_expert = tile_table; g.tile_row0 = tile_table + max_tiles;
   g.tile_rows = tile_table + 2 * max_tiles; g.max_tiles = max_tiles;
   g.out = static_cast<__nv_bfloat16*>(out_bf16); g.out_stride = g.n_rows;
-  g.route_weight = route_weight; g.permute_out = permute_out; g.status = status;
+  g.route_weight = route_weight; g.permute_out = permute_out; g.status = status; g.variant = variant;
   return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
 }
 

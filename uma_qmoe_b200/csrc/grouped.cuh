@@ -41,9 +41,12 @@ struct GroupedGemmArgs {
   const float* route_weight;
   int permute_out;
   unsigned* status;
+  int variant;                // 0: by size; 1: one CTA per tile (grouped.cu); 2: persistent CTA pairs (grouped_pair.cu)
 };
 
-int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);
+int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);        // picks the variant
+int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream);
+int launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream);
 
 // ---- routing (route.cu) ---------------------------------------------------------------------------
 struct RouterArgs {

@@ -1,0 +1,519 @@
+// Grouped-expert GEMMs on CTA pairs: persistent clusters of two CTAs, tcgen05.mma.cta_group::2.
+//
+// Same contract and same tiles as grouped.cu (gate/up + SwiGLU, down x routing weight, over routes
+// sorted by expert; replaces src/uma_qmoe/native/packed_q4_kernel.cu:560-776, :894-1099 and the
+// torch._grouped_mm path of src/uma_qmoe/native_backend.py:958-1005).  It is selected only when the
+// caller asks for it (variant 2): on B200 the quantised encodings run faster on grouped.cu, see the
+// note on pipeline depth below.
+//
+//  * A cluster of two CTAs (two SMs) owns one tile of 256 routes x 256 accumulator columns.  Each CTA
+//    holds 128 of the routes (its half of A) and 128 of the weight rows (its half of B); one
+//    tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16) issued by the even CTA drives both tensor
+//    cores, and each SM reads only A-half + B-half from its shared memory per instruction.
+//  * The 128 x 256 FP32 accumulator per CTA takes 256 tensor-memory columns, so there are two of
+//    them: four epilogue warps drain tile i while the tensor cores work on tile i + 1.
+//  * The kernel is persistent: 74 clusters walk the (row tile, column tile) list round-robin, column
+//    tile fastest, so that the clusters running at the same time share activation rows in L2.  TMA
+//    rings, the conversion warps and the accumulators run across tile boundaries without draining.
+//  * A pipeline step is 128 k deep (two 64-wide swizzle atoms per operand) and has one "full" and one
+//    "free" barrier, because every tcgen05.commit and every barrier hop between the two CTAs costs
+//    several hundred nanoseconds.
+//
+// Synchronisation.  The barriers the MMA issuer waits on (full, acc_empty) live in the even CTA; the
+// odd CTA signals them through the cluster shared-memory window, and its TMA loads complete on them
+// (cp.async.bulk.tensor ... cta_group::2, no multicast).  Barriers released by the tensor core (free,
+// acc_full) exist in both CTAs and are signalled by one multicast tcgen05.commit.  Every wait is
+// bounded; on a timeout the role records ERR_DEVICE_TIMEOUT, stops, and the kernel still passes
+// through the closing cluster barrier and frees its tensor memory.
+//
+// Pipeline depth.  Measured on B200 at 8192 tokens (OLMoE Q4): the barrier round trip commit -> free
+// -> producer -> full -> issuer between two CTAs is about 1.5 us with no work in it, a TMA tile load
+// adds about 1 us; covering that at the tensor rate needs about 110 KB of activation stages plus
+// 90 KB of converted-weight stages per SM, and with the packed codes and scales that does not fit in
+// 227 KB.  With the three steps that fit, the gate/up GEMM runs at 0.66 ms against 0.48 ms for
+// grouped.cu, whose barriers are CTA-local (round trip 0.7 us).
+#include "grouped.cuh"
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc.cuh"
+
+namespace umaq {
+namespace {
+
+constexpr int PM = 128;                 // routes per CTA (256 per pair)
+constexpr int PN = 256;                 // accumulator columns
+constexpr int PK = 128;                 // k per pipeline step: two 64-wide swizzle atoms per operand
+constexpr int kMaxStages = 3;           // ring of {A step, B step} pairs; Q8 has room for 2 (its codes take 32 KiB)
+constexpr int kPS = 2;                  // packed-weight ring (one step each)
+constexpr int kAtom = 128 * 128;        // [128 rows][64 bf16], 128-byte swizzle: 16 KiB
+constexpr int kStepBytes = 2 * kAtom;   // one operand, one step
+constexpr int kPairThreads = 512;       // warps: 0 A TMA, 1 MMA, 2 weight TMA, 3 idle, 4-7 epilogue, 8-15 convert
+constexpr int kPairConvertWarps = 8;
+constexpr int kPairEpilogueWarps = 4;
+constexpr int kPairMaxGroups = 16;
+constexpr int kPairTmemCols = 512;
+constexpr uint32_t kPairInstrDesc =
+    (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+// One tcgen05.commit costs the issuing thread a few hundred cycles, so a step has ONE "full" barrier
+// (activation bytes + converted-weight arrivals) and ONE "free" barrier, and a step is 128 k deep.
+struct PairShared {
+  uint64_t full[kMaxStages], free_[kMaxStages];
+  uint64_t p_full[kPS], p_empty[kPS];
+  uint64_t sc_full[2], sc_empty[2];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// ---- cluster helpers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_id_x() { uint32_t r; asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_count_x() { uint32_t r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t in_cta(const void* local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded like mbar_wait; for barriers that the other CTA of the pair signals
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (global_ns() - t0 > kWaitBudgetNs) return false;
+  }
+}
+// TMA tile load whose completion bytes go to a barrier of either CTA of the pair (no multicast)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// one arrival on the barrier at this shared-memory offset in BOTH CTAs when the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void spin_ns(uint64_t ns) {
+  const uint64_t t0 = global_ns();
+  while (global_ns() - t0 < ns) __nanosleep(200);
+}
+
+struct PairItem {
+  int tile_n, expert, row0, nrows;
+};
+
+template <int ENC, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+grouped_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                    const __grid_constant__ CUtensorMap map_b1, const GroupedParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr bool kQuant = ENC != ENC_BF16;
+  constexpr int kStages = ENC == ENC_Q8 ? 2 : kMaxStages;
+  constexpr int kPackedRow = ENC == ENC_Q4 ? PK / 2 : PK;           // bytes of codes per weight row and step
+  constexpr int kPackedBytes = PM * kPackedRow;
+  uint8_t* sA = smem_raw;                                           // [kStages][2 atoms]
+  uint8_t* sB = sA + kStages * kStepBytes;                          // [kStages][2 atoms], this CTA's 128 weight rows
+  uint8_t* sP = sB + kStages * kStepBytes;                          // [kPS][128 rows][kPackedRow], TMA-swizzled
+  float* sScales = reinterpret_cast<float*>(sP + (kQuant ? kPS * kPackedBytes : 0));   // [2][128 rows][groups]
+  PairShared& sh = *reinterpret_cast<PairShared*>(reinterpret_cast<uint8_t*>(sScales) +
+                                                  (kQuant ? 2 * PM * kPairMaxGroups * 4 : 0));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();              // 0: issues the MMAs and owns the shared barriers
+  const int K = p.k, nk = K / PK, groups = K >> 7;      // one scale group per step
+  const int n_col = p.n_rows / (MODE == 0 ? PN / 2 : PN);
+  const int total = *p.num_tiles * n_col;
+  const int first = (int)cluster_id_x(), step = (int)cluster_count_x();
+  volatile int* abort_flag = &sh.abort_flag;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      // quantised: the A producer's expect_tx + one arrival per conversion warp of both CTAs;
+      // BF16: the expect_tx of the A producer and of the weight producer
+      mbar_init(&sh.full[s], kQuant ? 1 + 2 * kPairConvertWarps : 2);
+      mbar_init(&sh.free_[s], 1);
+    }
+    for (int s = 0; s < kPS; ++s) { mbar_init(&sh.p_full[s], 1); mbar_init(&sh.p_empty[s], kPairConvertWarps); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sh.sc_full[s], 1); mbar_init(&sh.sc_empty[s], kPairConvertWarps);
+      mbar_init(&sh.acc_full[s], 1); mbar_init(&sh.acc_empty[s], 2 * kPairEpilogueWarps);
+    }
+    sh.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&sh.tmem_base, kPairTmemCols);
+    tmem_relinquish_pair();
+  }
+  __syncwarp();
+  tc_fence_before();
+  cluster_sync_all();                                   // both CTAs' barriers and tensor memory exist
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+
+  auto item_of = [&](int it) {
+    PairItem w;
+    const int tile_m = it / n_col;
+    w.tile_n = it - tile_m * n_col;
+    w.expert = p.tile_expert[tile_m]; w.row0 = p.tile_row0[tile_m]; w.nrows = p.tile_rows[tile_m];
+    return w;
+  };
+  // first weight row of this CTA's half of the tile inside the concatenated projection
+  auto weight_row = [&](const PairItem& w) {
+    return (long long)w.expert * p.n_rows + (MODE == 0 ? w.tile_n * (PN / 2) : w.tile_n * PN + (int)rank * PM);
+  };
+  auto fail = [&]() { atomicExch(p.status, (unsigned)ERR_DEVICE_TIMEOUT); *abort_flag = 1; };
+
+  if (warp == 0) {
+    // ===================== activation TMA: this CTA's 128 routes of every step =======================
+    if (lane == 0) {
+      const uint32_t full0 = in_cta(&sh.full[0], 0);
+      uint32_t kidx = 0;
+      for (int it = first; it < total && !*abort_flag; it += step) {
+        const PairItem w = item_of(it);
+        const bool both = w.nrows > PM;                  // otherwise the odd CTA's rows are padding: no load
+        bool ok = true;
+        for (int kc = 0; kc < nk; ++kc, ++kidx) {
+          const uint32_t s = kidx % kStages, use = kidx / kStages;
+          if (use > 0 && !mbar_wait(&sh.free_[s], (use - 1) & 1)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(&sh.full[s], both ? 2 * kStepBytes : kStepBytes);
+          if (rank == 0 || both) {
+            tma_load_2d_pair(sA + s * kStepBytes, &map_a, kc * PK, w.row0 + (int)rank * PM, full0 + s * 8);
+            tma_load_2d_pair(sA + s * kStepBytes + kAtom, &map_a, kc * PK + 64, w.row0 + (int)rank * PM, full0 + s * 8);
+          }
+        }
+        if (!ok) { fail(); break; }
+      }
+      if (*abort_flag) spin_ns(50000);                   // let copies in flight land before the CTA may exit
+    }
+  } else if (warp == 2) {
+    // ===================== weight TMA: scales + packed steps (quantised) or BF16 tiles ===============
+    if (lane == 0) {
+      const CUtensorMap* map_w = (MODE == 0 && rank == 1) ? &map_b1 : &map_b0;
+      const float* scales = (MODE == 0 && rank == 1) ? p.scales1 : p.scales0;
+      const uint32_t full0 = in_cta(&sh.full[0], 0);
+      uint32_t kidx = 0;
+      int seq = 0;
+      for (int it = first; it < total && !*abort_flag; it += step, ++seq) {
+        const PairItem w = item_of(it);
+        const long long wrow = weight_row(w);
+        bool ok = true;
+        if (kQuant) {
+          const int sb = seq & 1;
+          if (seq >= 2 && !mbar_wait(&sh.sc_empty[sb], ((seq >> 1) - 1) & 1)) { fail(); break; }
+          const uint32_t bytes = (uint32_t)PM * groups * 4;
+          mbar_expect_tx(&sh.sc_full[sb], bytes);
+          bulk_g2s(sScales + sb * PM * kPairMaxGroups, scales + wrow * groups, bytes, &sh.sc_full[sb]);
+          for (int kc = 0; kc < nk; ++kc, ++kidx) {
+            const uint32_t s = kidx % kPS, use = kidx / kPS;
+            if (use > 0 && !mbar_wait(&sh.p_empty[s], (use - 1) & 1)) { ok = false; break; }
+            mbar_expect_tx(&sh.p_full[s], kPackedBytes);
+            tma_load_2d(sP + s * kPackedBytes, map_w, kc * kPackedRow, (int)wrow, &sh.p_full[s]);
+          }
+        } else {
+          for (int kc = 0; kc < nk; ++kc, ++kidx) {
+            const uint32_t s = kidx % kStages, use = kidx / kStages;
+            if (use > 0 && !mbar_wait(&sh.free_[s], (use - 1) & 1)) { ok = false; break; }
+            if (rank == 0) mbar_expect_tx(&sh.full[s], 2 * kStepBytes);
+            tma_load_2d_pair(sB + s * kStepBytes, map_w, kc * PK, (int)wrow, full0 + s * 8);
+            tma_load_2d_pair(sB + s * kStepBytes + kAtom, map_w, kc * PK + 64, (int)wrow, full0 + s * 8);
+          }
+        }
+        if (!ok) { fail(); break; }
+      }
+      if (*abort_flag) spin_ns(50000);
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (even CTA only) ================================================
+    if (lane == 0 && rank == 0) {
+      uint32_t kidx = 0;
+      int seq = 0;
+      for (int it = first; it < total && !*abort_flag; it += step, ++seq) {
+        const int buf = seq & 1;
+        if (seq >= 2 && !mbar_wait_cluster(&sh.acc_empty[buf], ((seq >> 1) - 1) & 1)) { fail(); break; }
+        tc_fence_after();
+        const uint32_t acc = tmem + buf * PN;
+        bool ok = true;
+        for (int kc = 0; kc < nk; ++kc, ++kidx) {
+          const uint32_t s = kidx % kStages;
+          ok = mbar_wait_cluster(&sh.full[s], (kidx / kStages) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * kStepBytes), b_addr = smem_u32(sB + s * kStepBytes);
+#pragma unroll
+          for (int k = 0; k < PK / 16; ++k) {
+            const uint32_t off = (k >> 2) * kAtom + (k & 3) * 32;
+            tc_mma_bf16_pair(acc, smem_desc_sw128(a_addr + off), smem_desc_sw128(b_addr + off), kPairInstrDesc,
+                             (kc | k) ? 1u : 0u);
+          }
+          tc_commit_pair(&sh.free_[s]);
+        }
+        if (!ok) { fail(); break; }
+        tc_commit_pair(&sh.acc_full[buf]);
+      }
+    }
+  } else if (warp >= 8) {
+    // ===================== conversion warps: packed codes -> BF16 B step ==============================
+    if (kQuant) {
+      const int ct = tid - 256, row = ct & 127, half = ct >> 7;   // 8 consecutive lanes = 8 consecutive rows
+      const uint32_t full0 = in_cta(&sh.full[0], 0);
+      uint32_t kidx = 0;
+      int seq = 0;
+      for (int it = first; it < total && !*abort_flag; it += step, ++seq) {
+        const int sb = seq & 1;
+        bool ok = mbar_wait(&sh.sc_full[sb], (seq >> 1) & 1);
+        const float* sc = sScales + sb * PM * kPairMaxGroups + row * groups;
+        for (int kc = 0; kc < nk && ok; ++kc, ++kidx) {
+          const uint32_t ps = kidx % kPS, s = kidx % kStages, use = kidx / kStages;
+          ok = mbar_wait(&sh.p_full[ps], (kidx / kPS) & 1);
+          if (ok && use > 0) ok = mbar_wait(&sh.free_[s], (use - 1) & 1);
+          if (!ok) break;
+          const float scale = sc[kc];
+          const uint8_t* src = sP + ps * kPackedBytes + row * kPackedRow;
+          uint8_t* dstrow = sB + s * kStepBytes + half * kAtom + row * 128;   // this thread: 64 k of one row
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t out[16];
+            if (ENC == ENC_Q4) {
+              // 64-byte rows, 64-byte TMA swizzle: 16-byte chunk ^ ((row >> 1) & 3)
+              const int chunk = (half * 2 + h) ^ ((row >> 1) & 3);
+              convert_q4(*reinterpret_cast<const uint4*>(src + chunk * 16), scale, out);
+            } else {
+              // 128-byte rows, 128-byte TMA swizzle
+              const int c0 = (half * 4 + h * 2) ^ (row & 7), c1 = (half * 4 + h * 2 + 1) ^ (row & 7);
+              convert_q8(*reinterpret_cast<const uint4*>(src + c0 * 16), *reinterpret_cast<const uint4*>(src + c1 * 16), scale, out);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int chunk = (h * 4 + i) ^ (row & 7);
+              *reinterpret_cast<uint4*>(dstrow + chunk * 16) = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+            }
+          }
+          fence_proxy_async();                           // generic-proxy writes -> visible to the tensor core
+          __syncwarp();
+          if (lane == 0) {
+            if (rank == 0) mbar_arrive(&sh.full[s]); else mbar_arrive_remote(full0 + s * 8);
+            mbar_arrive(&sh.p_empty[ps]);
+          }
+        }
+        if (!ok) { if (lane == 0) fail(); break; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.sc_empty[sb]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ===================== epilogue warps: drain one accumulator while the other fills ================
+    const int quarter = warp & 3;
+    const uint32_t accempty0 = in_cta(&sh.acc_empty[0], 0);
+    int seq = 0;
+    for (int it = first; it < total && !*abort_flag; it += step, ++seq) {
+      const PairItem w = item_of(it);
+      const int buf = seq & 1;
+      if (!mbar_wait(&sh.acc_full[buf], (seq >> 1) & 1)) { if (lane == 0) fail(); break; }
+      tc_fence_after();
+      const int row = (int)rank * PM + quarter * 32 + lane;     // route row inside the tile
+      const bool valid = row < w.nrows;
+      const long long grow = (long long)w.row0 + row;
+      const uint32_t tbase = tmem + buf * PN + ((uint32_t)(quarter * 32) << 16);
+      if (MODE == 0) {
+        // columns [0, 128) gate, [128, 256) up of features tile_n * 128 ..
+#pragma unroll 1
+        for (int part = 0; part < 4; ++part) {
+          uint32_t g[32], u[32];
+          tmem_ld32(tbase + part * 32, g);
+          tmem_ld32(tbase + PN / 2 + part * 32, u);
+          tmem_ld_wait();
+          if (valid) {
+            __nv_bfloat16* dst = p.out + grow * p.out_stride + w.tile_n * (PN / 2) + part * 32;
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float a = silu_f32(__uint_as_float(g[j])) * __uint_as_float(u[j]);
+              const float b = silu_f32(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]);
+              const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+              o[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            if (p.permute_out) {
+              // natural pairs (f0,f1)(f2,f3)(f4,f5)(f6,f7) -> (f0,f4)(f1,f5)(f2,f6)(f3,f7) per run of 8
+#pragma unroll
+              for (int q8 = 0; q8 < 4; ++q8) {
+                const uint32_t a = o[4 * q8], b = o[4 * q8 + 1], c = o[4 * q8 + 2], d = o[4 * q8 + 3];
+                o[4 * q8] = prmt(a, c, 0x5410); o[4 * q8 + 1] = prmt(a, c, 0x7632);
+                o[4 * q8 + 2] = prmt(b, d, 0x5410); o[4 * q8 + 3] = prmt(b, d, 0x7632);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
+        }
+      } else {
+        const float wr = !valid ? 0.f : (p.route_weight ? p.route_weight[grow] : 1.f);
+#pragma unroll 1
+        for (int part = 0; part < 8; ++part) {
+          uint32_t a[32];
+          tmem_ld32(tbase + part * 32, a);
+          tmem_ld_wait();
+          if (valid) {
+            __nv_bfloat16* dst = p.out + grow * p.out_stride + w.tile_n * PN + part * 32;
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(a[j]) * wr, __uint_as_float(a[j + 1]) * wr);
+              o[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
+        }
+      }
+      tc_fence_before();                                 // the loads above are complete (wait::ld)
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(&sh.acc_empty[buf]); else mbar_arrive_remote(accempty0 + buf * 8);
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  cluster_sync_all();                                    // nobody signals or reads the other CTA after this
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, kPairTmemCols);
+  }
+}
+
+template <int ENC>
+constexpr size_t pair_smem_bytes() {
+  return (size_t)2 * (ENC == ENC_Q8 ? 2 : kMaxStages) * kStepBytes +
+         (ENC == ENC_BF16 ? 0 : (size_t)kPS * PM * (ENC == ENC_Q4 ? PK / 2 : PK) + 2 * PM * kPairMaxGroups * 4) +
+         sizeof(PairShared) + 1024;
+}
+
+template <int ENC, int MODE>
+int launch_pair(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1,
+                cudaStream_t stream) {
+  auto kernel = grouped_pair_kernel<ENC, MODE>;
+  constexpr size_t smem = pair_smem_bytes<ENC>();
+  static thread_local int configured = -1;
+  static thread_local int clusters = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("grouped pair: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+    // how many pairs the device holds at once; the persistent grid is exactly that many clusters
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * sm_count()); cfg.blockDim = dim3(kPairThreads); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+    if (e != cudaSuccess || n <= 0) {
+      set_error("grouped pair: cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      return ERR_LAUNCH;
+    }
+    clusters = n < sm_count() / 2 ? n : sm_count() / 2;
+    configured = dev;
+  }
+  kernel<<<dim3(2 * clusters), kPairThreads, smem, stream>>>(ma, mb0, mb1, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("grouped pair: launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+  return ERR_NONE;
+}
+
+}  // namespace
+
+int launch_grouped_gemm_pair(const GroupedGemmArgs& a, cudaStream_t stream) {
+  const int K = a.k;
+  if (K % 128 || a.n_rows % (a.mode == 0 ? PN / 2 : PN) || a.total_rows <= 0 || a.max_tiles <= 0 ||
+      (a.enc != ENC_BF16 && K > kPairMaxGroups * 128)) {
+    set_error("grouped pair: unsupported shape (k %d, rows per expert %d)", K, a.n_rows);
+    return ERR_BAD_ARGUMENT;
+  }
+  CUtensorMap ma, mb0, mb1;
+  if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.act, (uint64_t)K, (uint64_t)a.total_rows, 64, PM,
+                CU_TENSOR_MAP_SWIZZLE_128B))
+    return ERR_LAUNCH;
+  const uint64_t wrows = (uint64_t)a.num_experts * a.n_rows;
+  const void* w1 = a.mode == 0 ? a.w1 : a.w0;
+  bool ok;
+  if (a.enc == ENC_BF16) {
+    ok = make_map(&mb0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.w0, (uint64_t)K, wrows, 64, PM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+         make_map(&mb1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w1, (uint64_t)K, wrows, 64, PM, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    // one step of codes per box: 64 bytes (Q4) or 128 bytes (Q8) per row, swizzled so that the
+    // conversion warps' 16-byte reads of 8 consecutive rows hit 8 different bank groups
+    const uint64_t rowb = a.enc == ENC_Q4 ? K / 2 : K;
+    const uint32_t boxb = a.enc == ENC_Q4 ? PK / 2 : PK;
+    const CUtensorMapSwizzle swz = a.enc == ENC_Q4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+    ok = make_map(&mb0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w0, rowb, wrows, boxb, PM, swz) &&
+         make_map(&mb1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1, rowb, wrows, boxb, PM, swz);
+  }
+  if (!ok) return ERR_LAUNCH;
+  GroupedParams p{};
+  p.k = K; p.n_rows = a.n_rows;
+  p.scales0 = a.s0; p.scales1 = a.s1;
+  p.num_tiles = a.num_tiles; p.tile_expert = a.tile_expert; p.tile_row0 = a.tile_row0; p.tile_rows = a.tile_rows;
+  p.max_tiles = a.max_tiles;
+  p.out = a.out; p.out_stride = a.out_stride; p.route_weight = a.route_weight; p.permute_out = a.permute_out;
+  p.status = a.status;
+#define UMAQ_DISPATCH(E) return a.mode == 0 ? launch_pair<E, 0>(p, ma, mb0, mb1, stream) : launch_pair<E, 1>(p, ma, mb0, mb1, stream)
+  if (a.enc == ENC_Q4) { UMAQ_DISPATCH(ENC_Q4); }
+  if (a.enc == ENC_Q8) { UMAQ_DISPATCH(ENC_Q8); }
+  if (a.enc == ENC_BF16) { UMAQ_DISPATCH(ENC_BF16); }
+#undef UMAQ_DISPATCH
+  set_error("grouped pair: unknown encoding %d", a.enc);
+  return ERR_BAD_ARGUMENT;
+}
+
+}  // namespace umaq

@@ -226,6 +226,109 @@ __global__ void __launch_bounds__(256) router_tiled_kernel(const RouterArgs a) {
   }
 }
 
+// Tensor-core router for batches (E <= 64, tokens >= 128): a CTA takes 64 tokens and all experts.
+// x and Wr stream through a 3-stage cp.async ring of 128-wide k chunks (16-byte chunks XOR-swizzled by
+// row against bank conflicts); warp (g, h) = (token group of 16, expert half of 32) runs
+// mma.sync.m16n8k16 BF16 with ldmatrix fragments.  The BF16 products are exact in the FP32 accumulator;
+// a chunk's 128 products are summed by the tensor core in float32, the chunk sums in float64, so the
+// BF16 rounding of the logit equals that of an exactly rounded dot product in all but about one logit
+// in 10^4 (the same bound as the tiled kernel).  The logits then go through the same softmax / top-k.
+constexpr int kRmTokens = 64, kRmChunk = 128, kRmStages = 3;
+constexpr int kRmTile = 64 * kRmChunk * 2;                 // 16 KiB: 64 rows x 256 bytes
+constexpr int kRmSmem = kRmStages * 2 * kRmTile;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = smem_u32(dst);
+  const int bytes = valid ? 16 : 0;                        // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+__global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
+  extern __shared__ __align__(128) uint8_t rm_smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int token0 = blockIdx.x * kRmTokens;
+  const int H = a.hidden, E = a.experts, nchunks = H / kRmChunk;
+  const int g = warp >> 1, h = warp & 1;                   // tokens 16g.., experts 32h..
+
+  auto load_chunk = [&](int kc, int stage) {
+    uint8_t* xs = rm_smem + stage * 2 * kRmTile;
+    uint8_t* ws = xs + kRmTile;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int v = tid + i * 256, r = v >> 4, c = v & 15;
+      const int t = token0 + r;
+      const bool ok = t < a.tokens;
+      cp_async16(xs + r * 256 + ((c ^ (r & 7)) << 4), a.x + (size_t)(ok ? t : 0) * H + kc * kRmChunk + c * 8, ok);
+      const bool wok = r < E;
+      cp_async16(ws + r * 256 + ((c ^ (r & 7)) << 4), a.weight + (size_t)(wok ? r : 0) * H + kc * kRmChunk + c * 8, wok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  double acc[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[j][q] = 0.0;
+
+  for (int s = 0; s < kRmStages - 1; ++s) {
+    if (s < nchunks) load_chunk(s, s); else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  // ldmatrix row / chunk of this lane: A = 16 tokens x 16 k, B = 2 n-tiles (16 experts) x 16 k
+  const int a_row = g * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_sel = lane >> 4;
+  const int b_row = h * 32 + (lane & 7) + ((lane >> 4) & 1) * 8, b_sel = (lane >> 3) & 1;
+  for (int kc = 0; kc < nchunks; ++kc) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kRmStages - 2) : "memory");
+    __syncthreads();                                       // chunk kc has landed; chunk kc - 1's buffer is free
+    if (kc + kRmStages - 1 < nchunks) load_chunk(kc + kRmStages - 1, (kc + kRmStages - 1) % kRmStages);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t xs = smem_u32(rm_smem + (kc % kRmStages) * 2 * kRmTile), ws = xs + kRmTile;
+    float part[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) part[j][q] = 0.f;
+#pragma unroll
+    for (int k16 = 0; k16 < kRmChunk / 16; ++k16) {
+      uint32_t a0, a1, a2, a3, b[8];
+      ldmatrix_x4(xs + a_row * 256 + (((k16 * 2 + a_sel) ^ (a_row & 7)) << 4), a0, a1, a2, a3);
+      ldmatrix_x4(ws + b_row * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4), b[0], b[1], b[2], b[3]);
+      ldmatrix_x4(ws + (b_row + 16) * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4), b[4], b[5], b[6], b[7]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) mma_bf16_16816(part[j], a0, a1, a2, a3, b[2 * j], b[2 * j + 1]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[j][q] += (double)part[j][q];
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();                                         // every warp is done with the ring: reuse it for logits
+  float (*logit)[kRtExperts + 1] = reinterpret_cast<float (*)[kRtExperts + 1]>(rm_smem);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = g * 16 + (lane >> 2) + (q >> 1) * 8, e = h * 32 + j * 8 + (lane & 3) * 2 + (q & 1);
+      const float l = bf16_round((float)acc[j][q]);        // F.linear output in BF16
+      logit[r][e] = l;
+      const int t = token0 + r;
+      if (a.out_logits && t < a.tokens && e < E) a.out_logits[(size_t)t * E + e] = __float2bfloat16_rn(l);
+    }
+  __syncthreads();
+  for (int r = warp; r < kRmTokens; r += 8) {
+    const int t = token0 + r;
+    if (t < a.tokens)
+      softmax_topk_warp(logit[r], E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)t * a.top_k,
+                        a.out_indices + (size_t)t * a.top_k);
+  }
+}
+
 // ---- stable expert sort of the routes, one CTA --------------------------------------------------------
 // Route i = token * top_k + slot.  Warp w owns a contiguous chunk of routes; a per-warp histogram and
 // a scan over (expert, warp) give every warp its first position inside each expert's run, and ranks
@@ -495,6 +598,18 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
   if (a.tokens <= 0 || a.hidden % 256 || a.experts < a.top_k || a.top_k < 1 || a.top_k > 32 || a.experts > 1024) {
     set_error("router: unsupported shape (tokens %d, hidden %d, experts %d, top_k %d)", a.tokens, a.hidden, a.experts, a.top_k);
     return ERR_BAD_ARGUMENT;
+  }
+  if (a.experts <= kRtExperts && a.hidden % kRmChunk == 0 && a.tokens >= 128) {
+    static thread_local int configured = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured != dev) {
+      cudaError_t e = cudaFuncSetAttribute(router_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRmSmem);
+      if (e != cudaSuccess) { set_error("router: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+      configured = dev;
+    }
+    router_mma_kernel<<<(a.tokens + kRmTokens - 1) / kRmTokens, 256, kRmSmem, stream>>>(a);
+    return check_launch("router");
   }
   if (a.experts <= kRtExperts && a.hidden % kRtChunk == 0 && a.top_k <= 32) {
     router_tiled_kernel<<<(a.tokens + kRtTokens - 1) / kRtTokens, 256, 0, stream>>>(a);

@@ -1,0 +1,135 @@
+// tcgen05 / TMA / tensor-map helpers shared by the grouped GEMM kernels (grouped.cu, grouped_pair.cu).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace umaq {
+namespace {
+
+// ---- tcgen05 / TMA wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled operand tile whose rows are 128 bytes (64 bf16) and whose 8-row groups
+// are 1024 bytes apart; `addr` must be 1024-byte aligned plus a multiple of 32 bytes along K.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+// ---- conversion of one thread's 32 codes (row r, half h of the 64-wide k chunk) ------------------
+// Q4: 16 bytes -> 16 bf16x2 words in the permuted order, value = code * scale rounded to BF16.
+__device__ __forceinline__ void convert_q4(const uint4 raw, float scale, uint32_t (&out)[16]) {
+  const __nv_bfloat162 s2 = __float2bfloat162_rn(scale);
+  const __nv_bfloat162 off = __float2bfloat162_rn(136.f);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // ((w >> 4i) ^ 8) & 0xF | 0x4300 : bf16 128 + (code + 8) for nibbles i and i + 4
+      const uint32_t m = lop3<0x6A>(w[j] >> (4 * i), 0x000F000Fu, 0x43084308u);
+      __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&m);
+      v = __hmul2(__hsub2(v, off), s2);
+      out[j * 4 + i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+  }
+}
+// Q8: 32 bytes -> 16 bf16x2 words in the permuted order; code * scale in float32, one rounding.
+__device__ __forceinline__ void convert_q8(const uint4 r0, const uint4 r1, float scale, uint32_t (&out)[16]) {
+  const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {       // 8 codes: words 2j (k0..k3) and 2j+1 (k4..k7)
+    const uint32_t a = w[2 * j] ^ 0x80808080u, b = w[2 * j + 1] ^ 0x80808080u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // 0x4B0000xx = float 2^23 + (code + 128)
+      const float lo = __uint_as_float(prmt(a, 0x4B000000u, 0x7650 + i)) - 8388736.f;   // k_i
+      const float hi = __uint_as_float(prmt(b, 0x4B000000u, 0x7650 + i)) - 8388736.f;   // k_{i+4}
+      const __nv_bfloat162 v = __floats2bfloat162_rn(lo * scale, hi * scale);
+      out[j * 4 + i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+  }
+}
+
+// ---- tensor maps ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+bool make_map(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t inner,
+              uint64_t rows, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("grouped: cuTensorMapEncodeTiled is not available"); return false; }
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {inner * (uint64_t)elem_bytes};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("grouped: cuTensorMapEncodeTiled failed with code %d", (int)r); return false; }
+  return true;
+}
+
+}  // namespace
+}  // namespace umaq

@@ -212,8 +212,9 @@ def gather_rows(hidden: torch.Tensor, sorted_route: Optional[torch.Tensor], top_
 
 def grouped_gemm(layer: DeviceLayer, mode: int, act: torch.Tensor, routes: SortedRoutes,
                  route_weight: Optional[torch.Tensor] = None, permute_out: bool = False,
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One grouped GEMM launch (mode 0: gate/up + SwiGLU, mode 1: down * routing weight)."""
+                 out: Optional[torch.Tensor] = None, variant: int = 0) -> torch.Tensor:
+    """One grouped GEMM launch (mode 0: gate/up + SwiGLU, mode 1: down * routing weight).
+    ``variant``: 0/1 the default one-CTA-per-tile kernel, 2 the CTA-pair (cta_group::2) kernel."""
     _require_cuda_bf16(act, "activations")
     n = layer.intermediate if mode == 0 else layer.hidden
     if out is None:
@@ -221,7 +222,7 @@ def grouped_gemm(layer: DeviceLayer, mode: int, act: torch.Tensor, routes: Sorte
     code = _native.lib().umaq_grouped_gemm(
         C.byref(layer.struct()), mode, act.data_ptr(), act.shape[0], routes.num_tiles.data_ptr(),
         routes.tile_table.data_ptr(), routes.max_tiles, route_weight.data_ptr() if route_weight is not None else None,
-        int(permute_out), out.data_ptr(), routes.status.data_ptr(), _stream(act.device))
+        int(permute_out), out.data_ptr(), routes.status.data_ptr(), variant, _stream(act.device))
     _native.check(code, "umaq_grouped_gemm")
     return out
 
