@@ -37,6 +37,12 @@ sys.path.insert(0, str(ROOT))
 SEED = 20260917
 TOKENS, LAYERS = 8192, 16
 DECODE_BYTES = 8 * 3_342_336 + 8_192          # selected experts' codes + scales, x in, y out
+# DRAM bytes per launch from ncu (dram__bytes_read.sum + dram__bytes_write.sum), see profiles/:
+# decode pair 17.88 MB + 9.01 MB measured directly; gate/up GEMM measured at 2048 tokens (196.5 MB read of
+# which 138 MB are the layer's gate/up codes and scales, the rest the gathered activations) and scaled by
+# routes to 8192 tokens: 138 MB weights + 268 MB activations + 134 MB intermediate written.
+DECODE_TRAFFIC_BYTES = 26_886_000
+GEMM_TRAFFIC_BYTES = 540_000_000
 METRIC, UNIT = "prefill_tokens_per_s", "tokens/s"
 
 
@@ -286,7 +292,7 @@ def native_arm(args) -> None:
         flops = 2.0 * xs.shape[0] * shape.hidden * 2 * shape.intermediate
         line["roofline"] = {"bound": "tensor", "kernel": "grouped_gemm_kernel<Q4, gate/up+SwiGLU>",
                             "achieved": flops / (gemm_ms / 1e3) / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": flops / (gemm_ms / 1e3) / 1e12 / pk["bf16_tflops"], "traffic": None,
+                            "frac": flops / (gemm_ms / 1e3) / 1e12 / pk["bf16_tflops"], "traffic": GEMM_TRAFFIC_BYTES,
                             "peak_source": f"{pk_kind} (burst)", "ms_per_launch": gemm_ms,
                             "flops_per_launch": flops}
         # ---- batch-1 decode: the fused kernel over the 16 layers in rotation (428 MB > L2) -----------
@@ -300,12 +306,12 @@ def native_arm(args) -> None:
                 ops.moe_decode(stack.layers[l], xd, routes1[l][1], routes1[l][0], wsd, out=outd)
         dms = timed(graphed(decode_pass), 20, 3, 1) / LAYERS
         line["decode"] = {"metric": "decode_hbm_gbs", "us_per_layer": dms * 1e3,
-                          "roofline": {"bound": "hbm", "kernel": "moe_decode_kernel", "achieved": DECODE_BYTES / (dms / 1e3) / 1e9,
+                          "roofline": {"bound": "hbm", "kernel": "decode_gateup_kernel + decode_down_kernel", "achieved": DECODE_BYTES / (dms / 1e3) / 1e9,
                                        "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                       "frac": DECODE_BYTES / (dms / 1e3) / 1e9 / pk["hbm_gbs"], "traffic": None,
+                                       "frac": DECODE_BYTES / (dms / 1e3) / 1e9 / pk["hbm_gbs"], "traffic": DECODE_TRAFFIC_BYTES,
                                        "peak_source": pk_kind, "bytes_per_launch": DECODE_BYTES},
                           "status": ops.workspace_status(wsd)}
-        line["gpu_launches"] += 13 + 20 * LAYERS + 3 * LAYERS
+        line["gpu_launches"] += 13 + 2 * (20 + 3) * LAYERS      # roofline leg + two decode kernels per layer and pass
         line["cpu_baseline"] = run_cpu(64, 1, 0)
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -1,0 +1,138 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports every symbol the header
+declares, the operator registry mirrors the reference's registry / lease / fail-closed behaviour
+(``src/uma_qmoe/custom_op.py``), and the host codecs agree with the reference-made golden vectors."""
+
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from uma_qmoe_b200 import _native, custom_op, formats
+from uma_qmoe_b200.formats import ContractError
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols() -> list[str]:
+    text = (ROOT / "include" / "umaq_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(umaq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_loads_without_a_gpu_and_exports_every_declared_symbol():
+    lib = _native.lib()
+    declared = _declared_symbols()
+    assert len(declared) >= 14
+    assert sorted(_native.SIGNATURES) == declared, "ctypes table and header must list the same entry points"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/umaq_b200.h but not exported"
+
+
+def test_build_info_names_the_target_and_the_source_digest():
+    from uma_qmoe_b200 import build
+    lib = _native.lib()
+    import ctypes as C
+    raw = C.create_string_buffer(512)
+    n = lib.umaq_build_info(raw, 512)
+    info = raw.value.decode()
+    assert n > 0 and "sm_100a" in info
+    assert len(build.source_sha256()) == 64
+
+
+def test_workspace_sizes_are_host_arithmetic():
+    lib = _native.lib()
+    assert lib.umaq_decode_workspace_bytes(8, 1024, 0) == 1024 + 8 * 1024 * 4
+    assert lib.umaq_decode_workspace_bytes(4, 1408, 5632) == 1024 + (4 * 1408 + 5632) * 4
+    small = lib.umaq_prefill_workspace_bytes(1, 8, 64, 2048, 1024, 0)
+    big = lib.umaq_prefill_workspace_bytes(8192, 8, 64, 2048, 1024, 0)
+    assert 0 < small < big
+    # sorted activations + intermediate + weighted outputs dominate: routes * (H + I + H) * 2 bytes
+    assert big >= 65536 * (2048 + 1024 + 2048) * 2
+
+
+class _Reader:
+    mapping_count = 1
+
+
+def test_registry_handles_leases_and_unregister():
+    with pytest.raises(ContractError, match="exactly one ExpertPack mapping"):
+        custom_op.register_expert_pack(object())
+    handle = custom_op.register_expert_pack(_Reader())
+    other = custom_op.register_target_pack(_Reader())
+    assert other != handle
+    with pytest.raises(RuntimeError, match="active operator lease"):
+        custom_op.expert_pack_for_handle(handle)
+    with custom_op.acquire_expert_pack(handle) as reader:
+        assert isinstance(reader, _Reader)
+        assert custom_op.expert_pack_for_handle(handle) is reader
+        with pytest.raises(ContractError, match="active call"):
+            custom_op.unregister_expert_pack(handle)
+    custom_op.unregister_expert_pack(handle)
+    custom_op.unregister_expert_pack(other)
+    with pytest.raises(RuntimeError, match="unknown or closed ExpertPack handle"):
+        with custom_op.acquire_expert_pack(handle):
+            pass
+
+
+def test_backend_registration_checks_platform_and_callable():
+    with pytest.raises(ContractError, match="unsupported custom operator platform"):
+        custom_op.register_performance_backend("tpu_v5", lambda *a: None)
+    with pytest.raises(ContractError, match="must be callable"):
+        custom_op.register_performance_backend("cuda_sm100", 3)
+
+
+def test_operators_fail_closed_on_cpu_tensors():
+    """No backend is registered for CPU tensors and there is no reference fallback in this package:
+    both operators must raise the reference's fail-closed message instead of computing anything."""
+    custom_op.register_moe_forward()
+    handle = custom_op.register_expert_pack(_Reader())
+    try:
+        x = torch.zeros((1, 2048), dtype=torch.bfloat16)
+        idx = torch.zeros((1, 8), dtype=torch.int64)
+        w = torch.zeros((1, 8), dtype=torch.float32)
+        with pytest.raises(RuntimeError, match="performance mode has no registered cpu backend; "
+                                               "silent reference fallback is forbidden"):
+            torch.ops.uma_qmoe.moe_forward(x, idx, w, 0, handle, True)
+        with pytest.raises(RuntimeError, match="silent reference fallback is forbidden"):
+            torch.ops.uma_qmoe.moe_forward(x, idx, w, 0, handle, False)
+        with pytest.raises(RuntimeError, match="performance mode has no Qwen-capable cpu backend"):
+            torch.ops.uma_qmoe.qwen_moe_forward(x, idx, w, 0, handle, True)
+    finally:
+        custom_op.unregister_expert_pack(handle)
+
+
+def test_operator_schemas_match_the_reference():
+    custom_op.register_moe_forward()
+    want = ("(Tensor hidden_states, Tensor expert_indices, Tensor routing_weights, int layer_index, "
+            "int pack_handle, bool performance_mode=False) -> Tensor")
+    for op in (torch.ops.uma_qmoe.moe_forward, torch.ops.uma_qmoe.qwen_moe_forward):
+        assert str(op.default._schema).endswith(want)
+
+
+def test_product_package_never_imports_the_oracle():
+    for path in (ROOT / "uma_qmoe_b200").rglob("*.py"):
+        text = path.read_text()
+        assert "oracle" not in re.sub(r"#.*", "", text), f"{path} refers to the test oracle"
+
+
+def test_host_codecs_reproduce_the_golden_bytes(golden_dir):
+    """``formats.encode`` (what the native backend's staging and the synthetic packs use) against the
+    reference's own encoders on the four golden inputs (1, 129, 255 and 1000 values)."""
+    g = np.load(golden_dir / "codec.npz")
+    for i in range(4):
+        v = g[f"in_{i}"]
+        q4 = formats.encode(v, "q4_group128")
+        assert bytes(q4.data) == g[f"q4_packed_{i}"].tobytes()
+        assert np.array_equal(np.frombuffer(q4.scales, np.float32), g[f"q4_scales_{i}"])
+        q8 = formats.encode(v, "q8_group128")
+        assert bytes(q8.data) == g[f"q8_data_{i}"].tobytes()
+        assert np.array_equal(np.frombuffer(q8.scales, np.float32), g[f"q8_scales_{i}"])
+        bf = formats.encode(v, "bf16_le")
+        assert bytes(bf.data) == g[f"bf16_{i}"].astype("<u2").tobytes()
+        for packed in (q4, q8, bf):
+            back = formats.decode(packed)
+            assert back.shape == v.shape and np.isfinite(back).all()
+            bound = np.abs(v).max() / (7 if packed is q4 else 127) if packed is not bf else np.abs(v).max() * 2 ** -8
+            assert np.abs(back - v).max() <= bound + 1e-12
