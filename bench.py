@@ -215,8 +215,7 @@ def native_arm(args) -> None:
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=dev)
     shape = syn.OLMOE
-    per = shape.experts // world
-    mine = range(rank * per, (rank + 1) * per)
+    mine = range(rank, shape.experts, world)      # interleaved expert placement (ExpertParallelMoE's default)
     backend = native_backend.install_mixed_target_backend()
     stack = MoEStack.build(shape, "q4_group128", LAYERS, SEED, dev, renormalize=True, skew=1.0, experts=mine)
     share = TOKENS // world
@@ -242,12 +241,14 @@ def native_arm(args) -> None:
         from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE
         eps = [ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k) for layer in stack.layers]
 
+        exchange = {"mode": "gather"}           # all-gather rows, local experts over all tokens, all-to-all partial sums
+
         def run_stack(x):
             for l in range(LAYERS):
                 w, idx = stack.route(l, x)
-                x = rms_renorm(eps[l].forward(x, idx, w))
+                x = rms_renorm(eps[l].forward_gather(x, idx, w))
             return x
-        launches_per_step = LAYERS * 11         # router, sort, gather; on received rows sort, gather, 2 GEMMs, combine; combine
+        launches_per_step = LAYERS * 8          # router; sort (2 kernels), gather, 2 GEMMs, combine over all tokens; sum of the partials
 
     def step_resident():
         run_stack(x_dev)
@@ -260,6 +261,7 @@ def native_arm(args) -> None:
     with ClockSampler(local) as clocks:
         ms = timed(step_resident, args.steps, args.warmup, world)
         ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2), world)
+
     launches = launches_per_step * args.steps
     pk, pk_kind = peaks()
 
@@ -269,6 +271,7 @@ def native_arm(args) -> None:
             "e2e": {"value": TOKENS / (ms_e2e / 1e3), "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2 * world},
             "gpu_launches": launches, "clocks": clocks.summary(),
+            **({"exchange": "all_gather rows + all_to_all partial sums (NCCL)"} if world > 1 else {}),
             "tflops_step": 65536 * 12_582_912 * LAYERS / (ms / 1e3) / 1e12 / world}
 
     if rank == 0 and world == 1:

@@ -182,10 +182,23 @@ int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k
 int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows,
                       const int* num_tiles, const int* tile_table, int max_tiles, const float* route_weight,
                       int permute_out, void* out_bf16, unsigned* status, int variant, void* stream);
+/* Expert-parallel dispatch into fixed-capacity segments, so that the exchange needs no row counts
+ * on the host (no counterpart in the reference, which is single-device).  The routes were sorted by
+ * key = owner_rank * experts_per_rank + local_expert (umaq_route_sort over the keys; offsets is its
+ * [ranks*experts_per_rank + 1] output, sorted_key[s] the key of sorted route s).  Sorted route s of
+ * owner d and rank j among d's routes is written to slot d*capacity + j: its activation row to
+ * send_rows[slot], {local expert, weight bits} to send_meta[slot], slot to route_slot[route].  Unused
+ * slots keep meta -1, which every kernel of this library treats as an absent route; routes beyond
+ * the capacity get route_slot -1 and set *overflow (device int, sticky; the caller then repeats the
+ * layer with exact counts). */
+int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
+                 const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
+                 void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream);
 /* out[t] = BF16 running sum of weighted[route_pos[t*top_k+s]] over the token's routes in
  * ascending expert order: the accumulation order of the reference's CPU path
  * (src/uma_qmoe/custom_op.py:312-338), in place of
- * reduce_topk_route_output_kernel (src/uma_qmoe/native/packed_q4_kernel.cu:1349-1365). */
+ * reduce_topk_route_output_kernel (src/uma_qmoe/native/packed_q4_kernel.cu:1349-1365).
+ * Routes with expert index -1 or route_pos -1 are absent and contribute nothing. */
 int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, int indices_are_int64,
                         const int* route_pos, int tokens, int top_k, int hidden, void* out_bf16, void* stream);
 

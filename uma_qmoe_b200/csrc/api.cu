@@ -149,7 +149,7 @@ int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k
                      int permute, void* out_bf16, void* stream) {
   if (!hidden_bf16 || !out_bf16) { set_error("umaq_gather_rows: null argument"); return ERR_BAD_ARGUMENT; }
   return launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sorted_route, top_k, routes, hidden, permute,
-                            static_cast<__nv_bfloat16*>(out_bf16), static_cast<cudaStream_t>(stream));
+                            static_cast<__nv_bfloat16*>(out_bf16), nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows, const int* num_tiles,
@@ -172,6 +172,20 @@ int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, l
   g.out = static_cast<__nv_bfloat16*>(out_bf16); g.out_stride = g.n_rows;
   g.route_weight = route_weight; g.permute_out = permute_out; g.status = status; g.variant = variant;
   return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
+                 const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
+                 void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream) {
+  if (!hidden_bf16 || !sorted_route || !sorted_key || !sorted_weight || !offsets || !send_rows_bf16 || !send_meta ||
+      !route_slot || !overflow) {
+    set_error("umaq_ep_pack: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  return launch_ep_pack(static_cast<const __nv_bfloat16*>(hidden_bf16), sorted_route, sorted_key, sorted_weight, offsets,
+                        routes, top_k, hidden, ranks, experts_per_rank, capacity,
+                        static_cast<__nv_bfloat16*>(send_rows_bf16), send_meta, route_slot, overflow,
+                        static_cast<cudaStream_t>(stream));
 }
 
 int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, int indices_are_int64, const int* route_pos,
@@ -268,7 +282,9 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, 
   int rc = launch_route_sort(sa, stream);
   if (rc) return rc;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(at(pl.xs));
-  rc = launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sa.sorted_route, top_k, routes, H, quant, xs, stream);
+  // routes with expert id -1 are absent: only the first offsets[E] sorted rows exist
+  rc = launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sa.sorted_route, top_k, routes, H, quant, xs,
+                          sa.offsets + E, stream);
   if (rc) return rc;
 
   GroupedGemmArgs g{};

@@ -79,8 +79,12 @@ int launch_route_sort(const SortArgs& a, cudaStream_t stream);
 int launch_dense_tiles(int rows, int* num_tiles, int* tile_expert, int* tile_row0, int* tile_rows, cudaStream_t stream);
 
 // rows of x gathered into sorted order; `permute` writes each run of 8 as [0,4,1,5,2,6,3,7]
+// valid_rows (device, may be null): only the first *valid_rows sorted routes exist
 int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_k, long long routes, int hidden,
-                       int permute, __nv_bfloat16* out, cudaStream_t stream);
+                       int permute, __nv_bfloat16* out, const int* valid_rows, cudaStream_t stream);
+int launch_ep_pack(const __nv_bfloat16* x, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
+                   const int* offsets, int routes, int top_k, int hidden, int ranks, int per_rank, int capacity,
+                   __nv_bfloat16* send_rows, int* send_meta, int* route_slot, int* overflow, cudaStream_t stream);
 int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
                    int top_k, int hidden, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
                    const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream);

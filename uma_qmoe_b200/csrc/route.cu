@@ -354,6 +354,7 @@ __global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs
   bool bad = false;
   for (long long i = begin + lane; i < end; i += 32) {
     const int e = load_expert(a.indices, a.idx64, i);
+    if (e == -1) continue;                       // an absent route (padding of a fixed-capacity exchange)
     if (e < 0 || e >= E) bad = true; else atomicAdd(&hist[warp][e], 1);
   }
   if (bad) atomicExch(a.status, (unsigned)ERR_BAD_ARGUMENT);
@@ -417,6 +418,7 @@ __global__ void __launch_bounds__(kSortThreads) route_hist_kernel(const SortArgs
   bool bad = false;
   for (long long i = begin + tid; i < end; i += kSortThreads) {
     const int e = load_expert(a.indices, a.idx64, i);
+    if (e == -1) continue;
     if (e < 0 || e >= E) bad = true; else atomicAdd(&hist[e], 1);
   }
   if (bad) atomicExch(a.status, (unsigned)ERR_BAD_ARGUMENT);
@@ -494,9 +496,10 @@ __global__ void __launch_bounds__(kSortThreads) route_place_kernel(const SortArg
 
 // ---- gather: sorted_x[i] = x[sorted_route[i] / top_k], optionally in the permuted K order ------------------
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route, int top_k,
-                                   long long routes, int hidden, int permute, __nv_bfloat16* __restrict__ out) {
+                                   long long routes, int hidden, int permute, __nv_bfloat16* __restrict__ out,
+                                   const int* __restrict__ valid_rows) {
   const long long i = blockIdx.x;
-  if (i >= routes) return;
+  if (i >= routes || (valid_rows && i >= *valid_rows)) return;     // fewer present routes than the launch covers
   const int token = sorted_route ? sorted_route[i] / top_k : (int)i;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)token * hidden);
   uint4* dst = reinterpret_cast<uint4*>(out + (size_t)i * hidden);
@@ -512,6 +515,35 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
   }
 }
 
+// ---- expert-parallel dispatch: rows into fixed-capacity per-destination segments ---------------------------
+// Sorted route s (key = owner * experts_per_rank + local expert) goes to slot owner * capacity + j, j its
+// rank among the routes for that owner.  Slot gets the activation row, meta = {local expert, weight bits};
+// the route remembers its slot for the combine.  Routes beyond the capacity get slot -1 and raise *overflow.
+// The caller pre-fills meta with -1 so that unused slots read as absent routes on the receiving rank.
+__global__ void ep_pack_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route,
+                               const int* __restrict__ sorted_key, const float* __restrict__ sorted_weight,
+                               const int* __restrict__ offsets, int top_k, int hidden, int per_rank, int capacity,
+                               __nv_bfloat16* __restrict__ send_rows, int* __restrict__ send_meta,
+                               int* __restrict__ route_slot, int* __restrict__ overflow) {
+  const int s = blockIdx.x;
+  const int key = sorted_key[s], owner = key / per_rank;
+  const int j = s - offsets[owner * per_rank];
+  const int route = sorted_route[s];
+  if (j >= capacity) {
+    if (threadIdx.x == 0) { route_slot[route] = -1; atomicOr(overflow, 1); }
+    return;
+  }
+  const long long slot = (long long)owner * capacity + j;
+  if (threadIdx.x == 0) {
+    send_meta[2 * slot] = key - owner * per_rank;
+    send_meta[2 * slot + 1] = __float_as_int(sorted_weight[s]);
+    route_slot[route] = (int)slot;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(route / top_k) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(send_rows + (size_t)slot * hidden);
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) dst[v] = src[v];
+}
+
 // ---- combine: ordered BF16 running sum over a token's routes, then the Qwen shared branch -----------------
 // out[t] = (((0 + c_e1) + c_e2) + ...) with e1 < e2 < ... and every partial sum rounded to BF16; the
 // contributions are already BF16 (GEMM 2 epilogue).  With a shared expert: + bf16(sigmoid(bf16(x . wg))
@@ -523,22 +555,27 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
                const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_vec,
                __nv_bfloat16* __restrict__ out) {
   __shared__ int order_pos[8];
+  __shared__ int present;
   __shared__ float red[8];
   __shared__ float gate;
   const int t = blockIdx.x, tid = threadIdx.x;
   if (tid == 0) {
-    int ex[8], ps[8];
+    int ex[8], ps[8], n = 0;
     for (int s = 0; s < top_k; ++s) {
-      ex[s] = load_expert(indices, idx64, (long long)t * top_k + s);
-      ps[s] = route_pos[(long long)t * top_k + s];
+      const int e = load_expert(indices, idx64, (long long)t * top_k + s);
+      if (e == -1) continue;                      // absent route: contributes nothing
+      const int q = route_pos[(long long)t * top_k + s];
+      if (q < 0) continue;                        // route without a row (dropped by a fixed-capacity exchange)
+      ex[n] = e; ps[n] = q; ++n;
     }
-    for (int i = 1; i < top_k; ++i) {           // stable insertion sort by expert
+    for (int i = 1; i < n; ++i) {                 // stable insertion sort by expert
       const int e = ex[i], q = ps[i];
       int j = i - 1;
       while (j >= 0 && ex[j] > e) { ex[j + 1] = ex[j]; ps[j + 1] = ps[j]; --j; }
       ex[j + 1] = e; ps[j + 1] = q;
     }
-    for (int s = 0; s < top_k; ++s) order_pos[s] = ps[s];
+    for (int s = 0; s < n; ++s) order_pos[s] = ps[s];
+    present = n;
   }
   if (shared_out) {
     float acc = 0.f;
@@ -558,7 +595,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
   __syncthreads();
   for (int c = tid * 2; c < hidden; c += 512) {
     float r0 = 0.f, r1 = 0.f;
-    for (int s = 0; s < top_k; ++s) {
+    for (int s = 0; s < present; ++s) {
       const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(weighted + (size_t)order_pos[s] * hidden + c);
       r0 = bf16_round(r0 + __low2float(v));
       r1 = bf16_round(r1 + __high2float(v));
@@ -637,9 +674,9 @@ int launch_route_sort(const SortArgs& a, cudaStream_t stream) {
 }
 
 int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_k, long long routes, int hidden,
-                       int permute, __nv_bfloat16* out, cudaStream_t stream) {
+                       int permute, __nv_bfloat16* out, const int* valid_rows, cudaStream_t stream) {
   if (routes <= 0 || hidden % 8 || routes > 0x7fffffffLL) { set_error("gather: unsupported shape"); return ERR_BAD_ARGUMENT; }
-  gather_rows_kernel<<<(unsigned)routes, 128, 0, stream>>>(x, sorted_route, top_k, routes, hidden, permute, out);
+  gather_rows_kernel<<<(unsigned)routes, 128, 0, stream>>>(x, sorted_route, top_k, routes, hidden, permute, out, valid_rows);
   return check_launch("gather");
 }
 
@@ -649,6 +686,20 @@ int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64
   if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 2) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
   combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, shared_out, x, gate_vec, out);
   return check_launch("combine");
+}
+
+int launch_ep_pack(const __nv_bfloat16* x, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
+                   const int* offsets, int routes, int top_k, int hidden, int ranks, int per_rank, int capacity,
+                   __nv_bfloat16* send_rows, int* send_meta, int* route_slot, int* overflow, cudaStream_t stream) {
+  if (routes <= 0 || hidden % 8 || ranks < 1 || per_rank < 1 || capacity < 1) {
+    set_error("ep pack: unsupported shape");
+    return ERR_BAD_ARGUMENT;
+  }
+  cudaError_t e = cudaMemsetAsync(send_meta, 0xFF, (size_t)ranks * capacity * 8, stream);
+  if (e != cudaSuccess) { set_error("ep pack: memset: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+  ep_pack_kernel<<<routes, 128, 0, stream>>>(x, sorted_route, sorted_key, sorted_weight, offsets, top_k, hidden, per_rank,
+                                             capacity, send_rows, send_meta, route_slot, overflow);
+  return check_launch("ep pack");
 }
 
 }  // namespace umaq

@@ -1,18 +1,35 @@
 """Expert-parallel execution of one MoE layer over the GPUs of one node.
 
-The reference has no multi-GPU code; this mode exists because experts are independent units: rank r
-owns the contiguous experts [r*E/G, (r+1)*E/G) of every layer and a 1/G slice of the tokens.  Per
-layer and rank:
+The reference has no multi-GPU code; this mode exists because experts are independent units: every
+rank owns E/G experts of every layer and a 1/G slice of the tokens.  Placement is ``interleaved``
+(expert e lives on rank e % G as local expert e // G; the default, because routers tend to give
+neighbouring expert ids similar popularity and a contiguous split then overloads one rank) or
+``contiguous`` (rank r owns [r*E/G, (r+1)*E/G)).  Per layer and rank:
 
 1. route the local tokens (fused router kernel);
-2. stable-sort the local routes by global expert id -- which also groups them by destination rank,
-   since ranks own contiguous expert ranges -- and gather the activation rows into that order;
-3. exchange per-rank row counts, then the rows with their local expert id and routing weight
-   (``all_to_all_single`` over NCCL / NVLink);
+2. stable-sort the local routes by the key ``owner * E/G + local id`` -- which groups them by
+   destination rank and, inside a rank, by local expert -- and gather the activation rows into that
+   order;
+3. exchange per-rank row counts, then the rows and one 8-byte record per row (local expert id,
+   routing weight) (``all_to_all_single`` over NCCL / NVLink);
 4. run the grouped-GEMM pipeline on the received rows (each is one route) -> weighted BF16 rows;
 5. send the rows back (the reverse all-to-all) and combine each token's routes in ascending expert
    order with a BF16 running sum -- the same order and roundings as the single-GPU path, so the
    result does not depend on G.
+
+Three exchange schemes share the placement and the kernels:
+
+* :meth:`ExpertParallelMoE.forward` -- exact row counts (one host read per call), routes travel one by
+  one; bit-identical to the single-GPU path for any G.
+* :meth:`ExpertParallelMoE.forward_fixed` -- the same routes in fixed-capacity segments, no host read.
+* :meth:`ExpertParallelMoE.forward_gather` -- for dense routing (top-8 of 64 over a few ranks reaches
+  every rank from almost every token): all-gather the token rows once, every rank runs its own experts
+  over all tokens with the other ranks' routes marked absent (expert id -1, skipped by the sort /
+  gather / combine kernels), and the per-rank partial outputs return through one equal-split
+  all-to-all to be summed per token in rank order.  One row per token crosses NVLink in each direction
+  instead of one per route (4x fewer bytes at G = 2, top-8), and nothing waits on the host.  The sum
+  is a BF16 running sum over ranks of BF16 running sums over each rank's experts: within the path's
+  tolerance of the single-GPU result, not bit-identical to it.
 
 Everything that touches tensors goes through a ``kernels`` object; the default drives the CUDA
 kernels, the CPU tests substitute plain torch functions to exercise the exchange logic over gloo.
@@ -35,11 +52,18 @@ class CudaKernels:
         self.ops = ops
         self.layer = layer                      # DeviceLayer holding only this rank's experts
         self.top_k = top_k
-        self._ws: dict[int, torch.Tensor] = {}
+        self._ws: Optional[torch.Tensor] = None
+        self._ws_rows = 0
+        self._ws_moe: Optional[torch.Tensor] = None
+        self._ws_moe_shape = (0, 0)
 
     def route_sort(self, indices: torch.Tensor, weights: torch.Tensor, num_experts: int):
-        r = self.ops.route_sort(indices, weights, num_experts)
-        return r.counts, r.sorted_route, r.route_pos, r.sorted_weight
+        """-> object with counts, offsets, sorted_route, route_pos, sorted_weight"""
+        return self.ops.route_sort(indices, weights, num_experts)
+
+    def ep_pack(self, x: torch.Tensor, routes: Any, sorted_key: torch.Tensor, top_k: int, ranks: int, per_rank: int,
+                capacity: int, send_rows: torch.Tensor, send_meta: torch.Tensor, overflow: torch.Tensor) -> torch.Tensor:
+        return self.ops.ep_pack(x, routes, sorted_key, top_k, ranks, per_rank, capacity, send_rows, send_meta, overflow)
 
     def gather_rows(self, x: torch.Tensor, sorted_route: torch.Tensor, top_k: int) -> torch.Tensor:
         return self.ops.gather_rows(x, sorted_route, top_k, permute=False)
@@ -48,14 +72,21 @@ class CudaKernels:
         n = rows.shape[0]
         if n == 0:
             return rows
-        ws = self._ws.get(n)
-        if ws is None:
-            self._ws.clear()
-            ws = self._ws[n] = self.ops.prefill_workspace(self.layer, n, 1, None, rows.device)
-        return self.ops.moe_prefill(self.layer, rows, local_expert.view(n, 1), weight.view(n, 1), ws)
+        if self._ws_rows < n:                   # grow-only: the received row count changes every call
+            self._ws_rows = n + n // 4
+            self._ws = self.ops.prefill_workspace(self.layer, self._ws_rows, 1, None, rows.device)
+        return self.ops.moe_prefill(self.layer, rows, local_expert.view(n, 1), weight.view(n, 1), self._ws)
 
     def combine(self, weighted: torch.Tensor, indices: torch.Tensor, route_pos: torch.Tensor) -> torch.Tensor:
         return self.ops.combine_routes(weighted, indices, route_pos)
+
+    def local_moe(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """This rank's experts over all rows of x; local_indices -1 = the route belongs to another rank."""
+        n, top_k = local_indices.shape
+        if self._ws_moe is None or self._ws_moe_shape != (n, top_k):
+            self._ws_moe = self.ops.prefill_workspace(self.layer, n, top_k, None, x.device)
+            self._ws_moe_shape = (n, top_k)
+        return self.ops.moe_prefill(self.layer, x, local_indices, weights, self._ws_moe)
 
 
 @dataclass
@@ -65,7 +96,15 @@ class ExchangePlan:
 
 
 class ExpertParallelMoE:
-    def __init__(self, kernels: Any, num_experts: int, top_k: int, group: Optional[dist.ProcessGroup] = None) -> None:
+    def __init__(self, kernels: Any, num_experts: int, top_k: int, group: Optional[dist.ProcessGroup] = None,
+                 placement: str = "interleaved") -> None:
+        if placement not in ("interleaved", "contiguous"):
+            raise RuntimeError(f"unknown expert placement {placement!r}")
+        self.placement = placement
+        self._keys: Optional[torch.Tensor] = None
+        self._fixed: Optional[tuple] = None
+        self._gather: Optional[tuple] = None
+        self._overflow: Optional[torch.Tensor] = None
         self.kernels = kernels
         self.group = group
         self.world = dist.get_world_size(group)
@@ -75,6 +114,96 @@ class ExpertParallelMoE:
         self.num_experts = num_experts
         self.per_rank = num_experts // self.world
         self.top_k = top_k
+
+    def owned_experts(self, rank: Optional[int] = None) -> range:
+        """Global ids of the experts rank ``rank`` holds, in local-id order."""
+        r = self.rank if rank is None else rank
+        if self.placement == "interleaved":
+            return range(r, self.num_experts, self.world)
+        return range(r * self.per_rank, (r + 1) * self.per_rank)
+
+    def sort_keys(self, indices: torch.Tensor) -> torch.Tensor:
+        """owner * E/G + local id of every selected expert (the identity for contiguous placement)."""
+        if self.placement == "contiguous":
+            return indices
+        if self._keys is None or self._keys.device != indices.device:
+            e = torch.arange(self.num_experts, device=indices.device)
+            self._keys = ((e % self.world) * self.per_rank + e // self.world).to(torch.int64)
+        return self._keys[indices.long()].to(indices.dtype)
+
+    def capacity(self, local_routes: int, factor: float) -> int:
+        """Slots per (source, destination) pair of the fixed-capacity exchange."""
+        mean = -(-local_routes // self.world)
+        cap = min(local_routes, max(128, int(factor * mean)))
+        return -(-cap // 8) * 8
+
+    def overflowed(self) -> bool:
+        """True if any fixed-capacity call since the last query dropped a route (synchronises)."""
+        if self._overflow is None:
+            return False
+        hit = bool(self._overflow.item())
+        self._overflow.zero_()
+        return hit
+
+    def forward_fixed(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                      capacity_factor: float = 2.0, capacity: Optional[int] = None) -> torch.Tensor:
+        """Same result as :meth:`forward` without any host synchronisation: every (source, destination)
+        pair exchanges ``capacity`` slots, unused slots travel as absent routes (expert id -1) and are
+        skipped by the sort / gather / combine kernels.  If a destination gets more than ``capacity``
+        routes from this rank the extra routes are dropped and :meth:`overflowed` reports it; the caller
+        then repeats the step with :meth:`forward`."""
+        k = self.kernels
+        t, top_k = indices.shape
+        routes = t * top_k
+        cap = self.capacity(routes, capacity_factor) if capacity is None else capacity
+        slots = self.world * cap
+        if self._fixed is None or self._fixed[0].shape[0] != slots or self._fixed[0].device != x.device:
+            self._fixed = (x.new_empty((slots, x.shape[1])), torch.empty((slots, 2), dtype=torch.int32, device=x.device),
+                           x.new_empty((slots, x.shape[1])), torch.empty((slots, 2), dtype=torch.int32, device=x.device),
+                           x.new_empty((slots, x.shape[1])))
+            self._overflow = torch.zeros(1, dtype=torch.int32, device=x.device)
+        send_rows, send_meta, recv_rows, recv_meta, back = self._fixed
+        keys = self.sort_keys(indices)
+        r = k.route_sort(keys, weights, self.num_experts)
+        sorted_key = keys.reshape(-1).index_select(0, r.sorted_route.long()).to(torch.int32)
+        route_slot = k.ep_pack(x, r, sorted_key, top_k, self.world, self.per_rank, cap, send_rows, send_meta,
+                               self._overflow)
+        dist.all_to_all_single(recv_rows, send_rows, group=self.group)
+        dist.all_to_all_single(recv_meta, send_meta, group=self.group)
+        done = k.local_experts(recv_rows, recv_meta[:, 0].contiguous(), recv_meta[:, 1].contiguous().view(torch.float32))
+        dist.all_to_all_single(back, done, group=self.group)
+        return k.combine(back, indices, route_slot)
+
+    def local_ids(self, indices: torch.Tensor) -> torch.Tensor:
+        """Local expert id where this rank owns the expert, -1 (absent) elsewhere; int32."""
+        idx = indices.to(torch.int32)
+        if self.placement == "interleaved":
+            mine, local = idx % self.world == self.rank, idx // self.world
+        else:
+            mine, local = idx // self.per_rank == self.rank, idx % self.per_rank
+        return torch.where(mine, local, torch.full_like(local, -1))
+
+    def forward_gather(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """All-gather the rows, run the local experts over all of them, all-to-all the partial sums back."""
+        k = self.kernels
+        t, top_k = indices.shape
+        g = self.world
+        if self._gather is None or self._gather[0].shape[0] != g * t or self._gather[0].device != x.device:
+            self._gather = (x.new_empty((g * t, x.shape[1])),
+                            torch.empty((g * t, 2 * top_k), dtype=torch.int32, device=x.device),
+                            x.new_empty((g * t, x.shape[1])),
+                            torch.arange(g, dtype=torch.int32, device=x.device).repeat(t, 1).contiguous(),
+                            (torch.arange(g, dtype=torch.int32, device=x.device)[None, :] * t +
+                             torch.arange(t, dtype=torch.int32, device=x.device)[:, None]).contiguous())
+        all_x, all_meta, parts, rank_ids, part_pos = self._gather
+        # one record per token: its k expert ids and the bits of its k float32 weights
+        meta = torch.cat((indices.to(torch.int32), weights.contiguous().view(torch.int32)), dim=1)
+        dist.all_gather_into_tensor(all_x, x.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(all_meta, meta, group=self.group)
+        local = self.local_ids(all_meta[:, :top_k])
+        partial = k.local_moe(all_x, local, all_meta[:, top_k:].contiguous().view(torch.float32))
+        dist.all_to_all_single(parts, partial, group=self.group)      # parts[r * t + i] = rank r's sum for my token i
+        return k.combine(parts, rank_ids, part_pos)
 
     def plan(self, counts: torch.Tensor) -> ExchangePlan:
         """Rows this rank sends to / receives from every rank (one small collective + one host read)."""
@@ -92,16 +221,21 @@ class ExpertParallelMoE:
     def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """x [t, H] local tokens, indices/weights [t, k] over the GLOBAL experts -> [t, H]."""
         k = self.kernels
-        counts, sorted_route, route_pos, sorted_weight = k.route_sort(indices, weights, self.num_experts)
-        plan = self.plan(counts)
+        keys = self.sort_keys(indices)
+        r = k.route_sort(keys, weights, self.num_experts)
+        counts, sorted_route, route_pos, sorted_weight = r.counts, r.sorted_route, r.route_pos, r.sorted_weight
+        # queue the device work that does not need the counts before the host waits for them
         send_rows = k.gather_rows(x, sorted_route, self.top_k)
-        # local expert id of every sorted route: global id minus the owner's first expert
-        sorted_expert = indices.reshape(-1).index_select(0, sorted_route.long())
-        local_expert = (sorted_expert % self.per_rank).to(torch.int32)
+        # one record per sorted route: local expert id (key modulo E/G) and the float32 routing weight
+        sorted_key = keys.reshape(-1).index_select(0, sorted_route.long())
+        local_expert = (sorted_key % self.per_rank).to(torch.int32)
+        meta = torch.stack((local_expert, sorted_weight.contiguous().view(torch.int32)), dim=1)
+        plan = self.plan(counts)
         n_recv = sum(plan.recv_counts)
         recv_rows = self._exchange(n_recv, send_rows, plan.recv_counts, plan.send_counts)
-        recv_expert = self._exchange(n_recv, local_expert, plan.recv_counts, plan.send_counts)
-        recv_weight = self._exchange(n_recv, sorted_weight, plan.recv_counts, plan.send_counts)
+        recv_meta = self._exchange(n_recv, meta, plan.recv_counts, plan.send_counts)
+        recv_expert = recv_meta[:, 0].contiguous()
+        recv_weight = recv_meta[:, 1].contiguous().view(torch.float32)
         done = k.local_experts(recv_rows, recv_expert, recv_weight)
         back = self._exchange(send_rows.shape[0], done, plan.send_counts, plan.recv_counts)
         return k.combine(back, indices, route_pos)

@@ -227,6 +227,25 @@ def grouped_gemm(layer: DeviceLayer, mode: int, act: torch.Tensor, routes: Sorte
     return out
 
 
+def ep_pack(hidden: torch.Tensor, routes: SortedRoutes, sorted_key: torch.Tensor, top_k: int, ranks: int,
+            experts_per_rank: int, capacity: int, send_rows: torch.Tensor, send_meta: torch.Tensor,
+            overflow: torch.Tensor) -> torch.Tensor:
+    """Fixed-capacity expert-parallel dispatch (see ``umaq_ep_pack``); returns the slot of every route."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    n = routes.sorted_route.numel()
+    if sorted_key.dtype != torch.int32 or sorted_key.numel() != n:
+        raise RuntimeError("sorted_key must be int32 with one entry per route")
+    if send_rows.shape != (ranks * capacity, hidden.shape[1]) or send_meta.shape != (ranks * capacity, 2):
+        raise RuntimeError("send buffers must hold ranks * capacity slots")
+    route_slot = torch.empty(n, dtype=torch.int32, device=hidden.device)
+    code = _native.lib().umaq_ep_pack(
+        hidden.data_ptr(), routes.sorted_route.data_ptr(), sorted_key.data_ptr(), routes.sorted_weight.data_ptr(),
+        routes.offsets.data_ptr(), n, top_k, hidden.shape[1], ranks, experts_per_rank, capacity, send_rows.data_ptr(),
+        send_meta.data_ptr(), route_slot.data_ptr(), overflow.data_ptr(), _stream(hidden.device))
+    _native.check(code, "umaq_ep_pack")
+    return route_slot
+
+
 def combine_routes(weighted: torch.Tensor, indices: torch.Tensor, route_pos: torch.Tensor,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ordered BF16 top-k combine of per-route weighted outputs."""
