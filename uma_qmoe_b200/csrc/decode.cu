@@ -124,9 +124,10 @@ __device__ __forceinline__ void store_frag4(int enc, uint8_t* xf, int k0, const 
 // memory: every thread sums 32 stored halves with their coefficients, 4 (Q4) or 2 (Q8) neighbouring
 // lanes combine.  Q4: run positions 0,1,4,5 hold x (coefficient 1032), 2,3,6,7 hold x/16 (72 * 16);
 // Q8: every position holds x (1152).
+template <int NT = kThreads>
 __device__ __forceinline__ void build_bias(int enc, const uint8_t* xf, float* bias, int n, int tid) {
   const int chunks = n >> 5;
-  for (int ch = tid; ch < ((chunks + 31) & ~31); ch += kThreads) {
+  for (int ch = tid; ch < ((chunks + 31) & ~31); ch += NT) {
     float sum = 0.f;
     if (ch < chunks) {
       const uint4* src = reinterpret_cast<const uint4*>(xf + (size_t)ch * 64);
@@ -159,7 +160,8 @@ __device__ __forceinline__ float prescale_for(float amax) {
   return __uint_as_float((unsigned)(267 - eb) << 23);        // 2^(14 - (eb - 126))
 }
 
-// max over the CTA; `red` has kWarps floats
+// max over the CTA; `red` has NW floats
+template <int NW = kWarps>
 __device__ __forceinline__ float block_max(float v, float* red, int tid) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -167,7 +169,7 @@ __device__ __forceinline__ float block_max(float v, float* red, int tid) {
   __syncthreads();
   float m = red[0];
 #pragma unroll
-  for (int i = 1; i < kWarps; ++i) m = fmaxf(m, red[i]);
+  for (int i = 1; i < NW; ++i) m = fmaxf(m, red[i]);
   __syncthreads();
   return m;
 }
@@ -185,12 +187,12 @@ template <bool XG>
 __device__ __forceinline__ uint4 load_frag(const uint8_t* p) {
   return XG ? __ldcg(reinterpret_cast<const uint4*>(p)) : *reinterpret_cast<const uint4*>(p);
 }
-template <bool XG>
-__device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4], const uint4 (&rb)[4],
-                                            const uint8_t* const (&xf_lane)[4], bool xvalid, float (&d)[4][4]) {
-  float d0[4][4], d1[4][4];
+template <bool XG, int N = 4>
+__device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[N], const uint4 (&rb)[N],
+                                            const uint8_t* const (&xf_lane)[N], bool xvalid, float (&d)[N][4]) {
+  float d0[N][4], d1[N][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < N; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) d0[i][e] = d1[i][e] = 0.f;
   const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -198,7 +200,7 @@ __device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4]
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < N; ++i) {
         if (i < n) {
           const uint4 x = xvalid ? load_frag<XG>(xf_lane[i] + 16 * j) : zero;
           const uint32_t a = j == 0 ? ra[i].x : j == 1 ? ra[i].y : j == 2 ? ra[i].z : ra[i].w;
@@ -213,7 +215,7 @@ __device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4]
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < N; ++i) {
         if (i < n) {
           const uint4 x = xvalid ? load_frag<XG>(xf_lane[i] + 16 * j) : zero;
           const uint32_t a0 = (j == 0 ? ra[i].x : ra[i].z) ^ 0x80808080u, a1 = (j == 0 ? ra[i].y : ra[i].w) ^ 0x80808080u;
@@ -227,7 +229,7 @@ __device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4]
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < N; ++i) {
       if (i < n) {
         const uint4 x = xvalid ? load_frag<XG>(xf_lane[i]) : zero;
         mma_bf16_16816(d0[i], ra[i].x, rb[i].x, ra[i].y, rb[i].y, x.x, x.y);
@@ -236,9 +238,60 @@ __device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4]
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < N; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) d[i][e] = d0[i][e] + d1[i][e];
+}
+
+// The same for N complete blocks with the encoding fixed at compile time: no per-block predicates, so the
+// compiler emits straight-line LOP3 / HMMA code without convergence barriers around every warp MMA.
+// Two accumulator elements are returned: lo[i] = tile row q, MMA column 2c; hi[i] = tile row q + 8, column 2c
+// (HI = 2) or 2c + 1 (HI = 3).
+template <int ENC, int N, int HI = 2>
+__device__ __forceinline__ void mma_full(const uint4 (&ra)[N], const uint4 (&rb)[N], const uint8_t* const (&xf_lane)[N],
+                                         float (&lo)[N], float (&hi)[N]) {
+  float d0[N][4], d1[N][4];
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) d0[i][e] = d1[i][e] = 0.f;
+  if (ENC == ENC_Q4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const uint4 x = *reinterpret_cast<const uint4*>(xf_lane[i] + 16 * j);
+        const uint32_t a = j == 0 ? ra[i].x : j == 1 ? ra[i].y : j == 2 ? ra[i].z : ra[i].w;
+        const uint32_t b = j == 0 ? rb[i].x : j == 1 ? rb[i].y : j == 2 ? rb[i].z : rb[i].w;
+        const uint32_t ah = a >> 8, bh = b >> 8;
+        mma_f16_16816(d0[i], UMAQ_Q4_LO(a), UMAQ_Q4_LO(b), UMAQ_Q4_HI(a), UMAQ_Q4_HI(b), x.x, x.y);
+        mma_f16_16816(d1[i], UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x.z, x.w);
+      }
+    }
+  } else if (ENC == ENC_Q8) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        const uint4 x = *reinterpret_cast<const uint4*>(xf_lane[i] + 16 * j);
+        const uint32_t a0 = (j == 0 ? ra[i].x : ra[i].z) ^ 0x80808080u, a1 = (j == 0 ? ra[i].y : ra[i].w) ^ 0x80808080u;
+        const uint32_t b0 = (j == 0 ? rb[i].x : rb[i].z) ^ 0x80808080u, b1 = (j == 0 ? rb[i].y : rb[i].w) ^ 0x80808080u;
+        mma_f16_16816(d0[i], prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
+                      prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x.x, x.y);
+        mma_f16_16816(d1[i], prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
+                      prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x.z, x.w);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const uint4 x = *reinterpret_cast<const uint4*>(xf_lane[i]);
+      mma_bf16_16816(d0[i], ra[i].x, rb[i].x, ra[i].y, rb[i].y, x.x, x.y);
+      mma_bf16_16816(d1[i], ra[i].z, rb[i].z, ra[i].w, rb[i].w, x.z, x.w);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) { lo[i] = d0[i][0] + d1[i][0]; hi[i] = d0[i][HI] + d1[i][HI]; }
 }
 
 // ---- fragment records in global memory ------------------------------------------------------------------
@@ -249,21 +302,22 @@ __device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[4]
 __host__ __device__ __forceinline__ int frag_body_bytes(int n) { return n * 2 + (((n >> 6) + 3) & ~3) * 4; }
 __host__ __device__ __forceinline__ size_t frag_record_bytes(int n) { return (size_t)frag_body_bytes(n) + 16; }
 
-// Publishes the record of `n` float values held as vals[j] = value at index tid*4 + j*kThreads*4 + 0..3
-// (a CTA-wide layout); all threads of the CTA call it.  `stage` is frag_body_bytes(n) bytes of shared memory.
-template <int MAXV>
+// Publishes the record of `n` float values held as vals[j] = value at index tid*4 + j*NT*4 + 0..3
+// (a CTA-wide layout of NT threads); all threads of the CTA call it.  `stage` is frag_body_bytes(n) bytes of
+// shared memory.
+template <int MAXV, int NT = kThreads>
 __device__ __forceinline__ void publish_record(int enc, int n, const float (&vals)[MAXV][4], uint8_t* stage,
                                                float* red, uint8_t* dst, int tid) {
   float am = 0.f;
 #pragma unroll
   for (int j = 0; j < MAXV; ++j)
-    if (tid * 4 + j * kThreads * 4 < n)
+    if (tid * 4 + j * NT * 4 < n)
       am = fmaxf(am, fmaxf(fmaxf(fabsf(vals[j][0]), fabsf(vals[j][1])), fmaxf(fabsf(vals[j][2]), fabsf(vals[j][3]))));
-  const float m = block_max(am < 3.0e38f ? am : 0.f, red, tid);
+  const float m = block_max<NT / 32>(am < 3.0e38f ? am : 0.f, red, tid);
   const float sc = prescale_for(m);
 #pragma unroll
   for (int j = 0; j < MAXV; ++j) {
-    const int k0 = tid * 4 + j * kThreads * 4;
+    const int k0 = tid * 4 + j * NT * 4;
     if (k0 < n) {
       const float v[4] = {vals[j][0] * sc, vals[j][1] * sc, vals[j][2] * sc, vals[j][3] * sc};
       store_frag4(enc, stage, k0, v);
@@ -271,82 +325,97 @@ __device__ __forceinline__ void publish_record(int enc, int n, const float (&val
   }
   __syncthreads();
   float* bias = reinterpret_cast<float*>(stage + (size_t)n * 2);
-  build_bias(enc, stage, bias, n, tid);
+  build_bias<NT>(enc, stage, bias, n, tid);
   __syncthreads();
   const int words = frag_body_bytes(n) >> 4;                // 16-byte words of fragments + padded bias
-  for (int i = tid; i < words; i += kThreads) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(stage)[i];
+  for (int i = tid; i < words; i += NT) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(stage)[i];
   if (tid == 0) *reinterpret_cast<float*>(dst + frag_body_bytes(n)) = 1.f / sc;
 }
 
 // =====================================================================================================
-// Kernel A: one CTA = 8 features of one slot: tile rows 0..7 gate rows, 8..15 up rows, all of K = H.
-// The four warps split the 64-byte blocks of the rows; SwiGLU after the cross-warp sum.  The CTA that
-// completes a slot publishes the fragment record of that slot's intermediate vector in place.
+// Kernel A: one CTA = 32 features of one slot = four 16-row tiles (rows 0..7 gate rows, 8..15 up rows
+// of 8 features), all of K = H.  Two warps split the 64-byte blocks of a tile's rows; SwiGLU after the
+// cross-warp sum.  The activation fragments are built once per CTA and serve all four tiles (building
+// them costs about as many instructions as one tile's arithmetic, so a CTA per tile spent three
+// quarters of its instructions there).  Weight blocks stream through two register buffers of two
+// blocks each: the loads of group g + 2 are issued as soon as group g has been multiplied.  The CTA
+// that completes a slot publishes the fragment record of that slot's intermediate vector in place.
 // =====================================================================================================
-__global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const DecodeParams p) {
+constexpr int kWarpsA = 8, kThreadsA = kWarpsA * 32, kTilesA = 4, kSplitA = kWarpsA / kTilesA;
+
+struct BlockPair {
+  uint4 wa[2], wb[2];
+  float sa[2], sb[2];
+};
+
+__global__ void __launch_bounds__(kThreadsA, 2) decode_gateup_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ float red[kWarps * 16];
-  __shared__ float red2[kWarps];
+  __shared__ float red[kWarpsA * 16];
+  __shared__ float red2[kWarpsA];
   __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
   const int H = p.hidden;
   pdl_launch_dependents();
 
-  const int tiles_r = p.inter >> 3, routed = p.top_k * tiles_r;
+  constexpr int kFeat = 8 * kTilesA;                           // features per CTA
+  const int ctas_r = (p.inter + kFeat - 1) / kFeat, routed = p.top_k * ctas_r;
   const bool shared_tile = (int)blockIdx.x >= routed;
-  const int slot = shared_tile ? p.top_k : (int)blockIdx.x / tiles_r;
-  const int f0 = (shared_tile ? (int)blockIdx.x - routed : (int)blockIdx.x % tiles_r) * 8;
+  const int slot = shared_tile ? p.top_k : (int)blockIdx.x / ctas_r;
+  const int islot = shared_tile ? p.shared_inter : p.inter;
+  const int f0 = (shared_tile ? (int)blockIdx.x - routed : (int)blockIdx.x % ctas_r) * kFeat;
+  const int tile = warp / kSplitA, ws = warp % kSplitA;       // this warp: tile `tile`, blocks ws, ws + kSplitA, ...
+  const int ft = f0 + 8 * tile;                                // first feature of the warp's tile
+  const bool live = ft < islot;                                // the last CTA of a slot may have fewer tiles
   const int enc = shared_tile ? ENC_BF16 : p.enc;
   const int rb = row_bytes(enc, H), nblk = rb >> 6, gk = H >> 7;
-  const uint8_t *gate, *up;
+  const uint8_t *gate = nullptr, *up = nullptr;
   const float *gate_s = nullptr, *up_s = nullptr;
   if (shared_tile) {
-    gate = reinterpret_cast<const uint8_t*>(p.sh_gate) + (size_t)f0 * rb;
-    up = reinterpret_cast<const uint8_t*>(p.sh_up) + (size_t)f0 * rb;
+    gate = reinterpret_cast<const uint8_t*>(p.sh_gate) + (size_t)ft * rb;
+    up = reinterpret_cast<const uint8_t*>(p.sh_up) + (size_t)ft * rb;
   } else {
     long long e = load_index(p.idx, p.idx64, slot);
     if (e < 0 || e >= p.experts) {
       if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);
       return;
     }
-    const size_t row = (size_t)e * p.inter + f0;
+    const size_t row = (size_t)e * p.inter + ft;
     gate = p.gate + row * rb; up = p.up + row * rb;
     if (enc != ENC_BF16) { gate_s = p.gate_s + row * gk; up_s = p.up_s + row * gk; }
   }
 
-  // this warp's blocks: warp, warp+4, ...; groups of four are loaded, then multiplied
-  const int bpw = (nblk - warp + kWarps - 1) / kWarps;
-  uint4 wa[4], wb[4];
-  float sa[4], sb[4];
-  auto issue = [&](int first) {
+  const int bpw = live ? (nblk - ws + kSplitA - 1) / kSplitA : 0;
+  auto issue = [&](BlockPair& b, int first) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int kb = warp + (first + i) * kWarps;
+    for (int i = 0; i < 2; ++i) {
+      const int kb = ws + (first + i) * kSplitA;
       if (first + i < bpw) {
-        wa[i] = ldg_stream(gate + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
-        wb[i] = ldg_stream(up + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
+        b.wa[i] = ldg_stream(gate + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
+        b.wb[i] = ldg_stream(up + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
         if (enc != ENC_BF16) {
           const int g = enc == ENC_Q4 ? kb : (kb >> 1);
-          sa[i] = gate_s[q * gk + g];
-          sb[i] = up_s[q * gk + g];
+          b.sa[i] = gate_s[q * gk + g];
+          b.sb[i] = up_s[q * gk + g];
         }
       }
     }
   };
-  issue(0);                             // weights are in flight while the activation fragments are built
+  BlockPair b0, b1;
+  issue(b0, 0);                         // weights are in flight while the activation fragments are built
+  issue(b1, 2);
 
   // ---- x -> fragments in shared memory (quantised rows: prescaled fp16 + bias sums; BF16 rows: x as is) ---
   uint8_t* xf = smem;
   float* bias = reinterpret_cast<float*>(smem + (size_t)H * 2);
   float x_inv = 1.f;
   {
-    constexpr int kMaxV = 4;                                 // hidden <= 4 * 512 * ... handled in passes
-    for (int base = 0; base < H; base += kMaxV * kThreads * 4) {
+    constexpr int kMaxV = 2;                                 // hidden <= 2 * 256 * 4 in one pass
+    for (int base = 0; base < H; base += kMaxV * kThreadsA * 4) {
       float vals[kMaxV][4];
       float am = 0.f;
 #pragma unroll
       for (int j = 0; j < kMaxV; ++j) {
-        const int k0 = base + tid * 4 + j * kThreads * 4;
+        const int k0 = base + tid * 4 + j * kThreadsA * 4;
         vals[j][0] = vals[j][1] = vals[j][2] = vals[j][3] = 0.f;
         if (k0 < H) {
           const uint2 raw = *reinterpret_cast<const uint2*>(p.x + k0);
@@ -359,12 +428,12 @@ __global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const Decode
       if (enc != ENC_BF16) {
         // hidden sizes up to 2048 are one pass, so the block maximum is the vector maximum; wider
         // vectors would need the maximum over all passes first
-        sx = prescale_for(block_max(am < 3.0e38f ? am : 0.f, red2, tid));
+        sx = prescale_for(block_max<kWarpsA>(am < 3.0e38f ? am : 0.f, red2, tid));
         x_inv = 1.f / sx;
       }
 #pragma unroll
       for (int j = 0; j < kMaxV; ++j) {
-        const int k0 = base + tid * 4 + j * kThreads * 4;
+        const int k0 = base + tid * 4 + j * kThreadsA * 4;
         if (k0 < H) {
           const float v[4] = {vals[j][0] * sx, vals[j][1] * sx, vals[j][2] * sx, vals[j][3] * sx};
           store_frag4(enc, xf, k0, v);
@@ -372,39 +441,58 @@ __global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const Decode
       }
     }
     __syncthreads();
-    if (enc != ENC_BF16) { build_bias(enc, xf, bias, H, tid); __syncthreads(); }
+    if (enc != ENC_BF16) { build_bias<kThreadsA>(enc, xf, bias, H, tid); __syncthreads(); }
   }
   const int fb = frag_block_bytes(enc);
   float acc_lo = 0.f, acc_hi = 0.f;
-  for (int first = 0; first < bpw; first += 4) {
-    if (first) issue(first);
-    const int n = min(4, bpw - first);
-    const uint8_t* xp[4];
-    float bs[4];
+  auto multiply = [&](const BlockPair& b, int first) {
+    const int n = min(2, bpw - first);
+    const uint8_t* xp[2];
+    float bs[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int kb = warp + (first + min(i, n - 1)) * kWarps;
+    for (int i = 0; i < 2; ++i) {
+      const int kb = ws + (first + min(i, n - 1)) * kSplitA;
       xp[i] = xf + (size_t)kb * fb + c * (fb >> 2);
       bs[i] = enc == ENC_BF16 ? 0.f : bias[kb];
     }
-    float d[4][4];
-    mma_blocks4<false>(enc, n, wa, wb, xp, true, d);
+    if (n == 2) {                        // complete pair: straight-line code per encoding
+      float lo[2], hi[2];
+      if (enc == ENC_Q4) mma_full<ENC_Q4, 2>(b.wa, b.wb, xp, lo, hi);
+      else if (enc == ENC_Q8) mma_full<ENC_Q8, 2>(b.wa, b.wb, xp, lo, hi);
+      else mma_full<ENC_BF16, 2>(b.wa, b.wb, xp, lo, hi);
+      if (enc == ENC_BF16) { acc_lo += lo[0] + lo[1]; acc_hi += hi[0] + hi[1]; }
+      else {
+        acc_lo = fmaf(b.sa[0], lo[0] - bs[0], acc_lo); acc_hi = fmaf(b.sb[0], hi[0] - bs[0], acc_hi);
+        acc_lo = fmaf(b.sa[1], lo[1] - bs[1], acc_lo); acc_hi = fmaf(b.sb[1], hi[1] - bs[1], acc_hi);
+      }
+      return;
+    }
+    float d[2][4];
+    mma_blocks4<false, 2>(enc, n, b.wa, b.wb, xp, true, d);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       if (i < n) {
         if (enc == ENC_BF16) { acc_lo += d[i][0]; acc_hi += d[i][2]; }
-        else { acc_lo = fmaf(sa[i], d[i][0] - bs[i], acc_lo); acc_hi = fmaf(sb[i], d[i][2] - bs[i], acc_hi); }
+        else { acc_lo = fmaf(b.sa[i], d[i][0] - bs[i], acc_lo); acc_hi = fmaf(b.sb[i], d[i][2] - bs[i], acc_hi); }
       }
+    }
+  };
+  for (int first = 0; first < bpw; first += 4) {
+    multiply(b0, first);
+    if (first + 4 < bpw) issue(b0, first + 4);
+    if (first + 2 < bpw) {
+      multiply(b1, first + 2);
+      if (first + 6 < bpw) issue(b1, first + 6);
     }
   }
   if (c == 0) { red[warp * 16 + q] = acc_lo; red[warp * 16 + 8 + q] = acc_hi; }
   __syncthreads();
-  const int islot = shared_tile ? p.shared_inter : p.inter;
   const int ioff = shared_tile ? p.top_k * p.inter : slot * p.inter;
-  if (tid < 8) {
+  if (tid < kFeat && f0 + tid < islot) {
+    const int t = tid >> 3, j = tid & 7;
     float g = 0.f, u = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) { g += red[w * 16 + tid]; u += red[w * 16 + 8 + tid]; }
+    for (int w = 0; w < kSplitA; ++w) { g += red[(t * kSplitA + w) * 16 + j]; u += red[(t * kSplitA + w) * 16 + 8 + j]; }
     float v;
     if (shared_tile) {                  // Qwen2MoeMLP in BF16: every linear / activation output is rounded
       g = bf16_round(g); u = bf16_round(u);
@@ -421,18 +509,18 @@ __global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const Decode
   if (tid == 0) {
     __threadfence();
     const unsigned done = atomicAdd(p.amax + slot, 1u);
-    const unsigned tiles = (unsigned)(islot >> 3);
-    s_last = (done == tiles - 1);
+    const unsigned ctas = (unsigned)((islot + kFeat - 1) / kFeat);
+    s_last = (done == ctas - 1);
     if (s_last) { atomicExch(p.amax + slot, 0u); __threadfence(); }
   }
   __syncthreads();
   if (!s_last) return;
   const int enc_b = shared_tile ? ENC_BF16 : p.enc;          // encoding of the down rows that read it
-  constexpr int kMaxV = 12;                                  // intermediate size <= 12 * 512
+  constexpr int kMaxV = 6;                                   // intermediate size <= 6 * 1024
   float vals[kMaxV][4];
 #pragma unroll
   for (int j = 0; j < kMaxV; ++j) {
-    const int k0 = tid * 4 + j * kThreads * 4;
+    const int k0 = tid * 4 + j * kThreadsA * 4;
     vals[j][0] = vals[j][1] = vals[j][2] = vals[j][3] = 0.f;
     if (k0 < islot) {
       const float4 f = __ldcg(reinterpret_cast<const float4*>(p.inter_buf + ioff + k0));
@@ -444,11 +532,11 @@ __global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const Decode
   if (enc_b == ENC_BF16) {
 #pragma unroll
     for (int j = 0; j < kMaxV; ++j) {
-      const int k0 = tid * 4 + j * kThreads * 4;
+      const int k0 = tid * 4 + j * kThreadsA * 4;
       if (k0 < islot) store_frag4(ENC_BF16, dst, k0, vals[j]);
     }
   } else {
-    publish_record<kMaxV>(enc_b, islot, vals, smem, red2, dst, tid);
+    publish_record<kMaxV, kThreadsA>(enc_b, islot, vals, smem, red2, dst, tid);
   }
 }
 
@@ -456,7 +544,16 @@ __global__ void __launch_bounds__(kThreads, 4) decode_gateup_kernel(const Decode
 // Kernel B: one CTA = 8 output rows.  Slots are walked in ascending expert order, two per MMA tile
 // (tile rows 0..7: row n0+q of the first slot, rows 8..15: the same row of the second; the slots'
 // intermediate vectors are MMA columns 0 and 1).  The Qwen shared expert is a last, half-filled tile.
+// A warp owns the 64-byte blocks warp, warp + 4, ... of every tile and walks (tile, pair of blocks)
+// through four register buffers: their loads go out before griddepcontrol.wait, and every buffer is
+// refilled as soon as it has been multiplied.
 // =====================================================================================================
+struct DownTile {
+  const uint8_t* wa; const uint8_t* wb;        // row n0 + q of the two slots' experts (wb null: no second slot)
+  const float* sa; const float* sb;            // their scale rows
+  int rec_a, rec_b;                            // byte offsets of the slots' records in shared memory
+};
+
 __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_order[kMaxSlots];
@@ -467,6 +564,7 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
   __shared__ float s_tmp[kWarps];
   __shared__ float s_gate;
   __shared__ int s_bad;
+  __shared__ __align__(16) uint8_t s_zero[256];         // fragment block of the lanes that feed no MMA column
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
   const int H = p.hidden, I = p.inter, S = p.sh_gate ? p.shared_inter : 0;
   const int n0 = blockIdx.x * 8;
@@ -479,6 +577,7 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
 
   // ---- routes: order by expert (stable), shared expert last ----------------------------------------------
   if (tid == 0) s_bad = 0;
+  if (tid < 64) reinterpret_cast<uint32_t*>(s_zero)[tid] = 0u;
   __syncthreads();
   if (tid < p.top_k) {
     const long long e = load_index(p.idx, p.idx64, tid);
@@ -501,30 +600,89 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
   const int rb = row_bytes(enc, I), nblk = rb >> 6, gk = I >> 7;
   const int rtiles = (p.top_k + 1) >> 1;
   const int bpw = (nblk - warp + kWarps - 1) / kWarps;           // blocks of a routed tile this warp owns
-  const int items = rtiles * bpw;                                // (tile, block) items of this warp
-  constexpr int kUp = 8;                                         // items whose loads go out before the wait
-  uint4 wa[kUp], wb[kUp];
-  float sa[kUp], sb[kUp];
-  auto issue_routed = [&](int first) {
+  const int ppw = (bpw + 1) >> 1;                                // pairs of blocks per tile
+  const int npairs = rtiles * ppw;
+  const int fb = frag_block_bytes(enc);
+  auto tile_of = [&](int t) {
+    DownTile d;
+    const int a = s_order[2 * t], b = 2 * t + 1 < p.top_k ? s_order[2 * t + 1] : -1;
+    const size_t ra = (size_t)s_expert[a] * H + n0 + q;
+    d.wa = p.down + ra * rb + (c << 4);
+    d.sa = enc != ENC_BF16 ? p.down_s + ra * gk : nullptr;
+    d.rec_a = a * rec;
+    if (b >= 0) {
+      const size_t rbw = (size_t)s_expert[b] * H + n0 + q;
+      d.wb = p.down + rbw * rb + (c << 4);
+      d.sb = enc != ENC_BF16 ? p.down_s + rbw * gk : nullptr;
+      d.rec_b = b * rec;
+    } else { d.wb = nullptr; d.sb = nullptr; d.rec_b = d.rec_a; }
+    return d;
+  };
+  // (tile, first block of the pair) walked in order; one iterator for the loads, one for the arithmetic
+  struct Walk { int t, first, left; };
+  auto advance = [&](Walk& w) { w.first += 2; if (w.first >= bpw) { w.first = 0; ++w.t; } --w.left; };
+  auto issue = [&](BlockPair& b, const Walk& w) {
+    if (w.left <= 0) return;
+    const DownTile d = tile_of(w.t);
 #pragma unroll
-    for (int i = 0; i < kUp; ++i) {
-      const int it = first + i;
-      if (it < items) {
-        const int t = it / bpw, kb = warp + (it - t * bpw) * kWarps;
-        const int a = s_order[2 * t], b = 2 * t + 1 < p.top_k ? s_order[2 * t + 1] : -1;
-        const size_t ra = ((size_t)s_expert[a] * H + n0 + q);
-        wa[i] = ldg_stream(p.down + ra * rb + ((size_t)kb << 6) + (c << 4));
+    for (int i = 0; i < 2; ++i) {
+      if (w.first + i < bpw) {
+        const int kb = warp + (w.first + i) * kWarps;
         const int g = enc == ENC_Q4 ? kb : (kb >> 1);
-        if (enc != ENC_BF16) sa[i] = p.down_s[ra * gk + g];
-        if (b >= 0) {
-          const size_t rbw = ((size_t)s_expert[b] * H + n0 + q);
-          wb[i] = ldg_stream(p.down + rbw * rb + ((size_t)kb << 6) + (c << 4));
-          if (enc != ENC_BF16) sb[i] = p.down_s[rbw * gk + g];
-        } else { wb[i] = make_uint4(0, 0, 0, 0); sb[i] = 0.f; }
+        b.wa[i] = ldg_stream(d.wa + ((size_t)kb << 6));
+        if (enc != ENC_BF16) b.sa[i] = d.sa[g];
+        if (d.wb) {
+          b.wb[i] = ldg_stream(d.wb + ((size_t)kb << 6));
+          if (enc != ENC_BF16) b.sb[i] = d.sb[g];
+        } else { b.wb[i] = make_uint4(0, 0, 0, 0); b.sb[i] = 0.f; }
       }
     }
   };
-  issue_routed(0);                      // weights do not depend on kernel A: in flight before the wait
+  float acc_lo = 0.f, acc_hi = 0.f;
+  auto multiply = [&](const BlockPair& b, const Walk& w) {
+    const DownTile d = tile_of(w.t);
+    const int n = min(2, bpw - w.first);
+    const uint8_t* xp[2];
+    float bsa[2], bsb[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int kb = warp + (w.first + min(i, n - 1)) * kWarps;
+      // MMA column 0 <- first slot's vector (lanes of quad 0), column 1 <- second slot's (quad 1), others zero
+      const uint8_t* base = q == 0 ? recs + d.rec_a : recs + d.rec_b;
+      xp[i] = q < 2 ? base + (size_t)kb * fb + c * (fb >> 2) : s_zero + c * (fb >> 2);
+      if (enc != ENC_BF16) {
+        bsa[i] = reinterpret_cast<const float*>(recs + d.rec_a + (size_t)I * 2)[kb];
+        bsb[i] = reinterpret_cast<const float*>(recs + d.rec_b + (size_t)I * 2)[kb];
+      } else { bsa[i] = bsb[i] = 0.f; }
+    }
+    float lo[2], hi[2];
+    if (n == 2) {
+      if (enc == ENC_Q4) mma_full<ENC_Q4, 2, 3>(b.wa, b.wb, xp, lo, hi);
+      else if (enc == ENC_Q8) mma_full<ENC_Q8, 2, 3>(b.wa, b.wb, xp, lo, hi);
+      else mma_full<ENC_BF16, 2, 3>(b.wa, b.wb, xp, lo, hi);
+    } else {
+      float dd[2][4];
+      mma_blocks4<false, 2>(enc, n, b.wa, b.wb, xp, true, dd);
+      lo[0] = dd[0][0]; hi[0] = dd[0][3]; lo[1] = hi[1] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (i < n) {
+        if (enc == ENC_BF16) { acc_lo += lo[i]; acc_hi += hi[i]; }
+        else { acc_lo = fmaf(b.sa[i], lo[i] - bsa[i], acc_lo); acc_hi = fmaf(b.sb[i], hi[i] - bsb[i], acc_hi); }
+      }
+    }
+    if (w.first + 2 >= bpw) {              // last pair of the tile for this warp: park the partial sums
+      if (c == 0) { s_red[w.t][warp][q] = acc_lo; s_red[w.t][warp][8 + q] = acc_hi; }
+      acc_lo = acc_hi = 0.f;
+    }
+  };
+  Walk wi{0, 0, npairs}, wm{0, 0, npairs};
+  BlockPair b0, b1, b2, b3;
+  issue(b0, wi); advance(wi);            // weights do not depend on kernel A: in flight before the wait
+  issue(b1, wi); advance(wi);
+  issue(b2, wi); advance(wi);
+  issue(b3, wi); advance(wi);
 
   // sigmoid gate of the shared expert: bf16(sigmoid(bf16(x . wg)))
   if (S) {
@@ -563,52 +721,12 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
   }
   __syncthreads();
 
-  // ---- routed tiles: groups of four (tile, block) items, eight MMA chains in flight ------------------------
-  const int fb = frag_block_bytes(enc);
-  float acc_lo = 0.f, acc_hi = 0.f;
-  for (int first = 0; first < items; first += kUp) {
-    if (first) issue_routed(first);
-#pragma unroll
-    for (int g4 = 0; g4 < kUp; g4 += 4) {
-      if (first + g4 < items) {
-        const int n = min(4, items - first - g4);
-        const uint8_t* xp[4];
-        float bsa[4], bsb[4];
-        int tl[4], jl[4];
-        uint4 ga[4], gb[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int it = first + g4 + min(i, n - 1);
-          const int t = it / bpw, j = it - t * bpw, kb = warp + j * kWarps;
-          const int a = s_order[2 * t], b = 2 * t + 1 < p.top_k ? s_order[2 * t + 1] : a;
-          // MMA column 0 <- first slot's vector (lanes of quad 0), column 1 <- second slot's (quad 1)
-          const uint8_t* base = recs + (size_t)(q == 0 ? a : b) * rec;
-          xp[i] = base + (size_t)kb * fb + c * (fb >> 2);
-          if (enc != ENC_BF16) {
-            bsa[i] = reinterpret_cast<const float*>(recs + (size_t)a * rec + (size_t)I * 2)[kb];
-            bsb[i] = reinterpret_cast<const float*>(recs + (size_t)b * rec + (size_t)I * 2)[kb];
-          } else { bsa[i] = bsb[i] = 0.f; }
-          tl[i] = t; jl[i] = j;
-          ga[i] = wa[g4 + i]; gb[i] = wb[g4 + i];
-        }
-        float d[4][4];
-        mma_blocks4<false>(enc, n, ga, gb, xp, q < 2, d);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          if (i < n) {
-            if (enc == ENC_BF16) { acc_lo += d[i][0]; acc_hi += d[i][3]; }
-            else {
-              acc_lo = fmaf(sa[g4 + i], d[i][0] - bsa[i], acc_lo);
-              acc_hi = fmaf(sb[g4 + i], d[i][3] - bsb[i], acc_hi);
-            }
-            if (jl[i] == bpw - 1) {        // last block of the tile for this warp: park the partial sums
-              if (c == 0) { s_red[tl[i]][warp][q] = acc_lo; s_red[tl[i]][warp][8 + q] = acc_hi; }
-              acc_lo = acc_hi = 0.f;
-            }
-          }
-        }
-      }
-    }
+  // ---- routed tiles: pairs of blocks through the four buffers, four MMA chains per pair ---------------------
+  while (wm.left > 0) {
+    multiply(b0, wm); advance(wm); issue(b0, wi); advance(wi);
+    if (wm.left > 0) { multiply(b1, wm); advance(wm); issue(b1, wi); advance(wi); }
+    if (wm.left > 0) { multiply(b2, wm); advance(wm); issue(b2, wi); advance(wi); }
+    if (wm.left > 0) { multiply(b3, wm); advance(wm); issue(b3, wi); advance(wi); }
   }
   if (bpw == 0 && c == 0)
     for (int t = 0; t < rtiles; ++t) { s_red[t][warp][q] = 0.f; s_red[t][warp][8 + q] = 0.f; }
@@ -703,9 +821,10 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
     return ERR_UNSUPPORTED;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kThreadsA);
   cfg.stream = stream;
-  cfg.gridDim = dim3(p.top_k * (p.inter / 8) + (p.sh_gate ? p.shared_inter / 8 : 0));
+  constexpr int kFeat = 8 * kTilesA;
+  cfg.gridDim = dim3(p.top_k * ((p.inter + kFeat - 1) / kFeat) + (p.sh_gate ? (p.shared_inter + kFeat - 1) / kFeat : 0));
   cfg.dynamicSmemBytes = smem_a;
   cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gateup_kernel, p);
   if (e != cudaSuccess) { set_error("decode: gate/up launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
@@ -716,6 +835,7 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  cfg.blockDim = dim3(kThreads);
   cfg.gridDim = dim3((p.hidden + 7) / 8);
   cfg.dynamicSmemBytes = smem_b;
   e = cudaLaunchKernelEx(&cfg, decode_down_kernel, p);

@@ -282,55 +282,76 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (ok) ok = mbar_wait(&sh.acc_full, seq & 1);
       if (!ok) { if (lane == 0) fail(); break; }
       tc_fence_after();
+      // The accumulator reads are software-pipelined: the tcgen05.ld of chunk c + 1 is in flight while chunk c
+      // is converted and stored, and the accumulators are handed back to the MMA issuer as soon as the last
+      // chunk is in registers, before its arithmetic and stores.
       const int quarter = warp & 3, ch = (warp - 2) >> 2;
-      for (int half = 0; half < (two ? 2 : 1); ++half) {
-        const int row = half * BM + quarter * 32 + lane;   // route row inside the tile
-        const uint32_t tbase = tmem + half * BN + ((uint32_t)(quarter * 32) << 16);
-        const bool valid = row < t.nrows;
-        const long long grow = (long long)t.row0 + row;
-        if (MODE == 0) {
-          // columns [0, BN/2) gate, [BN/2, BN) up; this warp: features ch*64 .. ch*64+63 in two parts
+      const int nchunks = two ? 8 : 4;                   // per warp: {half 0, half 1} x 4 chunks
+      const uint32_t tq = tmem + ((uint32_t)(quarter * 32) << 16);
+      auto release = [&]() {
+        tc_fence_before();                               // every tcgen05.ld of this tile is complete (wait::ld)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.acc_empty);
+      };
+      if (MODE == 0) {
+        // columns [0, BN/2) gate, [BN/2, BN) up; this warp: features ch*64 .. ch*64+63, 16 per chunk
+        uint32_t g[2][16], u[2][16];
+        tmem_ld16(tq + ch * 64, g[0]);
+        tmem_ld16(tq + BN / 2 + ch * 64, u[0]);
 #pragma unroll
-          for (int part = 0; part < 2; ++part) {
-            uint32_t g[32], u[32];
-            const int c0 = ch * 64 + part * 32;
-            tmem_ld32(tbase + c0, g);
-            tmem_ld32(tbase + BN / 2 + c0, u);
+        for (int c = 0; c < 8; ++c) {
+          if (c < nchunks) {
             tmem_ld_wait();
-            if (valid) {
-              __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + c0;
-              uint32_t o[16];
+            if (c + 1 < nchunks) {
+              const uint32_t nb = tq + ((c + 1) >> 2) * BN + ch * 64 + ((c + 1) & 3) * 16;
+              tmem_ld16(nb, g[(c + 1) & 1]);
+              tmem_ld16(nb + BN / 2, u[(c + 1) & 1]);
+            } else {
+              release();
+            }
+            const int row = (c >> 2) * BM + quarter * 32 + lane;   // route row inside the tile
+            if (row < t.nrows) {
+              const uint32_t (&gg)[16] = g[c & 1];
+              const uint32_t (&uu)[16] = u[c & 1];
+              __nv_bfloat16* dst = p.out + ((long long)t.row0 + row) * p.out_stride + f0 + ch * 64 + (c & 3) * 16;
+              uint32_t o[8];
 #pragma unroll
-              for (int j = 0; j < 32; j += 2) {
-                const float a = silu_f32(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-                const float b = silu_f32(__uint_as_float(g[j + 1])) * __uint_as_float(u[j + 1]);
+              for (int j = 0; j < 16; j += 2) {
+                const float a = silu_f32(__uint_as_float(gg[j])) * __uint_as_float(uu[j]);
+                const float b = silu_f32(__uint_as_float(gg[j + 1])) * __uint_as_float(uu[j + 1]);
                 const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
                 o[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
               }
               if (p.permute_out) {
                 // natural pairs (f0,f1)(f2,f3)(f4,f5)(f6,f7) -> (f0,f4)(f1,f5)(f2,f6)(f3,f7) per run of 8
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                  const uint32_t a = o[4 * q8], b = o[4 * q8 + 1], c = o[4 * q8 + 2], d = o[4 * q8 + 3];
-                  o[4 * q8] = prmt(a, c, 0x5410); o[4 * q8 + 1] = prmt(a, c, 0x7632);
+                for (int q8 = 0; q8 < 2; ++q8) {
+                  const uint32_t a = o[4 * q8], b = o[4 * q8 + 1], c2 = o[4 * q8 + 2], d = o[4 * q8 + 3];
+                  o[4 * q8] = prmt(a, c2, 0x5410); o[4 * q8 + 1] = prmt(a, c2, 0x7632);
                   o[4 * q8 + 2] = prmt(b, d, 0x5410); o[4 * q8 + 3] = prmt(b, d, 0x7632);
                 }
               }
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
             }
           }
-        } else {
-          const float wr = !valid ? 0.f : (p.route_weight ? p.route_weight[grow] : 1.f);
+        }
+      } else {
+        // this warp: columns ch*128 .. ch*128+127, 32 per chunk
+        uint32_t acc[2][32];
+        tmem_ld32(tq + ch * 128, acc[0]);
 #pragma unroll
-          for (int part = 0; part < 4; ++part) {
-            uint32_t a[32];
-            const int c0 = ch * 128 + part * 32;
-            tmem_ld32(tbase + c0, a);
+        for (int c = 0; c < 8; ++c) {
+          if (c < nchunks) {
             tmem_ld_wait();
-            if (valid) {
-              __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + c0;
+            if (c + 1 < nchunks) tmem_ld32(tq + ((c + 1) >> 2) * BN + ch * 128 + ((c + 1) & 3) * 32, acc[(c + 1) & 1]);
+            else release();
+            const int row = (c >> 2) * BM + quarter * 32 + lane;
+            if (row < t.nrows) {
+              const long long grow = (long long)t.row0 + row;
+              const float wr = p.route_weight ? p.route_weight[grow] : 1.f;
+              const uint32_t (&a)[32] = acc[c & 1];
+              __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + ch * 128 + (c & 3) * 32;
               uint32_t o[16];
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
@@ -344,9 +365,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      tc_fence_before();                               // the tcgen05.ld above are complete (wait::ld)
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.acc_empty);
     }
   }
   tc_fence_before();
