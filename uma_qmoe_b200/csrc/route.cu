@@ -341,6 +341,38 @@ __device__ __forceinline__ int load_expert(const void* idx, int idx64, long long
   return idx64 ? (int)reinterpret_cast<const long long*>(idx)[i] : reinterpret_cast<const int*>(idx)[i];
 }
 
+// Offsets and the tile list from the per-expert counts in count[] (shared memory).  Thread 0 scans the counts
+// in shared memory only; the global stores (offsets, a few tiles per expert) are then spread over the threads.
+// start[e] receives the first sorted position of expert e.  All threads of the CTA call it.
+__device__ __forceinline__ void emit_offsets_and_tiles(const SortArgs& a, const int* count, int* start, int* tile_base,
+                                                       bool write, int tid, int nthreads) {
+  const int E = a.experts;
+  if (tid == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = count[e];
+      start[e] = run;
+      tile_base[e] = tiles;
+      run += c;
+      tiles += (c + kTileRows - 1) / kTileRows;
+    }
+    start[E] = run;
+    tile_base[E] = tiles;
+  }
+  __syncthreads();
+  if (write) {
+    for (int e = tid; e <= E; e += nthreads) a.offsets[e] = start[e];
+    for (int e = tid; e < E; e += nthreads) {
+      const int c = start[e + 1] - start[e];
+      int t = tile_base[e];
+      for (int r = 0; r < c && t < a.max_tiles; r += kTileRows, ++t) {
+        a.tile_expert[t] = e; a.tile_row0[t] = start[e] + r; a.tile_rows[t] = min(kTileRows, c - r);
+      }
+    }
+    if (tid == 0) *a.num_tiles = min(tile_base[E], a.max_tiles);
+  }
+}
+
 __global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs a) {
   __shared__ int hist[32][kMaxSortExperts];     // per-warp counts, then per-warp running positions
   __shared__ int total[kMaxSortExperts + 1];
@@ -367,20 +399,10 @@ __global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs
     a.counts[tid] = run;
   }
   __syncthreads();
-  if (tid == 0) {
-    int run = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      const int c = total[e];
-      a.offsets[e] = run;
-      total[e] = run;
-      for (int r = 0; r < c && tiles < a.max_tiles; r += kTileRows, ++tiles) {
-        a.tile_expert[tiles] = e; a.tile_row0[tiles] = run + r; a.tile_rows[tiles] = min(kTileRows, c - r);
-      }
-      run += c;
-    }
-    a.offsets[E] = run;
-    *a.num_tiles = tiles;
-  }
+  __shared__ int start[kMaxSortExperts + 1], tile_base[kMaxSortExperts + 1];
+  emit_offsets_and_tiles(a, total, start, tile_base, true, tid, kSortThreads);
+  __syncthreads();
+  if (tid < E) total[tid] = start[tid];
   __syncthreads();
   for (long long base = begin; base < end; base += 32) {
     const long long i = base + lane;
@@ -459,21 +481,10 @@ __global__ void __launch_bounds__(kSortThreads) route_place_kernel(const SortArg
     for (int w = 0; w < 32; ++w) { const int c2 = hist[w][tid]; hist[w][tid] = run; run += c2; }
   }
   __syncthreads();
-  if (tid == 0) {
-    int run = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      const int c2 = total[e];
-      if (blockIdx.x == 0) {
-        a.offsets[e] = run;
-        for (int r = 0; r < c2 && tiles < a.max_tiles; r += kTileRows, ++tiles) {
-          a.tile_expert[tiles] = e; a.tile_row0[tiles] = run + r; a.tile_rows[tiles] = min(kTileRows, c2 - r);
-        }
-      }
-      total[e] = run + before[e];
-      run += c2;
-    }
-    if (blockIdx.x == 0) { a.offsets[E] = run; *a.num_tiles = tiles; }
-  }
+  __shared__ int start[kMaxSortExperts + 1], tile_base[kMaxSortExperts + 1];
+  emit_offsets_and_tiles(a, total, start, tile_base, blockIdx.x == 0, tid, kSortThreads);
+  __syncthreads();
+  if (tid < E) total[tid] = start[tid] + before[tid];
   __syncthreads();
   for (long long base = begin; base < end; base += 32) {
     const long long i = base + lane;
@@ -559,23 +570,25 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
   __shared__ float red[8];
   __shared__ float gate;
   const int t = blockIdx.x, tid = threadIdx.x;
-  if (tid == 0) {
-    int ex[8], ps[8], n = 0;
-    for (int s = 0; s < top_k; ++s) {
-      const int e = load_expert(indices, idx64, (long long)t * top_k + s);
-      if (e == -1) continue;                      // absent route: contributes nothing
-      const int q = route_pos[(long long)t * top_k + s];
-      if (q < 0) continue;                        // route without a row (dropped by a fixed-capacity exchange)
-      ex[n] = e; ps[n] = q; ++n;
+  __shared__ int raw_e[8], raw_q[8];
+  if (tid < top_k) {                               // eight independent loads instead of a serial chain
+    raw_e[tid] = load_expert(indices, idx64, (long long)t * top_k + tid);
+    raw_q[tid] = route_pos[(long long)t * top_k + tid];
+  }
+  __syncthreads();
+  if (tid < 8) {
+    // rank of every present route among the present ones by (expert, slot): a stable sort by counting.
+    // Absent routes (expert -1) and routes without a row (position -1) contribute nothing.
+    const bool valid = tid < top_k && raw_e[tid] != -1 && raw_q[tid] >= 0;
+    int rank = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool vj = j < top_k && raw_e[j] != -1 && raw_q[j] >= 0;
+      rank += vj && (raw_e[j] < raw_e[tid] || (raw_e[j] == raw_e[tid] && j < tid));
     }
-    for (int i = 1; i < n; ++i) {                 // stable insertion sort by expert
-      const int e = ex[i], q = ps[i];
-      int j = i - 1;
-      while (j >= 0 && ex[j] > e) { ex[j + 1] = ex[j]; ps[j + 1] = ps[j]; --j; }
-      ex[j + 1] = e; ps[j + 1] = q;
-    }
-    for (int s = 0; s < n; ++s) order_pos[s] = ps[s];
-    present = n;
+    if (valid) order_pos[rank] = raw_q[tid];
+    const unsigned m = __ballot_sync(0xffu, valid);
+    if (tid == 0) present = __popc(m);
   }
   if (shared_out) {
     float acc = 0.f;
@@ -593,19 +606,45 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
     gate = bf16_round(1.f / (1.f + expf(-s)));
   }
   __syncthreads();
-  for (int c = tid * 2; c < hidden; c += 512) {
-    float r0 = 0.f, r1 = 0.f;
-    for (int s = 0; s < present; ++s) {
-      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(weighted + (size_t)order_pos[s] * hidden + c);
-      r0 = bf16_round(r0 + __low2float(v));
-      r1 = bf16_round(r1 + __high2float(v));
+  // all of a column pair's contributions are loaded first (independent loads), then summed in order
+  const int n = present;
+  const __nv_bfloat16* rows[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) rows[s] = weighted + (size_t)order_pos[s < n ? s : 0] * hidden;
+  for (int c = tid * 8; c < hidden; c += 2048) {        // 16 bytes per thread and row (hidden % 8 == 0)
+    uint4 v[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s < n) v[s] = *reinterpret_cast<const uint4*>(rows[s] + c);
+    float r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r[e] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < n) {
+        const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          r[2 * e] = bf16_round(r[2 * e] + __uint_as_float(w[e] << 16));
+          r[2 * e + 1] = bf16_round(r[2 * e + 1] + __uint_as_float(w[e] & 0xffff0000u));
+        }
+      }
     }
     if (shared_out) {
-      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(shared_out + (size_t)t * hidden + c);
-      r0 = bf16_round(r0 + bf16_round(gate * __low2float(v)));
-      r1 = bf16_round(r1 + bf16_round(gate * __high2float(v)));
+      const uint4 sv = *reinterpret_cast<const uint4*>(shared_out + (size_t)t * hidden + c);
+      const uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        r[2 * e] = bf16_round(r[2 * e] + bf16_round(gate * __uint_as_float(w[e] << 16)));
+        r[2 * e + 1] = bf16_round(r[2 * e + 1] + bf16_round(gate * __uint_as_float(w[e] & 0xffff0000u)));
+      }
     }
-    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * hidden + c) = __floats2bfloat162_rn(r0, r1);
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(r[0], r[1]), p1 = __floats2bfloat162_rn(r[2], r[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(r[4], r[5]), p3 = __floats2bfloat162_rn(r[6], r[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = o;
   }
 }
 
@@ -683,7 +722,7 @@ int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_
 int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
                    int top_k, int hidden, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
                    const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream) {
-  if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 2) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
+  if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 8) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
   combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, shared_out, x, gate_vec, out);
   return check_launch("combine");
 }
