@@ -301,6 +301,9 @@ __device__ __forceinline__ void mma_full(const uint4 (&ra)[N], const uint4 (&rb)
 // 16-byte boundary.  BF16 rows read the BF16 vector itself.
 __host__ __device__ __forceinline__ int frag_body_bytes(int n) { return n * 2 + (((n >> 6) + 3) & ~3) * 4; }
 __host__ __device__ __forceinline__ size_t frag_record_bytes(int n) { return (size_t)frag_body_bytes(n) + 16; }
+// The record the gate/up kernel leaves for quantised down rows: n fp16 fragments in 32-value chunks, each chunk
+// multiplied by its own power-of-two prescale, then the n/32 prescales and the n/32 chunk bias sums (float32).
+__host__ __device__ __forceinline__ int chunk_record_bytes(int n) { return n * 2 + (n >> 5) * 8; }
 
 // Publishes the record of `n` float values held as vals[j] = value at index tid*4 + j*NT*4 + 0..3
 // (a CTA-wide layout of NT threads); all threads of the CTA call it.  `stage` is frag_body_bytes(n) bytes of
@@ -338,8 +341,8 @@ __device__ __forceinline__ void publish_record(int enc, int n, const float (&val
 // cross-warp sum.  The activation fragments are built once per CTA and serve all four tiles (building
 // them costs about as many instructions as one tile's arithmetic, so a CTA per tile spent three
 // quarters of its instructions there).  Weight blocks stream through two register buffers of two
-// blocks each: the loads of group g + 2 are issued as soon as group g has been multiplied.  The CTA
-// that completes a slot publishes the fragment record of that slot's intermediate vector in place.
+// blocks each: the loads of group g + 2 are issued as soon as group g has been multiplied.  Every CTA
+// writes its 32 intermediates into the slot's record itself (chunk_record_bytes below).
 // =====================================================================================================
 constexpr int kWarpsA = 8, kThreadsA = kWarpsA * 32, kTilesA = 4, kSplitA = kWarpsA / kTilesA;
 
@@ -352,7 +355,6 @@ __global__ void __launch_bounds__(kThreadsA, 2) decode_gateup_kernel(const Decod
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float red[kWarpsA * 16];
   __shared__ float red2[kWarpsA];
-  __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
   const int H = p.hidden;
   pdl_launch_dependents();
@@ -487,9 +489,13 @@ __global__ void __launch_bounds__(kThreadsA, 2) decode_gateup_kernel(const Decod
   }
   if (c == 0) { red[warp * 16 + q] = acc_lo; red[warp * 16 + 8 + q] = acc_hi; }
   __syncthreads();
+  // ---- SwiGLU, then this CTA's 32 intermediates go straight into the slot's record for the down kernel ------
+  // Quantised down rows: fp16 fragments of the chunk with the chunk's own power-of-two prescale, the prescale
+  // and the chunk's bias sum (the down kernel brings the chunks of one weight block to a common scale).
+  // BF16 down rows: the BF16 values.  No CTA waits for another one.
   const int ioff = shared_tile ? p.top_k * p.inter : slot * p.inter;
-  if (tid < kFeat && f0 + tid < islot) {
-    const int t = tid >> 3, j = tid & 7;
+  if (warp == 0 && f0 + lane < islot) {           // islot is a multiple of 32: the whole warp or none of it
+    const int t = lane >> 3, j = lane & 7;
     float g = 0.f, u = 0.f;
 #pragma unroll
     for (int w = 0; w < kSplitA; ++w) { g += red[(t * kSplitA + w) * 16 + j]; u += red[(t * kSplitA + w) * 16 + 8 + j]; }
@@ -501,43 +507,37 @@ __global__ void __launch_bounds__(kThreadsA, 2) decode_gateup_kernel(const Decod
       g *= x_inv; u *= x_inv;
       v = silu_f32(g) * u;
     }
-    p.inter_buf[ioff + f0 + tid] = v;
+    const int enc_b = shared_tile ? ENC_BF16 : p.enc;          // encoding of the down rows that read it
+    uint8_t* recp = reinterpret_cast<uint8_t*>(p.inter_buf + ioff);
+    const int k = f0 + lane;
+    if (enc_b == ENC_BF16) {
+      reinterpret_cast<__nv_bfloat16*>(recp)[k] = __float2bfloat16_rn(v);
+    } else {
+      float am = fabsf(v);
+      am = am < 3.0e38f ? am : 0.f;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+      const float sc = prescale_for(am);
+      const int r = k & 7;
+      int pos = k;
+      float val = v * sc, coef = 1152.f;
+      if (enc_b == ENC_Q4) {            // run order [k0,k4,k1/16,k5/16,k2,k6,k3/16,k7/16], see store_frag4
+        pos = (k & ~7) + (r < 4 ? 2 * r : 2 * (r - 4) + 1);
+        if (r & 1) val *= 0.0625f; else coef = 1032.f;
+      }
+      const __half h = __float2half_rn(val);
+      reinterpret_cast<__half*>(recp)[pos] = h;
+      float bsum = coef * __half2float(h);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) bsum += __shfl_xor_sync(0xffffffffu, bsum, o);
+      if (lane == 0) {
+        float* tail = reinterpret_cast<float*>(recp + (size_t)islot * 2);
+        tail[k >> 5] = sc;
+        tail[(islot >> 5) + (k >> 5)] = bsum;
+      }
+    }
   }
   (void)x_inv;
-  // ---- the last CTA of the slot turns the slot's float32 intermediate into its fragment record, in place ---
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    const unsigned done = atomicAdd(p.amax + slot, 1u);
-    const unsigned ctas = (unsigned)((islot + kFeat - 1) / kFeat);
-    s_last = (done == ctas - 1);
-    if (s_last) { atomicExch(p.amax + slot, 0u); __threadfence(); }
-  }
-  __syncthreads();
-  if (!s_last) return;
-  const int enc_b = shared_tile ? ENC_BF16 : p.enc;          // encoding of the down rows that read it
-  constexpr int kMaxV = 6;                                   // intermediate size <= 6 * 1024
-  float vals[kMaxV][4];
-#pragma unroll
-  for (int j = 0; j < kMaxV; ++j) {
-    const int k0 = tid * 4 + j * kThreadsA * 4;
-    vals[j][0] = vals[j][1] = vals[j][2] = vals[j][3] = 0.f;
-    if (k0 < islot) {
-      const float4 f = __ldcg(reinterpret_cast<const float4*>(p.inter_buf + ioff + k0));
-      vals[j][0] = f.x; vals[j][1] = f.y; vals[j][2] = f.z; vals[j][3] = f.w;
-    }
-  }
-  __syncthreads();                       // every value is in registers before the region is overwritten
-  uint8_t* dst = reinterpret_cast<uint8_t*>(p.inter_buf + ioff);
-  if (enc_b == ENC_BF16) {
-#pragma unroll
-    for (int j = 0; j < kMaxV; ++j) {
-      const int k0 = tid * 4 + j * kThreadsA * 4;
-      if (k0 < islot) store_frag4(ENC_BF16, dst, k0, vals[j]);
-    }
-  } else {
-    publish_record<kMaxV, kThreadsA>(enc_b, islot, vals, smem, red2, dst, tid);
-  }
 }
 
 // =====================================================================================================
@@ -552,6 +552,7 @@ struct DownTile {
   const uint8_t* wa; const uint8_t* wb;        // row n0 + q of the two slots' experts (wb null: no second slot)
   const float* sa; const float* sb;            // their scale rows
   int rec_a, rec_b;                            // byte offsets of the slots' records in shared memory
+  int slot_a, slot_b;
 };
 
 __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParams p) {
@@ -559,7 +560,6 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
   __shared__ int s_order[kMaxSlots];
   __shared__ int s_expert[kMaxSlots];
   __shared__ float s_weight[kMaxSlots];
-  __shared__ float s_inv[kMaxSlots];
   __shared__ float s_red[5][kWarps][16];
   __shared__ float s_tmp[kWarps];
   __shared__ float s_gate;
@@ -571,9 +571,13 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
   // shared memory: the published records of the routed slots (fragments + bias), then the shared
   // expert's BF16 vector
   const int enc = p.enc;
-  const int rec = enc == ENC_BF16 ? I * 2 : frag_body_bytes(I);        // bytes copied per routed slot
+  const int rec = enc == ENC_BF16 ? I * 2 : chunk_record_bytes(I);     // bytes copied per routed slot
   uint8_t* recs = smem;
   uint8_t* xs = smem + (size_t)p.top_k * rec;
+  // per (slot, 64-byte weight block): bias sum and inverse of the common prescale of the block's chunks
+  const int nblk_all = row_bytes(enc, I) >> 6;
+  float* s_bbias = reinterpret_cast<float*>(xs + (size_t)(p.sh_gate ? p.shared_inter : 0) * 2);
+  float* s_binv = s_bbias + (size_t)p.top_k * nblk_all;
 
   // ---- routes: order by expert (stable), shared expert last ----------------------------------------------
   if (tid == 0) s_bad = 0;
@@ -609,13 +613,13 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
     const size_t ra = (size_t)s_expert[a] * H + n0 + q;
     d.wa = p.down + ra * rb + (c << 4);
     d.sa = enc != ENC_BF16 ? p.down_s + ra * gk : nullptr;
-    d.rec_a = a * rec;
+    d.rec_a = a * rec; d.slot_a = a;
     if (b >= 0) {
       const size_t rbw = (size_t)s_expert[b] * H + n0 + q;
       d.wb = p.down + rbw * rb + (c << 4);
       d.sb = enc != ENC_BF16 ? p.down_s + rbw * gk : nullptr;
-      d.rec_b = b * rec;
-    } else { d.wb = nullptr; d.sb = nullptr; d.rec_b = d.rec_a; }
+      d.rec_b = b * rec; d.slot_b = b;
+    } else { d.wb = nullptr; d.sb = nullptr; d.rec_b = d.rec_a; d.slot_b = a; }
     return d;
   };
   // (tile, first block of the pair) walked in order; one iterator for the loads, one for the arithmetic
@@ -643,7 +647,7 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
     const DownTile d = tile_of(w.t);
     const int n = min(2, bpw - w.first);
     const uint8_t* xp[2];
-    float bsa[2], bsb[2];
+    float bsa[2], bsb[2], iva[2], ivb[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int kb = warp + (w.first + min(i, n - 1)) * kWarps;
@@ -651,9 +655,9 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
       const uint8_t* base = q == 0 ? recs + d.rec_a : recs + d.rec_b;
       xp[i] = q < 2 ? base + (size_t)kb * fb + c * (fb >> 2) : s_zero + c * (fb >> 2);
       if (enc != ENC_BF16) {
-        bsa[i] = reinterpret_cast<const float*>(recs + d.rec_a + (size_t)I * 2)[kb];
-        bsb[i] = reinterpret_cast<const float*>(recs + d.rec_b + (size_t)I * 2)[kb];
-      } else { bsa[i] = bsb[i] = 0.f; }
+        bsa[i] = s_bbias[d.slot_a * nblk_all + kb]; bsb[i] = s_bbias[d.slot_b * nblk_all + kb];
+        iva[i] = s_binv[d.slot_a * nblk_all + kb]; ivb[i] = s_binv[d.slot_b * nblk_all + kb];
+      } else { bsa[i] = bsb[i] = 0.f; iva[i] = ivb[i] = 1.f; }
     }
     float lo[2], hi[2];
     if (n == 2) {
@@ -669,7 +673,10 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
     for (int i = 0; i < 2; ++i) {
       if (i < n) {
         if (enc == ENC_BF16) { acc_lo += lo[i]; acc_hi += hi[i]; }
-        else { acc_lo = fmaf(b.sa[i], lo[i] - bsa[i], acc_lo); acc_hi = fmaf(b.sb[i], hi[i] - bsb[i], acc_hi); }
+        else {
+          acc_lo = fmaf(b.sa[i] * iva[i], lo[i] - bsa[i], acc_lo);
+          acc_hi = fmaf(b.sb[i] * ivb[i], hi[i] - bsb[i], acc_hi);
+        }
       }
     }
     if (w.first + 2 >= bpw) {              // last pair of the tile for this warp: park the partial sums
@@ -707,12 +714,70 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
 
   pdl_wait();                           // kernel A's records are complete and visible from here on
 
-  // ---- copy the records into shared memory (straight 16-byte copies, no arithmetic) ------------------------
-  for (int s = 0; s < p.top_k; ++s) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I);
-    uint4* dst = reinterpret_cast<uint4*>(recs + (size_t)s * rec);
-    for (int i = tid; i < (rec >> 4); i += kThreads) dst[i] = __ldcg(src + i);
-    if (tid == 0 && enc != ENC_BF16) s_inv[s] = __ldcg(reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(src) + rec));
+  // ---- copy the records into shared memory -------------------------------------------------------------------
+  // Quantised rows: first the chunk prescales and bias sums; every weight block then gets the smallest prescale
+  // of its chunks (powers of two, so rescaling a chunk is exact), its bias sum and the inverse prescale; the
+  // fragments are copied with their chunk's ratio applied.  BF16 rows: straight 16-byte copies.
+  if (enc != ENC_BF16) {
+    const int chunks = I >> 5, cpb = enc == ENC_Q4 ? 4 : 2;           // 32-value chunks; chunks per weight block
+    const int tailw = (chunks * 8) >> 4;                              // 16-byte words of {prescales, bias sums}
+    const int fragw = (I * 2) >> 4;                                   // 16-byte words of fragments per slot
+    // all loads of this thread go out together (one L2 round trip): its words of the chunk tables and its
+    // first kHold fragment words, which wait in registers until the ratios are known
+    constexpr int kHold = 8;
+    uint4 held[kHold];
+#pragma unroll
+    for (int j = 0; j < kHold; ++j) {
+      const int w = tid + j * kThreads;                               // word index over all slots
+      if (w < p.top_k * fragw) {
+        const int s = w / fragw, i = w - s * fragw;
+        held[j] = __ldcg(reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I) + i);
+      }
+    }
+    for (int w = tid; w < p.top_k * tailw; w += kThreads) {
+      const int s = w / tailw, i = w - s * tailw;
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.inter_buf + (size_t)s * I) + (size_t)I * 2);
+      reinterpret_cast<uint4*>(recs + (size_t)s * rec + (size_t)I * 2)[i] = __ldcg(src + i);
+    }
+    __syncthreads();
+    for (int it = tid; it < p.top_k * nblk_all; it += kThreads) {
+      const int s = it / nblk_all, kb = it - s * nblk_all;
+      float* sc = reinterpret_cast<float*>(recs + (size_t)s * rec + (size_t)I * 2);
+      const float* cb = sc + chunks;
+      float m = sc[kb * cpb];
+      for (int c2 = 1; c2 < cpb; ++c2) m = fminf(m, sc[kb * cpb + c2]);
+      float bsum = 0.f;
+      for (int c2 = 0; c2 < cpb; ++c2) {
+        const float ratio = m / sc[kb * cpb + c2];                    // a power of two <= 1
+        bsum += cb[kb * cpb + c2] * ratio;
+        sc[kb * cpb + c2] = ratio;                                    // the fragment copy below reads the ratio
+      }
+      s_bbias[it] = bsum;
+      s_binv[it] = 1.f / m;
+    }
+    __syncthreads();
+    auto scaled_store = [&](uint4 w, int s, int i) {
+      const float* ratio = reinterpret_cast<const float*>(recs + (size_t)s * rec + (size_t)I * 2);
+      const __half2 r2 = __float2half2_rn(ratio[i >> 2]);             // 8 values per word, 32 per chunk
+      __half2* h = reinterpret_cast<__half2*>(&w);
+      h[0] = __hmul2(h[0], r2); h[1] = __hmul2(h[1], r2); h[2] = __hmul2(h[2], r2); h[3] = __hmul2(h[3], r2);
+      reinterpret_cast<uint4*>(recs + (size_t)s * rec)[i] = w;
+    };
+#pragma unroll
+    for (int j = 0; j < kHold; ++j) {
+      const int w = tid + j * kThreads;
+      if (w < p.top_k * fragw) { const int s = w / fragw; scaled_store(held[j], s, w - s * fragw); }
+    }
+    for (int w = tid + kHold * kThreads; w < p.top_k * fragw; w += kThreads) {     // shapes with more words
+      const int s = w / fragw, i = w - s * fragw;
+      scaled_store(__ldcg(reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I) + i), s, i);
+    }
+  } else {
+    for (int s = 0; s < p.top_k; ++s) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I);
+      uint4* dst = reinterpret_cast<uint4*>(recs + (size_t)s * rec);
+      for (int i = tid; i < (rec >> 4); i += kThreads) dst[i] = __ldcg(src + i);
+    }
   }
   if (S) {
     const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)p.top_k * I);
@@ -766,7 +831,6 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
       float y = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) y += s_red[t][w][half * 8 + tid];
-      if (enc != ENC_BF16) y *= s_inv[slot];
       run = bf16_round(run + bf16_round(y * s_weight[slot]));
     }
     if (S) {
@@ -784,8 +848,9 @@ size_t gateup_smem(const DecodeParams& p) {
   return (size_t)frag_body_bytes(big) + 64;                      // x fragments, later staging of a record
 }
 size_t down_smem(const DecodeParams& p) {
-  const size_t rec = p.enc == ENC_BF16 ? (size_t)p.inter * 2 : (size_t)frag_body_bytes(p.inter);
-  return (size_t)p.top_k * rec + (p.sh_gate ? (size_t)p.shared_inter * 2 : 0) + 64;
+  const size_t rec = p.enc == ENC_BF16 ? (size_t)p.inter * 2 : (size_t)chunk_record_bytes(p.inter);
+  const size_t blocks = (size_t)p.top_k * (row_bytes(p.enc, p.inter) >> 6);
+  return (size_t)p.top_k * rec + (p.sh_gate ? (size_t)p.shared_inter * 2 : 0) + blocks * 8 + 64;
 }
 
 }  // namespace
