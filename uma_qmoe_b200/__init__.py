@@ -8,11 +8,12 @@ from .custom_op import (PLATFORM, acquire_expert_pack, expert_pack_for_handle, r
                         register_moe_forward, register_performance_backend, register_target_pack,
                         unregister_expert_pack)
 from .formats import ContractError
+from .pack_files import ExpertPackFile, TargetPackFile
 
 __all__ = [
     "PLATFORM", "ContractError", "acquire_expert_pack", "expert_pack_for_handle", "register_expert_pack",
     "register_moe_forward", "register_performance_backend", "register_target_pack", "unregister_expert_pack",
-    "install_packed_q4_backend", "install_mixed_target_backend",
+    "install_packed_q4_backend", "install_mixed_target_backend", "ExpertPackFile", "TargetPackFile",
 ]
 
 
