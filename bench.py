@@ -329,6 +329,8 @@ def kernel_case(args) -> None:
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    if args.only == "model":
+        return model_case(args, dev)
     shape = syn.OLMOE
     stack = MoEStack.build(shape, "q4_group128", args.layers, SEED, dev, renormalize=True, skew=1.0)
     if args.only == "decode":
@@ -367,13 +369,44 @@ def kernel_case(args) -> None:
                           "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
 
 
+def model_case(args, dev) -> None:
+    """BASELINE config 3: a Qwen1.5-MoE-A2.7B-shaped model with random weights (24 layers unless --layers says
+    otherwise), experts of layers 0-15 BF16 and 16-23 Q8 (`--variant 0`) or all Q4 (`--variant 1`), greedy decode of
+    128 prompt tokens + 32 generated at batch 1 through the Hugging Face model with this package's blocks."""
+    import transformers
+    from uma_qmoe_b200.host import greedy_decode, install_quantized_blocks
+    layers = args.layers if args.layers != 2 else 24
+    cfg = transformers.Qwen2MoeConfig(vocab_size=151936, hidden_size=2048, num_hidden_layers=layers,
+                                      num_attention_heads=16, num_key_value_heads=16, max_position_embeddings=8192,
+                                      intermediate_size=5632, moe_intermediate_size=1408,
+                                      shared_expert_intermediate_size=5632, num_experts=60, num_experts_per_tok=4,
+                                      norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[])
+    torch.manual_seed(SEED)
+    with torch.device(dev):
+        model = transformers.Qwen2MoeForCausalLM(cfg).to(torch.bfloat16).eval()
+    policy = ("q4_group128" if args.variant == 1 else
+              {i: ("bf16_le" if i < layers * 2 // 3 else "q8_group128") for i in range(layers)})
+    host = install_quantized_blocks(model, policy)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 128), generator=torch.Generator().manual_seed(SEED)).to(dev)
+    greedy_decode(model, prompt, 4)                                  # warm-up: workspaces, autotuned attention
+    runs = [greedy_decode(model, prompt, 32) for _ in range(3)]
+    tpot = sorted(t for r in runs for t in r["tpot_ms"])
+    print(json.dumps({"case": "model", "layers": layers, "policy": "all q4_group128" if args.variant == 1 else
+                      "layers 0-15 bf16_le, 16-23 q8_group128", "prompt_tokens": 128, "new_tokens": 32,
+                      "ttft_ms": statistics.median(r["ttft_ms"] for r in runs), "tpot_ms_p50": statistics.median(tpot),
+                      "tpot_ms_p95": tpot[int(0.95 * (len(tpot) - 1))], "decode_tokens_per_s": 1e3 / statistics.median(tpot),
+                      "expert_storage_bytes": host.evidence["expert_storage_bytes"],
+                      "tokens_equal_across_runs": all(r["tokens"] == runs[0]["tokens"] for r in runs)}))
+    host.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
-    ap.add_argument("--only", choices=("all", "decode", "gemm"), default="all",
+    ap.add_argument("--only", choices=("all", "decode", "gemm", "model"), default="all",
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")

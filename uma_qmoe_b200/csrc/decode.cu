@@ -1,5 +1,4 @@
-// Batch-1 decode: two lean kernels, a thousand small CTAs each, chained by programmatic dependent
-// launch.
+// Batch-1 decode: two kernels chained by programmatic dependent launch.
 //
 //   out = sum_slot w_slot * Down_e( SiLU(Gate_e x) * Up_e x )   (+ Qwen shared expert)
 //
@@ -7,18 +6,19 @@
 // (src/uma_qmoe/native/packed_q4_kernel.cu:156-231 gate/up+SwiGLU, :1369-1426 down+route sum,
 // launched from :1486-1533; Q8 twins :781-892) and the per-expert Python GEMV loops for Qwen
 // (src/uma_qmoe/native_backend.py:319-372, :722-753).  Numerics follow the reference's CPU
-// correctness path (src/uma_qmoe/custom_op.py:301-340, :465-506): float32 intermediate, one BF16
-// rounding of every expert contribution and of the running sum, experts in ascending order.
+// correctness path (src/uma_qmoe/custom_op.py:301-340, :465-506): float32 accumulation, one BF16
+// rounding of every expert contribution and of the running sum, experts in ascending order; the
+// intermediate travels between the kernels as power-of-two-prescaled fp16 (BF16 for BF16 rows).
 //
 // The layer is ~27 MB (OLMoE Q4) to ~105 MB (Qwen Q8 + BF16 shared expert) of weights read exactly
 // once: a pure HBM stream of a few microseconds, during which nothing may serialise.  Kernel A
-// (gate/up + SwiGLU) gives every 16-row warp-MMA tile (8 features: 8 gate rows + 8 up rows, all of K)
-// its own 128-thread CTA; kernel B (down + ordered combine) gives every 8 output rows a CTA that
-// walks the selected experts in pairs.  Each thread issues all its 16-byte weight loads up front, so
-// with ~7 resident CTAs per SM well over 100 KB are in flight per SM and latency is hidden by
-// parallelism, not by a software pipeline; no CTA waits for another.  Kernel B is launched with
-// programmatic stream serialisation: its CTAs start while kernel A drains, issue their weight loads,
-// and only then wait for A's intermediate.
+// (gate/up + SwiGLU) gives every 32 features of a selected expert a 256-thread CTA: four 16-row
+// warp-MMA tiles (8 gate rows + 8 up rows each, all of K), two warps per tile, the activation
+// fragments built once per CTA; kernel B (down + ordered combine) gives every 8 output rows a CTA
+// that walks the selected experts in pairs.  Weight blocks stream through register buffers that are
+// refilled as soon as they have been multiplied; no CTA waits for another.  Kernel B is launched with
+// programmatic stream serialisation: its CTAs start while kernel A drains, issue their first weight
+// loads, and only then wait for A's records.
 //
 // Dequantisation is free of per-weight arithmetic: nibbles become exact integer-valued fp16
 // ((w ^ 8) & 0xF | 0x6400 = 1024 + code + 8, one LOP3 per two weights) and go straight into
@@ -55,42 +55,6 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // 2c, 2c+1; d[2], d[3] = row q+8.
 #define UMAQ_Q4_LO(w) lop3<0x6A>((w), 0x000F000Fu, 0x64086408u)   /* fp16 1024 + (code + 8)      */
 #define UMAQ_Q4_HI(w) lop3<0x6A>((w), 0x00F000F0u, 0x64806480u)   /* fp16 1024 + 16 * (code + 8) */
-
-__device__ __forceinline__ void mma_block(int enc, const uint4& ra, const uint4& rb, const uint8_t* xf_lane, bool xvalid,
-                                          float (&d)[4]) {
-  float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint32_t a[4] = {ra.x, ra.y, ra.z, ra.w}, b[4] = {rb.x, rb.y, rb.z, rb.w};
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  if (enc == ENC_Q4) {
-    const uint4* xp = reinterpret_cast<const uint4*>(xf_lane);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 x = xvalid ? xp[j] : zero;
-      const uint32_t ah = a[j] >> 8, bh = b[j] >> 8;
-      mma_f16_16816(d0, UMAQ_Q4_LO(a[j]), UMAQ_Q4_LO(b[j]), UMAQ_Q4_HI(a[j]), UMAQ_Q4_HI(b[j]), x.x, x.y);
-      mma_f16_16816(d1, UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x.z, x.w);
-    }
-  } else if (enc == ENC_Q8) {
-    const uint4* xp = reinterpret_cast<const uint4*>(xf_lane);
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint4 x = xvalid ? xp[j] : zero;
-      const uint32_t a0 = a[2 * j] ^ 0x80808080u, a1 = a[2 * j + 1] ^ 0x80808080u;
-      const uint32_t b0 = b[2 * j] ^ 0x80808080u, b1 = b[2 * j + 1] ^ 0x80808080u;
-      // byte | 0x6400 -> fp16 1024 + (code + 128)
-      mma_f16_16816(d0, prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
-                    prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x.x, x.y);
-      mma_f16_16816(d1, prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
-                    prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x.z, x.w);
-    }
-  } else {
-    const uint4 x = xvalid ? *reinterpret_cast<const uint4*>(xf_lane) : zero;
-    mma_bf16_16816(d0, a[0], b[0], a[1], b[1], x.x, x.y);
-    mma_bf16_16816(d1, a[2], b[2], a[3], b[3], x.z, x.w);
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) d[i] = d0[i] + d1[i];
-}
 
 // bytes of activation fragments per 64-byte weight block: Q4 128 k, Q8 64 k, BF16 32 k, 2 bytes each
 __device__ __forceinline__ int frag_block_bytes(int enc) { return enc == ENC_Q4 ? 256 : (enc == ENC_Q8 ? 128 : 64); }
@@ -294,46 +258,13 @@ __device__ __forceinline__ void mma_full(const uint4 (&ra)[N], const uint4 (&rb)
   for (int i = 0; i < N; ++i) { lo[i] = d0[i][0] + d1[i][0]; hi[i] = d0[i][HI] + d1[i][HI]; }
 }
 
-// ---- fragment records in global memory ------------------------------------------------------------------
-// A vector of n activations that quantised rows will multiply is published once as: n fp16 fragments
-// (2n bytes), then the bias sums of its 64-byte weight blocks (n/64 floats, padded to a multiple of
-// four), then the inverse of its power-of-two prescale in a 16-byte slot.  Every part starts on a
-// 16-byte boundary.  BF16 rows read the BF16 vector itself.
+// ---- activation fragments ------------------------------------------------------------------------------------
+// Shared memory the gate/up kernel needs for an n-long activation vector: n fp16 fragments (2n bytes) and the
+// bias sums of its 64-byte weight blocks (n/64 floats, padded to a multiple of four).
 __host__ __device__ __forceinline__ int frag_body_bytes(int n) { return n * 2 + (((n >> 6) + 3) & ~3) * 4; }
-__host__ __device__ __forceinline__ size_t frag_record_bytes(int n) { return (size_t)frag_body_bytes(n) + 16; }
 // The record the gate/up kernel leaves for quantised down rows: n fp16 fragments in 32-value chunks, each chunk
 // multiplied by its own power-of-two prescale, then the n/32 prescales and the n/32 chunk bias sums (float32).
 __host__ __device__ __forceinline__ int chunk_record_bytes(int n) { return n * 2 + (n >> 5) * 8; }
-
-// Publishes the record of `n` float values held as vals[j] = value at index tid*4 + j*NT*4 + 0..3
-// (a CTA-wide layout of NT threads); all threads of the CTA call it.  `stage` is frag_body_bytes(n) bytes of
-// shared memory.
-template <int MAXV, int NT = kThreads>
-__device__ __forceinline__ void publish_record(int enc, int n, const float (&vals)[MAXV][4], uint8_t* stage,
-                                               float* red, uint8_t* dst, int tid) {
-  float am = 0.f;
-#pragma unroll
-  for (int j = 0; j < MAXV; ++j)
-    if (tid * 4 + j * NT * 4 < n)
-      am = fmaxf(am, fmaxf(fmaxf(fabsf(vals[j][0]), fabsf(vals[j][1])), fmaxf(fabsf(vals[j][2]), fabsf(vals[j][3]))));
-  const float m = block_max<NT / 32>(am < 3.0e38f ? am : 0.f, red, tid);
-  const float sc = prescale_for(m);
-#pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int k0 = tid * 4 + j * NT * 4;
-    if (k0 < n) {
-      const float v[4] = {vals[j][0] * sc, vals[j][1] * sc, vals[j][2] * sc, vals[j][3] * sc};
-      store_frag4(enc, stage, k0, v);
-    }
-  }
-  __syncthreads();
-  float* bias = reinterpret_cast<float*>(stage + (size_t)n * 2);
-  build_bias<NT>(enc, stage, bias, n, tid);
-  __syncthreads();
-  const int words = frag_body_bytes(n) >> 4;                // 16-byte words of fragments + padded bias
-  for (int i = tid; i < words; i += NT) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(stage)[i];
-  if (tid == 0) *reinterpret_cast<float*>(dst + frag_body_bytes(n)) = 1.f / sc;
-}
 
 // =====================================================================================================
 // Kernel A: one CTA = 32 features of one slot = four 16-row tiles (rows 0..7 gate rows, 8..15 up rows
@@ -844,8 +775,7 @@ __global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParam
 }
 
 size_t gateup_smem(const DecodeParams& p) {
-  const int big = std::max(p.hidden, std::max(p.inter, p.sh_gate ? p.shared_inter : 0));
-  return (size_t)frag_body_bytes(big) + 64;                      // x fragments, later staging of a record
+  return (size_t)frag_body_bytes(p.hidden) + 64;                 // x fragments and their bias sums
 }
 size_t down_smem(const DecodeParams& p) {
   const size_t rec = p.enc == ENC_BF16 ? (size_t)p.inter * 2 : (size_t)chunk_record_bytes(p.inter);
