@@ -374,7 +374,7 @@ def model_case(args, dev) -> None:
     otherwise), experts of layers 0-15 BF16 and 16-23 Q8 (`--variant 0`) or all Q4 (`--variant 1`), greedy decode of
     128 prompt tokens + 32 generated at batch 1 through the Hugging Face model with this package's blocks."""
     import transformers
-    from uma_qmoe_b200.host import greedy_decode, install_quantized_blocks
+    from uma_qmoe_b200.host import greedy_decode, greedy_decode_graphed, install_quantized_blocks
     layers = args.layers if args.layers != 2 else 24
     cfg = transformers.Qwen2MoeConfig(vocab_size=151936, hidden_size=2048, num_hidden_layers=layers,
                                       num_attention_heads=16, num_key_value_heads=16, max_position_embeddings=8192,
@@ -391,12 +391,23 @@ def model_case(args, dev) -> None:
     greedy_decode(model, prompt, 4)                                  # warm-up: workspaces, autotuned attention
     runs = [greedy_decode(model, prompt, 32) for _ in range(3)]
     tpot = sorted(t for r in runs for t in r["tpot_ms"])
+    graphed = {}
+    try:                                            # the same loop with the decode step replayed from a CUDA graph
+        first = greedy_decode_graphed(model, prompt, 32)
+        more = [greedy_decode_graphed(model, prompt, 32, decoder=first["decoder"]) for _ in range(3)]
+        gt = sorted(t for r in more for t in r["tpot_ms"])
+        graphed = {"graphed_tpot_ms_p50": statistics.median(gt), "graphed_tpot_ms_p95": gt[int(0.95 * (len(gt) - 1))],
+                   "graphed_decode_tokens_per_s": 1e3 / statistics.median(gt),
+                   "graphed_ttft_ms": statistics.median(r["ttft_ms"] for r in more),
+                   "graphed_tokens_equal_eager": more[0]["tokens"] == runs[0]["tokens"]}
+    except Exception as exc:
+        graphed = {"graphed": f"capture failed: {type(exc).__name__}: {exc}"[:300]}
     print(json.dumps({"case": "model", "layers": layers, "policy": "all q4_group128" if args.variant == 1 else
                       "layers 0-15 bf16_le, 16-23 q8_group128", "prompt_tokens": 128, "new_tokens": 32,
                       "ttft_ms": statistics.median(r["ttft_ms"] for r in runs), "tpot_ms_p50": statistics.median(tpot),
                       "tpot_ms_p95": tpot[int(0.95 * (len(tpot) - 1))], "decode_tokens_per_s": 1e3 / statistics.median(tpot),
                       "expert_storage_bytes": host.evidence["expert_storage_bytes"],
-                      "tokens_equal_across_runs": all(r["tokens"] == runs[0]["tokens"] for r in runs)}))
+                      "tokens_equal_across_runs": all(r["tokens"] == runs[0]["tokens"] for r in runs), **graphed}))
     host.close()
 
 

@@ -74,3 +74,24 @@ def test_quantised_policy_stays_close_to_the_bf16_model():
         cos = torch.nn.functional.cosine_similarity(got["logits"][0], want, dim=0).item()
         assert cos > 0.98, cos
         assert len(got["tokens"]) == 3 and len(got["tpot_ms"]) == 2 and got["ttft_ms"] > 0
+
+
+def test_graphed_decode_equals_the_eager_loop():
+    """The decode step captured in a CUDA graph (static cache, arg-max and position update on the device) must
+    generate the tokens of the eager loop, twice in a row with the same decoder."""
+    from uma_qmoe_b200.host import greedy_decode, greedy_decode_graphed, install_quantized_blocks
+    model = _tiny("qwen")
+    prompt = torch.randint(0, 1024, (1, 20), generator=torch.Generator().manual_seed(9)).to(DEV)
+    with install_quantized_blocks(model, {0: "q8_group128", 1: "bf16_le"}):
+        eager = greedy_decode(model, prompt, 8)
+        first = greedy_decode_graphed(model, prompt, 8, keep_logits=True)
+        again = greedy_decode_graphed(model, prompt, 8, decoder=first["decoder"])
+        assert first["tokens"] == again["tokens"]
+        scale = eager["logits"].abs().max().item()
+        assert (first["logits"] - eager["logits"]).abs().max().item() <= 0.04 * scale + 4e-2
+        margin = eager["logits"].topk(2, dim=-1).values
+        decisive = (margin[:, 0] - margin[:, 1]) > 0.1 * scale          # steps whose arg-max is not a near-tie
+        prefix = 0
+        while prefix < 8 and eager["tokens"][prefix] == first["tokens"][prefix]:
+            prefix += 1
+        assert prefix == 8 or not bool(decisive[prefix]), (prefix, eager["tokens"], first["tokens"])

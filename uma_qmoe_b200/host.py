@@ -145,3 +145,100 @@ def greedy_decode(model: Any, input_ids: torch.Tensor, new_tokens: int) -> dict[
     steps = [marks[i].elapsed_time(marks[i + 1]) for i in range(1, new_tokens)]
     return {"tokens": torch.cat(tokens).tolist(), "logits": torch.cat(logits).cpu(),
             "ttft_ms": marks[0].elapsed_time(marks[1]), "tpot_ms": steps}
+
+
+class GraphedDecoder:
+    """Batch-1 decode with the whole step -- embedding, attention over a static key/value cache, the MoE blocks,
+    the LM head, the arg-max that picks the next token and the position increment -- captured once in a CUDA graph
+    and replayed per token, so that the host issues one launch per token instead of a few hundred (the reference's
+    host runs the step eagerly, ``benchmarks/runners/pytorch_reference_host.py:148-164``)."""
+
+    def __init__(self, model: Any, max_len: int) -> None:
+        from transformers import StaticCache
+
+        self.model = model
+        self.device = next(model.parameters()).device
+        self.cache = StaticCache(config=model.config, max_cache_len=max_len)
+        self.max_len = max_len
+        self.token = torch.zeros((1, 1), dtype=torch.long, device=self.device)        # next input token
+        self.position = torch.zeros((1,), dtype=torch.long, device=self.device)       # its position
+        self.graph: Any = None
+        self.logits: Any = None                                                          # logits of the last replay
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor) -> torch.Tensor:
+        tokens = input_ids.shape[1]
+        if tokens >= self.max_len:
+            raise RuntimeError("the prompt does not fit the static cache")
+        self.cache.reset()
+        out = self.model(input_ids=input_ids, past_key_values=self.cache,
+                         cache_position=torch.arange(tokens, device=self.device), use_cache=True)
+        logits = out.logits[:, -1].float()
+        self.token.copy_(logits.argmax(dim=-1)[:, None])
+        self.position.fill_(tokens)
+        return logits
+
+    @torch.no_grad()
+    def _step(self) -> torch.Tensor:
+        out = self.model(input_ids=self.token, past_key_values=self.cache, cache_position=self.position, use_cache=True)
+        logits = out.logits[:, -1].float()
+        self.token.copy_(logits.argmax(dim=-1)[:, None])
+        self.position.add_(1)
+        return logits
+
+    def capture(self) -> None:
+        """Capture one step (call after a prefill, and prefill again before generating: the two warm-up steps and
+        the capture run disturb the cache state)."""
+        token, position = self.token.clone(), self.position.clone()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._step()
+            self._step()
+            self.token.copy_(token)
+            self.position.copy_(position)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                self.logits = self._step()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self.token.copy_(token)
+        self.position.copy_(position)
+        self.graph = graph
+
+    def step(self) -> torch.Tensor:
+        """One token: returns the (static) logits tensor; ``self.token`` then holds the next input."""
+        if self.graph is None:
+            raise RuntimeError("capture() first")
+        self.graph.replay()
+        return self.logits
+
+
+@torch.no_grad()
+def greedy_decode_graphed(model: Any, input_ids: torch.Tensor, new_tokens: int, decoder: Any = None,
+                          keep_logits: bool = False) -> dict[str, Any]:
+    """:func:`greedy_decode` with the decode steps replayed from a CUDA graph; the only host synchronisation is the
+    one at the end."""
+    if input_ids.dim() != 2 or input_ids.shape[0] != 1 or new_tokens < 1:
+        raise RuntimeError("greedy_decode_graphed takes one prompt [1, T] and at least one new token")
+    dec = decoder or GraphedDecoder(model, input_ids.shape[1] + new_tokens + 8)
+    if dec.graph is None:
+        # one-off: a throw-away prefill gives the capture a populated cache; the warm-up and capture runs leave
+        # the cache and the library's host-side counters in a state that only a fresh prefill resets, so the
+        # generation below always starts with its own prefill
+        dec.prefill(input_ids)
+        dec.capture()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(new_tokens + 1)]
+    marks[0].record()
+    logits = [dec.prefill(input_ids)]
+    tokens = [dec.token.clone()]
+    marks[1].record()
+    for step in range(1, new_tokens):
+        out = dec.step()
+        if keep_logits:
+            logits.append(out.clone())
+        tokens.append(dec.token.clone())
+        marks[step + 1].record()
+    torch.cuda.synchronize()
+    return {"tokens": torch.cat(tokens, dim=1)[0].tolist(), "logits": torch.cat(logits).cpu(),
+            "ttft_ms": marks[0].elapsed_time(marks[1]),
+            "tpot_ms": [marks[i].elapsed_time(marks[i + 1]) for i in range(1, new_tokens)], "decoder": dec}
