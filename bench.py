@@ -331,21 +331,28 @@ def kernel_case(args) -> None:
     torch.cuda.set_device(dev)
     if args.only == "model":
         return model_case(args, dev)
-    shape = syn.OLMOE
-    stack = MoEStack.build(shape, "q4_group128", args.layers, SEED, dev, renormalize=True, skew=1.0)
+    qwen = args.only == "decode" and args.model == "qwen"
+    shape = syn.QWEN if qwen else syn.OLMOE
+    stack = MoEStack.build(shape, "q8_group128" if qwen else "q4_group128", args.layers, SEED, dev,
+                           renormalize=not qwen, skew=1.0)
     if args.only == "decode":
+        # BASELINE config 0 (OLMoE layer, Q4) or config 2 (Qwen layer: Q8 routed experts, BF16 shared expert + gate)
+        from uma_qmoe_b200.stack import random_shared_expert
+        shared = [random_shared_expert(shape, SEED + l, dev) for l in range(args.layers)] if qwen else None
+        nbytes = (4 * 8_921_088 + 69_206_016 + 4_096 + 8_192) if qwen else DECODE_BYTES
         x = syn.activations(SEED, 1).to(dev)
         routes = [stack.route(l, x) for l in range(args.layers)]
-        ws = ops.decode_workspace(stack.layers[0], shape.top_k, None, dev)
+        ws = ops.decode_workspace(stack.layers[0], shape.top_k, shared[0] if qwen else None, dev)
         out = torch.empty_like(x)
 
         def run():
             for l in range(args.layers):
-                ops.moe_decode(stack.layers[l], x, routes[l][1], routes[l][0], ws, out=out)
+                ops.moe_decode(stack.layers[l], x, routes[l][1], routes[l][0], ws, shared[l] if qwen else None, out=out)
         ms = timed(run, args.steps, args.warmup, 1) / args.layers
         msg = timed(graphed(run), args.steps, args.warmup, 1) / args.layers
-        print(json.dumps({"case": "decode", "us_per_layer_eager": ms * 1e3, "us_per_layer": msg * 1e3,
-                          "gbs": DECODE_BYTES / (msg / 1e3) / 1e9, "status": ops.workspace_status(ws)}))
+        print(json.dumps({"case": "decode", "model": args.model, "bytes_per_layer": nbytes,
+                          "us_per_layer_eager": ms * 1e3, "us_per_layer": msg * 1e3,
+                          "gbs": nbytes / (msg / 1e3) / 1e9, "status": ops.workspace_status(ws)}))
     else:
         x = syn.activations(SEED, args.tokens).to(dev)
         w, idx = stack.route(0, x)
@@ -421,6 +428,8 @@ def main() -> None:
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")
+    ap.add_argument("--model", choices=("olmoe", "qwen"), default="olmoe",
+                    help="layer shape of the --only decode case: olmoe = config 0 (Q4), qwen = config 2 (Q8 + shared)")
     ap.add_argument("--variant", type=int, default=0, choices=(0, 1, 2),
                     help="grouped GEMM kernel of the --only gemm case: 0/1 one CTA per tile (default), 2 CTA pairs")
     args = ap.parse_args()

@@ -99,7 +99,6 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared, c
   p.out = static_cast<__nv_bfloat16*>(out_bf16);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.sync = reinterpret_cast<unsigned*>(ws);
-  p.amax = reinterpret_cast<unsigned*>(ws + 64);
   p.inter_buf = reinterpret_cast<float*>(ws + kDecodeWsHeader);
   return launch_moe_decode(p, static_cast<cudaStream_t>(stream));
 }

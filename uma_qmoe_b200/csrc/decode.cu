@@ -801,7 +801,6 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
     set_error("decode: quantised layer without scales");
     return ERR_BAD_ARGUMENT;
   }
-  p.inter_total = p.top_k * p.inter + (p.sh_gate ? p.shared_inter : 0);
   const size_t smem_a = gateup_smem(p), smem_b = down_smem(p);
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -930,7 +929,6 @@ extern "C" int umaq_moe_decode_static(const umaq_layer* layer, const umaq_shared
   p.out = static_cast<__nv_bfloat16*>(out_bf16);
   uint8_t* ws = static_cast<uint8_t*>(scratch);
   p.sync = reinterpret_cast<unsigned*>(ws);
-  p.amax = reinterpret_cast<unsigned*>(ws + 64);
   p.inter_buf = reinterpret_cast<float*>(ws + kDecodeWsHeader);
   return launch_moe_decode(p, st);
 }

@@ -1,4 +1,4 @@
-// Parameter block and host launcher of the batch-1 decode kernel (decode.cu).
+// Parameter block and host launcher of the batch-1 decode kernels (decode.cu).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -8,11 +8,11 @@
 
 namespace umaq {
 
-// Workspace layout (bytes): [0,1024) header -- the uint32 at byte 8 is the sticky status word, the
-// uint32 words from byte 64 count finished gate/up tiles per slot (self-resetting); [1024,...) one run
-// per slot (routed slots in route order, then the shared expert) that first holds the float32
-// intermediate and then, in place, its fragment record.
-// Must be zero before its first use.
+// Workspace layout (bytes): [0,1024) header -- the uint32 at byte 8 is the sticky status word;
+// [1024,...) 4 * intermediate bytes per slot (routed slots in route order, then the shared expert) that
+// hold the record the gate/up kernel leaves for the down kernel (fp16 fragments in 32-value chunks with
+// their prescales and bias sums, or the BF16 vector for BF16 rows).  The header must be zero before the
+// first use.
 constexpr size_t kDecodeWsHeader = 1024;
 
 struct DecodeParams {
@@ -41,17 +41,12 @@ struct DecodeParams {
   int shared_inter;
   __nv_bfloat16* out;         // [hidden]
   // workspace
-  unsigned* sync;             // control words
-  unsigned* amax;             // [2][16]
-  float* inter_buf;
-  // derived by the launcher
-  int inter_total;            // sum of intermediate sizes over slots
-  int stage_bytes;            // weight bytes per ring stage (16 rows x slice)
-  int nstages;
+  unsigned* sync;             // header words; sync[2] is the status word
+  float* inter_buf;           // the slots' records (4 * intermediate bytes apart)
 };
 
 size_t decode_workspace_bytes(int top_k, int inter, int shared_inter);
-// Fills the derived fields, checks shapes and launches cooperatively on `stream`.
+// Checks the shapes and launches the two kernels on `stream`.
 int launch_moe_decode(DecodeParams p, cudaStream_t stream);
 
 }  // namespace umaq
