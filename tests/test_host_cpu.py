@@ -136,3 +136,52 @@ def test_host_codecs_reproduce_the_golden_bytes(golden_dir):
             assert back.shape == v.shape and np.isfinite(back).all()
             bound = np.abs(v).max() / (7 if packed is q4 else 127) if packed is not bf else np.abs(v).max() * 2 ** -8
             assert np.abs(back - v).max() <= bound + 1e-12
+
+
+def test_unregister_waits_for_the_call_in_flight_and_refuses_new_calls():
+    """``src/uma_qmoe`` lifecycle contract (the reference's ``test_custom_operator_lifecycle.py:37-67``): closing a
+    handle blocks until the active call has left, and nobody can enter in between."""
+    import threading
+    handle = custom_op.register_expert_pack(_Reader())
+    entered, release, closed = threading.Event(), threading.Event(), threading.Event()
+
+    def call():
+        with custom_op.acquire_expert_pack(handle):
+            entered.set()
+            assert release.wait(timeout=5)
+
+    def close():
+        custom_op.unregister_expert_pack(handle)
+        closed.set()
+
+    worker, closer = threading.Thread(target=call), threading.Thread(target=close)
+    worker.start()
+    assert entered.wait(timeout=5)
+    closer.start()
+    assert not closed.wait(timeout=0.1)
+    with pytest.raises(RuntimeError, match="unknown or closed"):
+        with custom_op.acquire_expert_pack(handle):
+            pass
+    release.set()
+    worker.join(timeout=5)
+    closer.join(timeout=5)
+    assert not worker.is_alive() and not closer.is_alive() and closed.is_set()
+
+
+def test_backend_needs_every_entry_point_and_drops_the_caches_of_a_closed_pack():
+    from types import SimpleNamespace
+    from uma_qmoe_b200.native_backend import MixedTargetNativeBackend, PackedQ4NativeBackend
+    with pytest.raises(ContractError, match="unsupported native platform"):
+        MixedTargetNativeBackend("cuda_sm121", _native.lib())
+    partial = SimpleNamespace(**{name: None for name in list(_native.SIGNATURES)[:-1]})
+    with pytest.raises(ContractError, match="does not export"):
+        MixedTargetNativeBackend("cuda_sm100", partial)
+    backend = PackedQ4NativeBackend("cuda_sm100", _native.lib())
+    assert backend.allowed_encodings == ("q4_group128",)
+    layer = SimpleNamespace(num_experts=64, device_storage_bytes=10)
+    backend.preload_layer(1, 0, "cuda:0", layer)
+    backend.preload_layer(1, 5, "cuda:0", layer)
+    backend.preload_layer(2, 0, "cuda:0", layer)
+    assert backend.cache_summary() == {"tensor_count": 3 * 64 * 3, "device_storage_bytes": 30, "dequantized_weight_bytes": 0}
+    backend.release_pack(1)
+    assert backend.cache_summary()["device_storage_bytes"] == 10

@@ -188,3 +188,38 @@ def test_large_batch_prefill_matches_the_pair_kernel_and_the_oracle():
     sample = torch.arange(0, tokens, 512)
     want = orc.moe_forward(x[sample], idx[sample], w[sample], src, num_experts=experts, top_k=8, qwen=False)
     assert_parity(y[sample], want)
+
+
+def test_operator_edge_shapes_through_the_registered_backend():
+    """The public operator on an empty batch, on one token (decode kernels) and on two tokens (prefill kernels):
+    same pack, results consistent with each other."""
+    from uma_qmoe_b200 import custom_op, native_backend
+    from uma_qmoe_b200.packs import InMemoryPack, expert_tensor_name
+    from uma_qmoe_b200.formats import encode
+    pack = InMemoryPack({0: "q4_group128"})
+    packed = {}                                      # 8 distinct experts, repeated to fill the layer's 64
+    for e in range(8):
+        for proj, m in zip(("gate_proj", "up_proj", "down_proj"), syn.expert_weights(SEED, 0, e, syn.OLMOE)):
+            packed[e, proj] = encode(m, "q4_group128")
+    for e in range(64):
+        for proj in ("gate_proj", "up_proj", "down_proj"):
+            pack.add_packed(expert_tensor_name(0, e, proj), packed[e % 8, proj])
+    native_backend.install_mixed_target_backend()
+    handle = custom_op.register_expert_pack(pack)
+    try:
+        x = syn.activations(SEED + 3, 2).to(DEV)
+        idx = torch.tensor([[0, 1, 2, 3, 4, 5, 6, 7], [7, 6, 5, 4, 3, 2, 1, 0]], device=DEV)
+        w = torch.full((2, 8), 0.125, device=DEV)
+        both = torch.ops.uma_qmoe.moe_forward(x, idx, w, 0, handle, True)
+        one = torch.ops.uma_qmoe.moe_forward(x[:1], idx[:1], w[:1], 0, handle, True)
+        none = torch.ops.uma_qmoe.moe_forward(x[:0], idx[:0], w[:0], 0, handle, True)
+        assert none.shape == (0, 2048) and none.dtype == torch.bfloat16
+        assert_parity(one.cpu(), both[:1].cpu(), max_abs=4e-3)
+        three_d = torch.ops.uma_qmoe.moe_forward(x.reshape(1, 2, 2048), idx, w, 0, handle, True)
+        assert three_d.shape == (1, 2, 2048) and torch.equal(three_d.reshape(2, 2048), both)
+        with pytest.raises(RuntimeError, match=r"requires \[tokens, 8\] routes"):
+            torch.ops.uma_qmoe.moe_forward(x, idx[:, :4], w[:, :4], 0, handle, True)
+        with pytest.raises(RuntimeError, match="layer_index must be in"):
+            torch.ops.uma_qmoe.moe_forward(x, idx, w, 16, handle, True)
+    finally:
+        custom_op.unregister_expert_pack(handle)

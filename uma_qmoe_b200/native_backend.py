@@ -217,6 +217,8 @@ class MixedTargetNativeBackend:
         weights = routing_weights.to(dtype=torch.float32).contiguous()     # float32 routing weights, no BF16 rounding
         tokens = flat.shape[0]
         out = torch.empty_like(flat)
+        if tokens == 0:                       # an empty batch has an empty result; there is nothing to launch
+            return out.reshape(hidden_states.shape)
         if tokens == 1:
             ws = self._workspace("decode", layer, 1, top_k, shared, hidden_states.device)
             ops.moe_decode(layer, flat, indices, weights, ws, shared, out=out)
