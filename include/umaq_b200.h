@@ -191,6 +191,11 @@ int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, l
  * slots keep meta -1, which every kernel of this library treats as an absent route; routes beyond
  * the capacity get route_slot -1 and set *overflow (device int, sticky; the caller then repeats the
  * layer with exact counts). */
+/* Expert-parallel routing table (no counterpart in the reference): local_ids[i] = local expert id of
+ * expert_indices[i] on rank `rank`, or -1 (absent route) when another rank owns the expert.
+ * placement 0: expert e on rank e % ranks as local e / ranks; 1: rank e / experts_per_rank, local e % experts_per_rank. */
+int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long long count, int ranks, int rank,
+                      int experts_per_rank, int placement, int* local_ids, void* stream);
 int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                  const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
                  void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream);

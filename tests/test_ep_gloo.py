@@ -57,6 +57,11 @@ class TorchKernels:
         out = (rows.float() * (s * weight)[:, None]).to(torch.bfloat16)
         return torch.where(present[:, None], out, torch.zeros_like(out))
 
+    def local_ids(self, indices, ranks, rank, per_rank, interleaved):
+        idx = indices.to(torch.int32)
+        mine, local = (idx % ranks == rank, idx // ranks) if interleaved else (idx // per_rank == rank, idx % per_rank)
+        return torch.where(mine, local, torch.full_like(local, -1))
+
     def local_moe(self, x, local_indices, weights):
         """umaq_moe_prefill with absent routes: ordered BF16 running sum over the present local experts."""
         t, k = local_indices.shape

@@ -173,6 +173,13 @@ int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, l
   return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
+int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long long count, int ranks, int rank,
+                       int experts_per_rank, int placement, int* local_ids, void* stream) {
+  if (!expert_indices || !local_ids) { set_error("umaq_ep_local_ids: null argument"); return ERR_BAD_ARGUMENT; }
+  return launch_ep_local_ids(expert_indices, indices_are_int64, count, ranks, rank, experts_per_rank, placement, local_ids,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                  const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
                  void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream) {

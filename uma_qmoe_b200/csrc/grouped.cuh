@@ -82,6 +82,8 @@ int launch_dense_tiles(int rows, int* num_tiles, int* tile_expert, int* tile_row
 // valid_rows (device, may be null): only the first *valid_rows sorted routes exist
 int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_k, long long routes, int hidden,
                        int permute, __nv_bfloat16* out, const int* valid_rows, cudaStream_t stream);
+int launch_ep_local_ids(const void* indices, int idx64, long long n, int ranks, int rank, int per_rank, int placement,
+                        int* out, cudaStream_t stream);
 int launch_ep_pack(const __nv_bfloat16* x, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                    const int* offsets, int routes, int top_k, int hidden, int ranks, int per_rank, int capacity,
                    __nv_bfloat16* send_rows, int* send_meta, int* route_slot, int* overflow, cudaStream_t stream);

@@ -727,6 +727,31 @@ int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64
   return check_launch("combine");
 }
 
+// ---- expert-parallel routing: global expert id -> this rank's local id, or -1 (absent) --------------------------
+// placement 0: expert e lives on rank e % ranks as local expert e / ranks; 1: rank e / per_rank, local e % per_rank.
+__global__ void ep_local_ids_kernel(const void* __restrict__ indices, int idx64, long long n, int ranks, int rank,
+                                    int per_rank, int placement, int* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int e = load_expert(indices, idx64, i);
+  int local = -1;
+  if (e >= 0 && e < ranks * per_rank) {
+    if (placement == 0) { if (e % ranks == rank) local = e / ranks; }
+    else if (e / per_rank == rank) local = e % per_rank;
+  }
+  out[i] = local;
+}
+
+int launch_ep_local_ids(const void* indices, int idx64, long long n, int ranks, int rank, int per_rank, int placement,
+                        int* out, cudaStream_t stream) {
+  if (n <= 0 || ranks < 1 || rank < 0 || rank >= ranks || per_rank < 1 || (placement != 0 && placement != 1)) {
+    set_error("ep local ids: bad argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  ep_local_ids_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(indices, idx64, n, ranks, rank, per_rank, placement, out);
+  return check_launch("ep local ids");
+}
+
 int launch_ep_pack(const __nv_bfloat16* x, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                    const int* offsets, int routes, int top_k, int hidden, int ranks, int per_rank, int capacity,
                    __nv_bfloat16* send_rows, int* send_meta, int* route_slot, int* overflow, cudaStream_t stream) {

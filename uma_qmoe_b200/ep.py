@@ -80,6 +80,9 @@ class CudaKernels:
     def combine(self, weighted: torch.Tensor, indices: torch.Tensor, route_pos: torch.Tensor) -> torch.Tensor:
         return self.ops.combine_routes(weighted, indices, route_pos)
 
+    def local_ids(self, indices: torch.Tensor, ranks: int, rank: int, per_rank: int, interleaved: bool) -> torch.Tensor:
+        return self.ops.ep_local_ids(indices, ranks, rank, per_rank, interleaved)
+
     def local_moe(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """This rank's experts over all rows of x; local_indices -1 = the route belongs to another rank."""
         n, top_k = local_indices.shape
@@ -174,15 +177,6 @@ class ExpertParallelMoE:
         dist.all_to_all_single(back, done, group=self.group)
         return k.combine(back, indices, route_slot)
 
-    def local_ids(self, indices: torch.Tensor) -> torch.Tensor:
-        """Local expert id where this rank owns the expert, -1 (absent) elsewhere; int32."""
-        idx = indices.to(torch.int32)
-        if self.placement == "interleaved":
-            mine, local = idx % self.world == self.rank, idx // self.world
-        else:
-            mine, local = idx // self.per_rank == self.rank, idx % self.per_rank
-        return torch.where(mine, local, torch.full_like(local, -1))
-
     def forward_gather(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """All-gather the rows, run the local experts over all of them, all-to-all the partial sums back."""
         k = self.kernels
@@ -190,18 +184,18 @@ class ExpertParallelMoE:
         g = self.world
         if self._gather is None or self._gather[0].shape[0] != g * t or self._gather[0].device != x.device:
             self._gather = (x.new_empty((g * t, x.shape[1])),
-                            torch.empty((g * t, 2 * top_k), dtype=torch.int32, device=x.device),
+                            (torch.empty((g * t, top_k), dtype=indices.dtype, device=x.device),
+                             torch.empty((g * t, top_k), dtype=torch.float32, device=x.device)),
                             x.new_empty((g * t, x.shape[1])),
                             torch.arange(g, dtype=torch.int32, device=x.device).repeat(t, 1).contiguous(),
                             (torch.arange(g, dtype=torch.int32, device=x.device)[None, :] * t +
                              torch.arange(t, dtype=torch.int32, device=x.device)[:, None]).contiguous())
-        all_x, all_meta, parts, rank_ids, part_pos = self._gather
-        # one record per token: its k expert ids and the bits of its k float32 weights
-        meta = torch.cat((indices.to(torch.int32), weights.contiguous().view(torch.int32)), dim=1)
+        all_x, (all_idx, all_w), parts, rank_ids, part_pos = self._gather
         dist.all_gather_into_tensor(all_x, x.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(all_meta, meta, group=self.group)
-        local = self.local_ids(all_meta[:, :top_k])
-        partial = k.local_moe(all_x, local, all_meta[:, top_k:].contiguous().view(torch.float32))
+        dist.all_gather_into_tensor(all_idx, indices.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(all_w, weights.contiguous(), group=self.group)
+        local = k.local_ids(all_idx, g, self.rank, self.per_rank, self.placement == "interleaved")
+        partial = k.local_moe(all_x, local, all_w)
         dist.all_to_all_single(parts, partial, group=self.group)      # parts[r * t + i] = rank r's sum for my token i
         return k.combine(parts, rank_ids, part_pos)
 

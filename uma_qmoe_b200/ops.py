@@ -227,6 +227,18 @@ def grouped_gemm(layer: DeviceLayer, mode: int, act: torch.Tensor, routes: Sorte
     return out
 
 
+def ep_local_ids(indices: torch.Tensor, ranks: int, rank: int, experts_per_rank: int, interleaved: bool) -> torch.Tensor:
+    """int32 local expert ids of the routes this rank owns, -1 elsewhere (see ``umaq_ep_local_ids``)."""
+    if not indices.is_cuda or indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("expert_indices must be a CUDA int32 or int64 tensor")
+    idx = indices.contiguous()
+    out = torch.empty(idx.shape, dtype=torch.int32, device=idx.device)
+    code = _native.lib().umaq_ep_local_ids(idx.data_ptr(), int(idx.dtype == torch.int64), idx.numel(), ranks, rank,
+                                           experts_per_rank, 0 if interleaved else 1, out.data_ptr(), _stream(idx.device))
+    _native.check(code, "umaq_ep_local_ids")
+    return out
+
+
 def ep_pack(hidden: torch.Tensor, routes: SortedRoutes, sorted_key: torch.Tensor, top_k: int, ranks: int,
             experts_per_rank: int, capacity: int, send_rows: torch.Tensor, send_meta: torch.Tensor,
             overflow: torch.Tensor) -> torch.Tensor:
