@@ -19,6 +19,7 @@ per projection; nothing is dequantised, ``dequantized_weight_bytes`` stays 0.
 from __future__ import annotations
 
 import threading
+import warnings
 from pathlib import Path
 from typing import Any, Optional
 
@@ -134,9 +135,11 @@ class MixedTargetNativeBackend:
                         raise RuntimeError(f"tensor of layer {layer_index} is not {encoding}")
                     if len(data) != nbytes:
                         raise RuntimeError("pack tensor byte count does not match its shape")
-                    host[e].copy_(torch.frombuffer(data, dtype=torch.uint8))
-                    if quantised:
-                        host_s[e].copy_(torch.frombuffer(scales, dtype=torch.float32))
+                    with warnings.catch_warnings():       # the mapping is read-only and is only read here
+                        warnings.filterwarnings("ignore", message="The given buffer is not writable")
+                        host[e].copy_(torch.frombuffer(data, dtype=torch.uint8))
+                        if quantised:
+                            host_s[e].copy_(torch.frombuffer(scales, dtype=torch.float32))
                 finally:
                     data.release()
                     scales.release()
