@@ -506,23 +506,40 @@ __global__ void __launch_bounds__(kSortThreads) route_place_kernel(const SortArg
 }
 
 // ---- gather: sorted_x[i] = x[sorted_route[i] / top_k], optionally in the permuted K order ------------------
-__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route, int top_k,
-                                   long long routes, int hidden, int permute, __nv_bfloat16* __restrict__ out,
-                                   const int* __restrict__ valid_rows) {
-  const long long i = blockIdx.x;
+// One warp per row, eight rows per CTA; a lane keeps up to eight 16-byte loads in flight before it stores.
+constexpr int kGatherRows = 8;
+__global__ void __launch_bounds__(kGatherRows * 32)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_route, int top_k,
+                   long long routes, int hidden, int permute, __nv_bfloat16* __restrict__ out,
+                   const int* __restrict__ valid_rows) {
+  const long long i = (long long)blockIdx.x * kGatherRows + (threadIdx.x >> 5);
   if (i >= routes || (valid_rows && i >= *valid_rows)) return;     // fewer present routes than the launch covers
+  const int lane = threadIdx.x & 31;
   const int token = sorted_route ? sorted_route[i] / top_k : (int)i;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)token * hidden);
   uint4* dst = reinterpret_cast<uint4*>(out + (size_t)i * hidden);
-  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
-    uint4 w = src[v];
-    if (permute) {
-      // (e0,e1)(e2,e3)(e4,e5)(e6,e7) -> (e0,e4)(e1,e5)(e2,e6)(e3,e7)
-      const uint32_t a = w.x, b = w.y, c = w.z, d = w.w;
-      w.x = prmt(a, c, 0x5410); w.y = prmt(a, c, 0x7632);
-      w.z = prmt(b, d, 0x5410); w.w = prmt(b, d, 0x7632);
+  const int words = hidden / 8;
+  for (int base = 0; base < words; base += 256) {
+    uint4 w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int v = base + j * 32 + lane;
+      if (v < words) w[j] = src[v];
     }
-    dst[v] = w;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int v = base + j * 32 + lane;
+      if (v < words) {
+        uint4 q = w[j];
+        if (permute) {
+          // (e0,e1)(e2,e3)(e4,e5)(e6,e7) -> (e0,e4)(e1,e5)(e2,e6)(e3,e7)
+          const uint32_t a = q.x, b = q.y, c = q.z, d = q.w;
+          q.x = prmt(a, c, 0x5410); q.y = prmt(a, c, 0x7632);
+          q.z = prmt(b, d, 0x5410); q.w = prmt(b, d, 0x7632);
+        }
+        dst[v] = q;
+      }
+    }
   }
 }
 
@@ -560,7 +577,7 @@ __global__ void ep_pack_kernel(const __nv_bfloat16* __restrict__ x, const int* _
 // contributions are already BF16 (GEMM 2 epilogue).  With a shared expert: + bf16(sigmoid(bf16(x . wg))
 // * shared_out[t]), as QuantizedQwenMoEBlock does after the operator
 // (src/uma_qmoe/qwen_compressed_loader.py:82-85).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restrict__ indices, int idx64,
                const int* __restrict__ route_pos, int top_k, int hidden, const __nv_bfloat16* __restrict__ shared_out,
                const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_vec,
@@ -608,14 +625,15 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
   __syncthreads();
   // all of a column pair's contributions are loaded first (independent loads), then summed in order
   const int n = present;
-  const __nv_bfloat16* rows[8];
+  unsigned rows[8];                               // row starts in 16-byte words (fewer registers than pointers)
 #pragma unroll
-  for (int s = 0; s < 8; ++s) rows[s] = weighted + (size_t)order_pos[s < n ? s : 0] * hidden;
+  for (int s = 0; s < 8; ++s) rows[s] = (unsigned)(((size_t)order_pos[s < n ? s : 0] * hidden) >> 3);
+  const uint4* wbase = reinterpret_cast<const uint4*>(weighted);
   for (int c = tid * 8; c < hidden; c += 2048) {        // 16 bytes per thread and row (hidden % 8 == 0)
     uint4 v[8];
 #pragma unroll
     for (int s = 0; s < 8; ++s)
-      if (s < n) v[s] = *reinterpret_cast<const uint4*>(rows[s] + c);
+      if (s < n) v[s] = wbase[rows[s] + (c >> 3)];
     float r[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) r[e] = 0.f;
@@ -715,7 +733,8 @@ int launch_route_sort(const SortArgs& a, cudaStream_t stream) {
 int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_k, long long routes, int hidden,
                        int permute, __nv_bfloat16* out, const int* valid_rows, cudaStream_t stream) {
   if (routes <= 0 || hidden % 8 || routes > 0x7fffffffLL) { set_error("gather: unsupported shape"); return ERR_BAD_ARGUMENT; }
-  gather_rows_kernel<<<(unsigned)routes, 128, 0, stream>>>(x, sorted_route, top_k, routes, hidden, permute, out, valid_rows);
+  gather_rows_kernel<<<(unsigned)((routes + kGatherRows - 1) / kGatherRows), kGatherRows * 32, 0, stream>>>(
+      x, sorted_route, top_k, routes, hidden, permute, out, valid_rows);
   return check_launch("gather");
 }
 
