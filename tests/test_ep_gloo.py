@@ -149,11 +149,11 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _run(placement, fixed):
+def _run(placement, fixed, world=2):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out, placement, fixed)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out, placement, fixed)) for r in range(world)]
     for p in procs:
         p.start()
     got = out.get(timeout=90)
@@ -187,16 +187,16 @@ def test_overflow_is_reported_and_the_exact_path_recovers():
     assert np.array_equal(got, _single_rank().float().numpy())
 
 
-@pytest.mark.timeout(120)
-@pytest.mark.parametrize("placement", ["interleaved", "contiguous"])
-def test_gather_exchange_is_the_rank_ordered_sum_of_per_rank_sums(placement):
+@pytest.mark.timeout(180)
+@pytest.mark.parametrize("placement,world", [("interleaved", 2), ("contiguous", 2), ("interleaved", 4)])
+def test_gather_exchange_is_the_rank_ordered_sum_of_per_rank_sums(placement, world):
     """forward_gather regroups the BF16 running sum by rank: equal to the single-rank result up to the
     rounding of that regrouping, and exactly equal to the regrouped sum computed directly."""
-    got, _ = _run(placement, "gather")
+    got, _ = _run(placement, "gather", world)
     x, idx, w, scale = _inputs()
     want = torch.zeros((TOKENS, HIDDEN), dtype=torch.bfloat16)
-    for r in range(2):
-        owned = idx % 2 == r if placement == "interleaved" else idx // (EXPERTS // 2) == r
+    for r in range(world):
+        owned = idx % world == r if placement == "interleaved" else idx // (EXPERTS // world) == r
         local = torch.where(owned, idx, torch.full_like(idx, -1))
         part = TorchKernels(scale).local_moe(x, local, w)
         want = (want.float() + part.float()).to(torch.bfloat16)
