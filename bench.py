@@ -12,8 +12,9 @@ from HBM.  With N ranks the experts and the tokens are split N ways (strong scal
 One JSON line on rank 0.  `value` = tokens/s with inputs resident on the device; `e2e` = the same
 through torch.ops.uma_qmoe.moe_forward with the step's activations coming from pinned host memory
 and the result read back; `roofline` = the gate/up grouped GEMM alone (tensor-bound) and `decode`
-= the batch-1 decode kernels rotating over the 16 layers, replayed from a CUDA graph (HBM-bound); `cpu_baseline` = the CPU
-oracle (a port of the reference's correctness path) timed on a bounded sample on this host.
+= the batch-1 decode kernels rotating over the 16 layers, replayed from a CUDA graph (HBM-bound); `cpu_baseline` = the
+reference's own CPU correctness path (the package installed under oracle/_ref by oracle/make_ref.py; the port in
+oracle/ only if that is absent, `kind` says which) timed on one full-size call of layer 0 on this host.
 `--impl reference` times that CPU path as the measured arm.
 """
 
@@ -128,64 +129,121 @@ def timed(fn, steps: int, warmup: int, world: int) -> float:
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU oracle arm
+# CPU arm: the reference's own correctness path (oracle/_ref), else this repository's port of it
 # ---------------------------------------------------------------------------------------------
 
-def cpu_sample(sample_tokens: int):
-    """A bounded sample of the workload for the CPU path: the first `sample_tokens` tokens through
-    layer 0 (its 64 experts quantised on the host with the oracle's packer)."""
+def _layer0_inputs(tokens: int):
     from oracle import moe_oracle as orc
     from uma_qmoe_b200 import synthetic as syn
-
     shape = syn.OLMOE
-    x = syn.activations(SEED, sample_tokens)
+    x = syn.activations(SEED, TOKENS)[:tokens].contiguous()
     wr = syn.router_weight(SEED, 0, shape, skew=1.0)
-    _p, w, idx = orc.router_topk(x, wr, shape.top_k, True)
+    return orc, syn, shape, x, wr
+
+
+def reference_layer_call(tokens: int):
+    """-> (callable running layer 0 on `tokens` tokens once, kind, cleanup).  kind "reference": the
+    UMA-QMoE package installed under oracle/_ref (oracle/make_ref.py) runs its own
+    torch.ops.uma_qmoe.moe_forward(..., performance_mode=False) on an ExpertPack its own writer made
+    (all 64 experts of layer 0, packed Q4 group-128).  kind "port": oracle/moe_oracle.py."""
+    import tempfile
+    orc, syn, shape, x, wr = _layer0_inputs(tokens)
+    ref_dir = ROOT / "oracle" / "_ref"
+    if (ref_dir / "uma_qmoe" / "custom_op.py").exists():
+        try:
+            sys.path.insert(0, str(ref_dir))
+            from uma_qmoe import custom_op as ref_op
+            from uma_qmoe.expert_pack import ExpertPackReader, write_expert_pack
+
+            def stream():
+                for e in range(shape.experts):
+                    for proj, m in zip(("gate", "up", "down"), syn.expert_weights(SEED, 0, e, shape)):
+                        yield f"model.layers.0.mlp.experts.{e}.{proj}_proj.weight", m
+            tmp = Path(tempfile.mkdtemp(prefix="umaq_ref_"))
+            path = tmp / "layer0.uqmoepk"
+            write_expert_pack(path, stream(), model_id="allenai/OLMoE-1B-7B-0125", model_revision="0" * 40,
+                              model_manifest_sha256="0" * 64)
+            ref_op.register_moe_forward()
+            reader = ExpertPackReader(path)
+            handle = ref_op.register_expert_pack(reader)
+
+            def call():
+                # the Hugging Face router's arithmetic (BF16 logits, float32 softmax, top-k, renormalise), then the op
+                logits = torch.nn.functional.linear(x, wr)
+                probs = torch.softmax(logits, dim=-1, dtype=torch.float)
+                w, idx = torch.topk(probs, shape.top_k, dim=-1)
+                w = w / w.sum(dim=-1, keepdim=True)
+                return torch.ops.uma_qmoe.moe_forward(x, idx, w, 0, handle, False)
+
+            def cleanup():
+                ref_op.unregister_expert_pack(handle)
+                reader.close()
+                path.unlink(missing_ok=True)
+            return call, "reference", cleanup
+        except Exception as exc:                     # say why the port is used instead
+            print(f"bench: oracle/_ref unusable ({type(exc).__name__}: {exc}); timing the port", file=sys.stderr)
     cache: dict[int, tuple] = {}
 
     def experts(e: int):
         if e not in cache:
             cache[e] = tuple(orc.encode_matrix(m, "q4_group128") for m in syn.expert_weights(SEED, 0, e, shape))
         return cache[e]
-
-    for e in sorted(set(idx.reshape(-1).tolist())):
+    for e in range(shape.experts):
         experts(e)                                  # packing is offline work, not part of the timed call
 
     def call():
         _pp, ww, ii = orc.router_topk(x, wr, shape.top_k, True)
         return orc.moe_forward(x, ii, ww, experts, num_experts=64, top_k=8, qwen=False)
+    return call, "port", lambda: None
 
-    return call
+
+def run_cpu(tokens: int, steps: int, warmup: int, budget_s: float) -> dict:
+    """Times layer 0 of the stack on `tokens` tokens (one call = the router and the CPU correctness path over
+    every hit expert), at most `steps` times and for at most `budget_s` seconds; the step time is that x 16
+    layers (the layers are alike; stated as an extrapolation over layers only)."""
+    call, kind, cleanup = reference_layer_call(tokens)
+    try:
+        for _ in range(warmup):
+            call()
+        times = []
+        t_begin = time.perf_counter()
+        while len(times) < steps and (not times or time.perf_counter() - t_begin + times[-1] < budget_s):
+            t0 = time.perf_counter()
+            call()
+            times.append(time.perf_counter() - t0)
+    finally:
+        cleanup()
+    per_layer = statistics.median(times)
+    return {"value": tokens / (per_layer * LAYERS), "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+            "seconds_per_layer_call": per_layer, "calls_timed": len(times), "sample_tokens": tokens,
+            "sample": f"layer 0 of {LAYERS} on {'all ' if tokens == TOKENS else 'the first '}{tokens} of the {TOKENS} tokens "
+                      f"(router + CPU correctness path over all 64 experts), {len(times)} call(s) timed, "
+                      f"step time = median x {LAYERS} layers (extrapolated over layers only)"}
 
 
-def run_cpu(sample_tokens: int, steps: int, warmup: int) -> dict:
-    call = cpu_sample(sample_tokens)
-    for _ in range(warmup):
-        call()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        call()
-    per_layer = (time.perf_counter() - t0) / steps
-    return {"value": sample_tokens / (per_layer * LAYERS), "unit": UNIT, "cores": torch.get_num_threads(),
-            "kind": "port", "seconds_per_layer_call": per_layer,
-            "sample": f"first {sample_tokens} of the {TOKENS} tokens through layer 0 of {LAYERS} "
-                      f"(router + CPU correctness path), time x {LAYERS} layers"}
+def cpu_baseline_subprocess() -> dict:
+    """One full-size layer-0 call of the CPU arm in a process of its own: the reference package defines the same
+    torch.library namespace as the product package, so the two cannot register their operators in one process."""
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0", "--cpu-budget", "60"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        for text in reversed(proc.stdout.strip().splitlines()):
+            if text.startswith("{"):
+                return json.loads(text)["cpu_baseline"]
+        return {"value": None, "unit": UNIT, "error": (proc.stderr or "no output")[-300:]}
+    except Exception as exc:
+        return {"value": None, "unit": UNIT, "error": f"{type(exc).__name__}: {exc}"[:300]}
 
 
 def reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 64
-    probe = run_cpu(sample, 1, 0)
-    budget = 180.0
-    while sample > 8 and probe["seconds_per_layer_call"] * (args.steps + args.warmup) > budget:
-        sample //= 2
-        probe = run_cpu(sample, 1, 0)
-    res = run_cpu(sample, args.steps, args.warmup)
+    res = run_cpu(args.cpu_tokens, args.steps, min(args.warmup, 1), budget_s=args.cpu_budget)
     line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": res["seconds_per_layer_call"] * 1e3 * LAYERS * (TOKENS / sample),
+            "steps": res["calls_timed"], "warmup": min(args.warmup, 1),
+            "ms_per_step": res["seconds_per_layer_call"] * 1e3 * LAYERS * (TOKENS / res["sample_tokens"]),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config_block(1), "cpu_baseline": res,
             "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -315,7 +373,7 @@ def native_arm(args) -> None:
                                        "peak_source": pk_kind, "bytes_per_launch": DECODE_BYTES},
                           "status": ops.workspace_status(wsd)}
         line["gpu_launches"] += 13 + 2 * (20 + 3) * LAYERS      # roofline leg + two decode kernels per layer and pass
-        line["cpu_baseline"] = run_cpu(64, 1, 0)
+        line["cpu_baseline"] = cpu_baseline_subprocess()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -424,6 +482,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
+    ap.add_argument("--cpu-tokens", type=int, default=TOKENS, help="tokens of the CPU arm's layer-0 call")
+    ap.add_argument("--cpu-budget", type=float, default=240.0, help="seconds the CPU arm may spend on timed calls")
     ap.add_argument("--only", choices=("all", "decode", "gemm", "model"), default="all",
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")

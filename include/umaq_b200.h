@@ -84,7 +84,9 @@ int umaq_sm_count(void);
  * by the caller before its first use; calls sharing a workspace must not overlap
  * on the device.  Word 2 (uint32 at byte offset 8) is a sticky device-side
  * status: 0, or a UMAQ_ERR_* code if a bounded wait gave up or an expert index
- * was out of range (then re-zero the workspace before reusing it). */
+ * was out of range.  A route with an out-of-range index contributes nothing, as
+ * in the reference's kernels (src/uma_qmoe/native/packed_q4_kernel.cu:176), and
+ * the output is still complete; after a timeout the output is undefined. */
 size_t umaq_decode_workspace_bytes(int top_k, int intermediate, int shared_intermediate);
 int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /* may be NULL */,
                     const void* hidden_bf16 /* device [H] */,
@@ -93,9 +95,16 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /*
                     void* out_bf16 /* device [H] */, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* Launch geometry umaq_moe_decode would use for a shape on a device with `sms` SMs; nothing is launched
+ * and no device is touched (no counterpart in the reference).  out[0..5]: gate/up kernel CTAs, ring
+ * stages, bytes per stage, dynamic shared memory, most work units of a CTA, 64-byte items per stage;
+ * out[6..11]: the same for the down kernel.  UMAQ_ERR_UNSUPPORTED when a shape does not fit an SM. */
+int umaq_decode_plan(int encoding, int hidden, int intermediate, int top_k, int shared_intermediate, int sms,
+                     int* out /* host [12] */, int out_len);
+
 /* Decode for callers that cannot allocate device memory.  It has no counterpart in the
  * reference.  Same computation and result as umaq_moe_decode, but the scratch the kernel
- * needs (control words and the float32 intermediate of the selected experts) lives in a
+ * needs (control words and the intermediate of the selected experts) lives in a
  * 64 KiB block built into the library instead of a caller workspace.  It is meant for
  * hosts that are handed only their input and output buffers: code running inside another
  * framework's stream callback or custom-call hook, or a plug-in whose memory is owned by
@@ -103,9 +112,12 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /*
  * would serialise the device.  The call itself allocates nothing.
  *
  * Limits and rules:
- *  - top_k * intermediate + shared intermediate must fit: at most 16128 float32 values
- *    (OLMoE 8 x 1024 and Qwen 4 x 1408 + 5632 fit); larger shapes are refused with
- *    UMAQ_ERR_WORKSPACE and a message, use umaq_moe_decode then.
+ *  - top_k (rounded up to a power of two) * intermediate + shared intermediate must fit:
+ *    at most 15,744 values of four bytes (OLMoE 8 x 1024 and Qwen 4 x 1408 + 5632 fit);
+ *    larger shapes are refused with UMAQ_ERR_WORKSPACE and a message, use umaq_moe_decode then.
+ *  - The status word of the built-in block cannot be read by the caller and is cleared by
+ *    the next call: a route with an out-of-range expert index contributes nothing (as in
+ *    umaq_moe_decode) but is not reported.  Validate indices first if that matters.
  *  - Every device that loads the library holds its own 64 KiB block until the process
  *    exits.  The first call on a device looks up the block's device address; make that
  *    first call outside any stream capture.

@@ -131,3 +131,34 @@ def test_rejects_cpu_tensors_and_bad_shapes():
         ops.moe_decode(layer, syn.activations(1, 2).to(DEV), idx, w, ws)       # two tokens
     with pytest.raises(RuntimeError):
         ops.moe_decode(layer, syn.activations(1, 1).to(DEV), idx, w, ws[:64])  # workspace too small
+
+
+def test_reference_validator_and_route_trace_decode(golden_dir):
+    """One token of the reference validator's inputs (linspace hidden state, experts 0..7, weights 0.125) and the
+    first decode event of layer 0 of the reference's frozen route trace, against the reference's CPU outputs."""
+    g = np.load(golden_dir / "reference_cases.npz")
+    src = expert_source(SEED, int(g["layer"]), "olmoe", "q4_group128")
+    layer = stage_layer({int(e): src(int(e)) for e in g["hit"]}, 64, 2048, 1024, "q4_group128", DEV)
+    y = _run_decode(layer, bits_to_bf16(g["val_x1_bits"]), torch.from_numpy(g["val_idx"]),
+                    bits_to_bf16(g["val_w_bits"]).float())
+    assert_parity(y, bits_to_bf16(g["val_y1_bits"]))
+    y = _run_decode(layer, bits_to_bf16(g["trace_decode_x_bits"]), torch.from_numpy(g["trace_decode_idx"]),
+                    torch.from_numpy(g["trace_decode_w"]))
+    assert_parity(y, bits_to_bf16(g["trace_decode_y_bits"]))
+
+
+def test_bad_expert_index_is_skipped_like_the_reference():
+    """An out-of-range index contributes nothing (the reference's kernels skip it,
+    src/uma_qmoe/native/packed_q4_kernel.cu:176); the other routes still produce the complete output."""
+    ops = _ops()
+    src = expert_source(SEED, 6, "olmoe", "q4_group128")
+    layer = stage_layer({e: src(e) for e in range(4)}, 4, 2048, 1024, "q4_group128", DEV)
+    x = syn.activations(SEED + 14, 1)
+    idx = torch.tensor([[0, 1, 2, 3, 0, 1, 2, 99]])
+    w = torch.full((1, 8), 0.125)
+    ws = ops.decode_workspace(layer, 8, None, torch.device(DEV))
+    y = ops.moe_decode(layer, x.to(DEV), idx.to(DEV), w.to(DEV), ws).cpu()
+    torch.cuda.synchronize()
+    assert ops.workspace_status(ws) == -1
+    want = orc.moe_forward(x, idx[:, :7].contiguous(), w[:, :7].contiguous(), src, num_experts=64, top_k=7, qwen=False)
+    assert_parity(y, want)

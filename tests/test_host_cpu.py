@@ -43,13 +43,38 @@ def test_build_info_names_the_target_and_the_source_digest():
 
 def test_workspace_sizes_are_host_arithmetic():
     lib = _native.lib()
-    assert lib.umaq_decode_workspace_bytes(8, 1024, 0) == 1024 + 8 * 1024 * 4
-    assert lib.umaq_decode_workspace_bytes(4, 1408, 5632) == 1024 + (4 * 1408 + 5632) * 4
+    # header + four bytes per intermediate value (slot count rounded up to a power of two) + alignment slack
+    assert lib.umaq_decode_workspace_bytes(8, 1024, 0) == 1024 + 8 * 1024 * 4 + 512
+    assert lib.umaq_decode_workspace_bytes(4, 1408, 5632) == 1024 + (4 * 1408 + 5632) * 4 + 512
+    assert lib.umaq_decode_workspace_bytes(6, 1024, 0) == 1024 + 8 * 1024 * 4 + 512
+    assert lib.umaq_decode_workspace_bytes(4, 1408, 5632) <= 64 * 1024        # fits the built-in scratch block
     small = lib.umaq_prefill_workspace_bytes(1, 8, 64, 2048, 1024, 0)
     big = lib.umaq_prefill_workspace_bytes(8192, 8, 64, 2048, 1024, 0)
     assert 0 < small < big
     # sorted activations + intermediate + weighted outputs dominate: routes * (H + I + H) * 2 bytes
     assert big >= 65536 * (2048 + 1024 + 2048) * 2
+
+
+def test_decode_launch_plans_fit_one_sm_together():
+    """Host arithmetic of the decode launcher: for every shape of the benchmark configurations the two kernels'
+    shared memory fits one SM side by side, every CTA's share fits its ring or the ring has at least two stages,
+    and the work is spread over all SMs."""
+    import ctypes as C
+    lib = _native.lib()
+    out = (C.c_int * 12)()
+    shapes = {"olmoe q4": (0, 2048, 1024, 8, 0), "olmoe q8": (1, 2048, 1024, 8, 0), "olmoe bf16": (2, 2048, 1024, 8, 0),
+              "qwen q8 + shared": (1, 2048, 1408, 4, 5632), "qwen bf16 + shared": (2, 2048, 1408, 4, 5632),
+              "qwen q4 + shared": (0, 2048, 1408, 4, 5632), "small": (0, 512, 256, 2, 0)}
+    for name, args in shapes.items():
+        assert lib.umaq_decode_plan(*args, 148, out, 12) == 0, (name, lib.umaq_last_error())
+        g_grid, g_stages, g_stage, g_smem, g_units, g_ips, d_grid, d_stages, d_stage, d_smem, d_units, d_ips = list(out)
+        assert g_smem + d_smem <= 226 * 1024, name
+        assert g_stages >= min(2, g_units) and d_stages >= min(2, d_units), name
+        assert 1 <= g_grid <= 148 and 1 <= d_grid <= 148, name
+    assert lib.umaq_decode_plan(0, 2048, 1024, 8, 0, 148, out, 12) == 0
+    assert list(out)[:2] == [148, 7] and list(out)[6:8] == [148, 7]        # OLMoE: a CTA's whole share is in flight at once
+    assert lib.umaq_decode_plan(0, 2048, 1000, 8, 0, 148, out, 12) == -1   # intermediate not a multiple of 128
+    assert lib.umaq_decode_plan(0, 2048, 1024, 9, 0, 148, out, 12) == -1   # more than 8 routes
 
 
 class _Reader:

@@ -133,3 +133,25 @@ def test_sorted_routes_is_stable_counting_sort():
     order, offsets = orc.sorted_routes(idx, 4)
     assert order.tolist() == [3, 1, 2, 0, 4, 5]
     assert offsets.tolist() == [0, 1, 3, 3, 6]
+
+
+def test_reference_validator_and_route_trace_cases(golden_dir):
+    """The reference validator's own inputs (benchmarks/runners/validate_packed_q4_kernel.py:151-178) and one
+    layer of its frozen route trace (src/uma_qmoe/route_trace.py:382-404), outputs made by the reference."""
+    g = np.load(golden_dir / "reference_cases.npz")
+    src = expert_source(SEED, int(g["layer"]), "olmoe", "q4_group128")
+    idx = torch.from_numpy(g["val_idx"])
+    w = bits_to_bf16(g["val_w_bits"])                       # the validator passes BF16 routing weights
+    y = orc.moe_forward(bits_to_bf16(g["val_x1_bits"]), idx, w, src, num_experts=64, top_k=8, qwen=False)
+    _assert_close_bf16(y, bits_to_bf16(g["val_y1_bits"]))
+    y = orc.moe_forward(bits_to_bf16(g["val_x32_bits"]), idx.repeat(32, 1), w.repeat(32, 1), src, num_experts=64,
+                        top_k=8, qwen=False)
+    _assert_close_bf16(y, bits_to_bf16(g["val_y32_bits"]))
+    for phase in ("prefill", "decode"):
+        idx = torch.from_numpy(g[f"trace_{phase}_idx"])
+        w = torch.from_numpy(g[f"trace_{phase}_w"])
+        y = orc.moe_forward(bits_to_bf16(g[f"trace_{phase}_x_bits"]), idx, w, src, num_experts=64, top_k=8, qwen=False)
+        _assert_close_bf16(y, bits_to_bf16(g[f"trace_{phase}_y_bits"]))
+    counts = torch.bincount(torch.from_numpy(g["trace_prefill_idx"]).reshape(-1), minlength=64)
+    assert int((counts > 0).sum()) == 32 and int(counts.max()) == 53      # the skew the survey quotes for this layer
+    assert abs(float(g["trace_prefill_w"][0].sum()) - 1.0) > 0.1          # real routes are not renormalised

@@ -223,3 +223,65 @@ def test_operator_edge_shapes_through_the_registered_backend():
             torch.ops.uma_qmoe.moe_forward(x, idx, w, 16, handle, True)
     finally:
         custom_op.unregister_expert_pack(handle)
+
+
+def test_reference_validator_and_route_trace_prefill(golden_dir):
+    """The reference validator's 32-token case and the 128-token prefill event of layer 0 of its frozen route
+    trace (32 of 64 experts hit, 53 routes on the busiest, un-normalised weights), against the reference's CPU
+    outputs."""
+    g = np.load(golden_dir / "reference_cases.npz")
+    src = expert_source(SEED, int(g["layer"]), "olmoe", "q4_group128")
+    layer = stage_layer({int(e): src(int(e)) for e in g["hit"]}, 64, 2048, 1024, "q4_group128", DEV)
+    idx = torch.from_numpy(g["val_idx"]).repeat(32, 1)
+    w = bits_to_bf16(g["val_w_bits"]).float().repeat(32, 1)
+    assert_parity(_run_prefill(layer, bits_to_bf16(g["val_x32_bits"]), idx, w), bits_to_bf16(g["val_y32_bits"]))
+    y = _run_prefill(layer, bits_to_bf16(g["trace_prefill_x_bits"]), torch.from_numpy(g["trace_prefill_idx"]),
+                     torch.from_numpy(g["trace_prefill_w"]))
+    assert_parity(y, bits_to_bf16(g["trace_prefill_y_bits"]))
+
+
+def test_baseline_prefill_512_tokens_skewed_router():
+    """The 512-token prefill configuration exactly: all 64 experts staged, routes from the skewed seeded router
+    through the router kernel (some experts get no token, the busiest at least three times the mean), result
+    against the CPU oracle."""
+    from uma_qmoe_b200 import ops
+    shape = syn.OLMOE
+    src = expert_source(SEED, 2, "olmoe", "q4_group128")
+    layer = stage_layer({e: src(e) for e in range(64)}, 64, 2048, 1024, "q4_group128", DEV)
+    x = syn.activations(SEED + 51, 512)
+    wr = syn.router_weight(SEED, 2, shape, skew=1.5)
+    w, idx = ops.route_topk(x.to(DEV), wr.to(DEV), shape.top_k, True)
+    w, idx = w.cpu(), idx.cpu()
+    counts = torch.bincount(idx.reshape(-1), minlength=64)
+    assert int(counts.min()) == 0 and int(counts.max()) >= 3 * counts.float().mean(), counts.tolist()
+    want = orc.moe_forward(x, idx, w, src, num_experts=64, top_k=8, qwen=False)
+    assert_parity(_run_prefill(layer, x, idx, w), want)
+
+
+def test_stack_shape_8192_tokens_sampled_rows():
+    """The expert-parallel stack's shape (8192 tokens x 64 experts x top-8, layer 0 of the benchmark stack) on one
+    GPU; 64 sampled token rows against the CPU oracle, which dequantises the staged bytes of the experts they hit."""
+    from uma_qmoe_b200 import ops
+    from uma_qmoe_b200.stack import random_layer
+    shape = syn.OLMOE
+    dev = torch.device(DEV)
+    layer = random_layer(shape, "q4_group128", SEED, dev)
+    x = syn.activations(SEED, 8192)
+    wr = syn.router_weight(SEED, 0, shape, skew=1.0)
+    w, idx = ops.route_topk(x.to(dev), wr.to(dev), shape.top_k, True)
+    y = _run_prefill(layer, x, idx.cpu(), w.cpu())
+    rows = torch.arange(0, 8192, 128)
+    idx_s, w_s = idx.cpu()[rows], w.cpu()[rows]
+
+    def staged(e: int):
+        def take(t, s, n, k):
+            per = n * k // 2
+            data = t[e * per:(e + 1) * per].cpu().numpy()
+            scales = s[e * (n * k // 128):(e + 1) * (n * k // 128)].cpu().numpy()
+            return orc.EncodedMatrix("q4_group128", (n, k), data, scales)
+        return (take(layer.gate, layer.gate_scales, 1024, 2048), take(layer.up, layer.up_scales, 1024, 2048),
+                take(layer.down, layer.down_scales, 2048, 1024))
+    cache = {}
+    src = lambda e: cache.setdefault(e, staged(e))
+    want = orc.moe_forward(x[rows], idx_s, w_s, src, num_experts=64, top_k=8, qwen=False)
+    assert_parity(y[rows], want)

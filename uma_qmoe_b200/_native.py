@@ -36,6 +36,7 @@ SIGNATURES = {
     "umaq_decode_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "umaq_moe_decode": (C.c_int, [C.POINTER(Layer), C.POINTER(SharedExpert), C.c_void_p, C.c_void_p, C.c_int,
                                   C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "umaq_decode_plan": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int]),
     "umaq_moe_decode_static": (C.c_int, [C.POINTER(Layer), C.POINTER(SharedExpert), C.c_void_p, C.c_void_p, C.c_int,
                                          C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "umaq_route_topk": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,

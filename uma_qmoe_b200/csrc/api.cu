@@ -99,7 +99,7 @@ int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared, c
   p.out = static_cast<__nv_bfloat16*>(out_bf16);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.sync = reinterpret_cast<unsigned*>(ws);
-  p.inter_buf = reinterpret_cast<float*>(ws + kDecodeWsHeader);
+  p.inter_buf = ws + kDecodeWsHeader;
   return launch_moe_decode(p, static_cast<cudaStream_t>(stream));
 }
 
@@ -201,7 +201,7 @@ int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, i
     return ERR_BAD_ARGUMENT;
   }
   return launch_combine(static_cast<const __nv_bfloat16*>(weighted_bf16), expert_indices, indices_are_int64, route_pos,
-                        tokens, top_k, hidden, nullptr, nullptr, nullptr, static_cast<__nv_bfloat16*>(out_bf16),
+                        tokens, top_k, hidden, 0x7fffffff, nullptr, nullptr, nullptr, static_cast<__nv_bfloat16*>(out_bf16),
                         static_cast<cudaStream_t>(stream));
 }
 
@@ -330,7 +330,7 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, 
     shared_out = d.out;
   }
   return launch_combine(reinterpret_cast<const __nv_bfloat16*>(at(pl.yw)), expert_indices, indices_are_int64, sa.route_pos,
-                        (int)tokens, top_k, H, shared_out, static_cast<const __nv_bfloat16*>(hidden_bf16),
+                        (int)tokens, top_k, H, E, shared_out, static_cast<const __nv_bfloat16*>(hidden_bf16),
                         shared ? static_cast<const __nv_bfloat16*>(shared->gate_vec) : nullptr,
                         static_cast<__nv_bfloat16*>(out_bf16), stream);
 }

@@ -8,791 +8,867 @@
 // (src/uma_qmoe/native_backend.py:319-372, :722-753).  Numerics follow the reference's CPU
 // correctness path (src/uma_qmoe/custom_op.py:301-340, :465-506): float32 accumulation, one BF16
 // rounding of every expert contribution and of the running sum, experts in ascending order; the
-// intermediate travels between the kernels as power-of-two-prescaled fp16 (BF16 for BF16 rows).
+// intermediate SiLU(gate) * up travels between the kernels rounded once to BF16, as in the
+// reference's own CUDA kernels (packed_q4_kernel.cu:228).
 //
 // The layer is ~27 MB (OLMoE Q4) to ~105 MB (Qwen Q8 + BF16 shared expert) of weights read exactly
-// once: a pure HBM stream of a few microseconds, during which nothing may serialise.  Kernel A
-// (gate/up + SwiGLU) gives every 32 features of a selected expert a 256-thread CTA: four 16-row
-// warp-MMA tiles (8 gate rows + 8 up rows each, all of K), two warps per tile, the activation
-// fragments built once per CTA; kernel B (down + ordered combine) gives every 8 output rows a CTA
-// that walks the selected experts in pairs.  Weight blocks stream through register buffers that are
-// refilled as soon as they have been multiplied; no CTA waits for another.  Kernel B is launched with
-// programmatic stream serialisation: its CTAs start while kernel A drains, issue their first weight
-// loads, and only then wait for A's records.
+// once: a pure HBM stream of a few microseconds, so everything is organised around keeping that
+// stream busy from the first cycle.
 //
-// Dequantisation is free of per-weight arithmetic: nibbles become exact integer-valued fp16
-// ((w ^ 8) & 0xF | 0x6400 = 1024 + code + 8, one LOP3 per two weights) and go straight into
-// m16n8k16 warp MMAs whose B operand is the activation vector; the group scale and the constant
-// bias (1032 * sum x etc.) are applied once per 128-wide group in float32.  On B200 the
-// HBM-to-issue-rate ratio leaves < 3 instructions per 4-bit weight, which rules out per-weight FMA
-// on the CUDA cores; the warp MMA does the multiply-add and the CUDA cores only unpack.
+//  * One CTA per SM per kernel.  A producer warp moves the CTA's weight rows and their group scales
+//    into a shared-memory ring (cp.async.bulk for the rows, cp.async for the scales, one mbarrier per
+//    stage); with the OLMoE shape a CTA's whole share (~120 KB gate/up, ~60 KB down) is in flight at
+//    once.  Eight consumer warps split K: each takes 64-byte columns ("items") of the 16 MMA rows of
+//    a stage, so no warp waits for another until the partial sums meet in shared memory.
+//  * Both kernels carry the programmatic-stream-serialisation attribute.  The gate/up kernel waits
+//    for its predecessor (the routes come from it), then lets the down kernel start: the down CTAs
+//    become resident beside the gate/up CTAs (the two kernels' shared memory and registers fit one
+//    SM together), stream their weights while gate/up computes, and only then wait for the
+//    intermediate.  The down kernel in turn lets the next kernel of the stream start early.
+//  * Dequantisation costs no per-weight arithmetic: a nibble becomes the exact BF16 value
+//    128 + (code + 8) with one LOP3 per two weights (0x4300 | nibble) and goes straight into
+//    m16n8k16 BF16 warp MMAs whose B operand is the activation vector, exact in BF16 as it is; the
+//    constant 136 is removed by starting every accumulator at -136 * sum(x) of its 128-wide group,
+//    and the group scale is applied once per group in float32.  Q8 bytes are split into two nibbles
+//    that meet x and 16 x in the B operand, so they run through the same instructions.  On B200 the
+//    HBM-to-issue-rate ratio leaves < 3 instructions per 4-bit weight, which rules out per-weight
+//    FMA on the CUDA cores; the warp MMA does the multiply-add and the CUDA cores only unpack.
+//  * Gate/up tile = 8 gate rows + 8 up rows of 8 features (column 0 of the MMA).  Down tile = 2
+//    output rows x up to 8 routed slots: MMA row g holds slot g's weight row, MMA column g slot g's
+//    intermediate, the diagonal of the product is what is kept -- all slots of an output row meet in
+//    one CTA, which therefore does the ordered BF16 combine itself.  The BF16 shared expert enters
+//    the same tiles with its K dimension cut into 8 segments in place of the slots.
 #include "../../include/umaq_b200.h"
 #include "common.cuh"
 #include "decode.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace umaq {
 namespace {
 
-constexpr int kWarps = 4;
-constexpr int kThreads = kWarps * 32;
-constexpr int kMaxSlots = 9;                    // top-k <= 8 routed + 1 shared
+constexpr int kNW = 8;                        // consumer warps; warp kNW is the producer
+constexpr int kConsumers = kNW * 32;
+constexpr int kThreadsD = (kNW + 1) * 32;
+constexpr int kMaxSlots = 8;
+// The two kernels share an SM: their dynamic shared memory together stays under kPairSmemBudget (228 KB per SM
+// minus 1 KB reserve and the static arrays of each CTA).  The down kernel is planned first and takes what its
+// whole share needs, up to kDownSmemMax; the gate/up kernel gets the rest.
+constexpr int kPairSmemBudget = 224 * 1024;
+constexpr int kDownSmemMax = 112 * 1024;
+constexpr long long kDecodeWaitCycles = 40ll * 1000 * 1000;     // ~20 ms of SM clock: far beyond any healthy wait
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// ---- block arithmetic: 16 tile rows x one 64-byte block of each row ---------------------------------
-// lane = 4*q + c supplies tile rows q and q+8.  Every block runs two accumulator chains; d[] returns
-// the four accumulator elements of the lane summed over the chains: d[0], d[1] = row q, MMA columns
-// 2c, 2c+1; d[2], d[3] = row q+8.
-#define UMAQ_Q4_LO(w) lop3<0x6A>((w), 0x000F000Fu, 0x64086408u)   /* fp16 1024 + (code + 8)      */
-#define UMAQ_Q4_HI(w) lop3<0x6A>((w), 0x00F000F0u, 0x64806480u)   /* fp16 1024 + 16 * (code + 8) */
-
-// bytes of activation fragments per 64-byte weight block: Q4 128 k, Q8 64 k, BF16 32 k, 2 bytes each
-__device__ __forceinline__ int frag_block_bytes(int enc) { return enc == ENC_Q4 ? 256 : (enc == ENC_Q8 ? 128 : 64); }
-
-// ---- activation fragments in shared memory -------------------------------------------------------------
-// fp16 fragments for Q4 rows: each run of 8 activations k0..k7 is stored as
-// [k0, k4, k1/16, k5/16, k2, k6, k3/16, k7/16] (the nibble pairs one LOP3 extracts and the 1/16 that
-// undoes the in-place high nibble).  Q8 and BF16 rows use natural order.  v[] = four consecutive
-// activations starting at k0 (a multiple of 4), already multiplied by the prescale.
-__device__ __forceinline__ void store_frag4(int enc, uint8_t* xf, int k0, const float (&v)[4]) {
-  if (enc == ENC_Q4) {
-    __half* o = reinterpret_cast<__half*>(xf) + (k0 & ~7) + ((k0 >> 2) & 1);
-    o[0] = __float2half_rn(v[0]); o[2] = __float2half_rn(v[1] * 0.0625f);
-    o[4] = __float2half_rn(v[2]); o[6] = __float2half_rn(v[3] * 0.0625f);
-    return;
-  }
-  uint2 w;
-  if (enc == ENC_BF16) {
-    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-    w.x = *reinterpret_cast<uint32_t*>(&lo);
-    w.y = *reinterpret_cast<uint32_t*>(&hi);
-  } else {
-    __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
-    w.x = *reinterpret_cast<uint32_t*>(&lo);
-    w.y = *reinterpret_cast<uint32_t*>(&hi);
-  }
-  *reinterpret_cast<uint2*>(xf + (size_t)k0 * 2) = w;
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+// The barrier receives one arrival when all cp.async copies this thread issued so far have landed
+// (the arrival is part of the barrier's initial count).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Bias sums of the 64-byte weight blocks of an n-activation fragment vector, read back from shared
-// memory: every thread sums 32 stored halves with their coefficients, 4 (Q4) or 2 (Q8) neighbouring
-// lanes combine.  Q4: run positions 0,1,4,5 hold x (coefficient 1032), 2,3,6,7 hold x/16 (72 * 16);
-// Q8: every position holds x (1152).
-template <int NT = kThreads>
-__device__ __forceinline__ void build_bias(int enc, const uint8_t* xf, float* bias, int n, int tid) {
-  const int chunks = n >> 5;
-  for (int ch = tid; ch < ((chunks + 31) & ~31); ch += NT) {
-    float sum = 0.f;
-    if (ch < chunks) {
-      const uint4* src = reinterpret_cast<const uint4*>(xf + (size_t)ch * 64);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 w = src[i];
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-        const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
-        if (enc == ENC_Q4) sum += (a.x + a.y + c2.x + c2.y) * 1032.f + (b.x + b.y + d.x + d.y) * (72.f * 16.f);
-        else sum += (a.x + a.y + b.x + b.y + c2.x + c2.y + d.x + d.y) * 1152.f;
-      }
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    if (enc == ENC_Q4) {
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (ch < chunks && (ch & 3) == 0) bias[ch >> 2] = sum;
-    } else if (ch < chunks && (ch & 1) == 0) {
-      bias[ch >> 1] = sum;
-    }
+// Bounded wait that also gives up when another warp of the CTA has already failed.
+__device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, volatile int* fail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();                 // the SM's own counter: cheap to read inside a spin
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*fail || clock64() - t0 > kDecodeWaitCycles) { *fail = 1; return false; }
   }
 }
 
-// Power of two s with amax * s in [2^13, 2^14), built from the exponent bits; 1 when amax is zero,
-// tiny or not finite.  Keeps every activation inside fp16's range whatever its magnitude.
-__device__ __forceinline__ float prescale_for(float amax) {
-  const int eb = (__float_as_uint(amax) >> 23) & 0xff;      // amax = m * 2^(eb-126), m in [0.5, 1)
-  if (eb < 32 || eb > 240) return 1.f;
-  return __uint_as_float((unsigned)(267 - eb) << 23);        // 2^(14 - (eb - 126))
-}
-
-// max over the CTA; `red` has NW floats
-template <int NW = kWarps>
-__device__ __forceinline__ float block_max(float v, float* red, int tid) {
-#pragma unroll
-  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((tid & 31) == 0) red[tid >> 5] = v;
-  __syncthreads();
-  float m = red[0];
-#pragma unroll
-  for (int i = 1; i < NW; ++i) m = fmaxf(m, red[i]);
-  __syncthreads();
-  return m;
+// Measurement aid (debug bit 4): CTA 0 leaves %globaltimer stamps in the workspace header, 8 bytes each
+// from byte 128 on.
+__device__ __forceinline__ void stamp(const DecodeParams& p, int slot, int tid_wanted) {
+  if ((p.debug & 4) && blockIdx.x == 0 && (int)threadIdx.x == tid_wanted)
+    reinterpret_cast<unsigned long long*>(p.sync)[16 + slot] = global_ns();
 }
 
 __device__ __forceinline__ long long load_index(const void* idx, int idx64, int i) {
   return idx64 ? reinterpret_cast<const long long*>(idx)[i] : (long long)reinterpret_cast<const int*>(idx)[i];
 }
 
-// Four blocks at once: eight accumulator chains issued round-robin, so no MMA waits for the one
-// before it (a dependent warp MMA on this architecture takes ~130 cycles to issue).  n = valid blocks;
-// d[i] as in mma_block().
-// XG: the fragments are in global memory and were written by the preceding kernel of the chain:
-// they are read through L2 (ld.global.cg), never through a cache that may predate that kernel.
-template <bool XG>
-__device__ __forceinline__ uint4 load_frag(const uint8_t* p) {
-  return XG ? __ldcg(reinterpret_cast<const uint4*>(p)) : *reinterpret_cast<const uint4*>(p);
+// ---- shared-memory loads by 32-bit shared address ------------------------------------------------------
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
 }
-template <bool XG, int N = 4>
-__device__ __forceinline__ void mma_blocks4(int enc, int n, const uint4 (&ra)[N], const uint4 (&rb)[N],
-                                            const uint8_t* const (&xf_lane)[N], bool xvalid, float (&d)[N][4]) {
-  float d0[N][4], d1[N][4];
-#pragma unroll
-  for (int i = 0; i < N; ++i)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) d0[i][e] = d1[i][e] = 0.f;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
+__device__ __forceinline__ float lds32(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 lds64(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a) : "memory");
+  return v;
+}
+
+// ---- activation fragments ----------------------------------------------------------------------------
+// An "item" is 64 bytes of each of the 16 MMA rows of a stage: 128 (Q4), 64 (Q8) or 32 (BF16)
+// activations.  Byte offset of activation k of slot `vs` in a fragment buffer laid out
+// [item][chunk r][slot][t] x 16 bytes: lane (g, t) of a warp reads, for item i and chunk r, the 16 bytes
+// at ((i*R + r)*ng + slot)*64 + t*16 and uses them as the B registers of two MMAs (R = 4 chunks per item
+// for Q4 / Q8, 1 for BF16).  Where a value sits inside its 16 bytes follows from how the weight codes
+// leave their 32-bit words:
+//   Q4   a lane's word holds 8 nibbles k0..k7; (w >> 4p) & 0x000F000F yields the pair (k_p, k_{p+4}),
+//        so the 8 values are stored [k0,k4,k1,k5,k2,k6,k3,k7];
+//   Q8   a word holds 4 bytes = nibbles (l0,h0,l1,h1,l2,h2,l3,h3); the same four extractions yield
+//        (l0,l2), (h0,h2), (l1,l3), (h1,h3), which meet [x0,x2,16x0,16x2,x1,x3,16x1,16x3];
+//   BF16 natural order.
+// hi selects the 16 x copy of a Q8 value.
+__host__ __device__ __forceinline__ int frag_offset(int enc, int ng, int vs, int k, int hi) {
+  int item, r, t, e, nr;
   if (enc == ENC_Q4) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-#pragma unroll
-      for (int i = 0; i < N; ++i) {
-        if (i < n) {
-          const uint4 x = xvalid ? load_frag<XG>(xf_lane[i] + 16 * j) : zero;
-          const uint32_t a = j == 0 ? ra[i].x : j == 1 ? ra[i].y : j == 2 ? ra[i].z : ra[i].w;
-          const uint32_t b = j == 0 ? rb[i].x : j == 1 ? rb[i].y : j == 2 ? rb[i].z : rb[i].w;
-          const uint32_t ah = a >> 8, bh = b >> 8;
-          mma_f16_16816(d0[i], UMAQ_Q4_LO(a), UMAQ_Q4_LO(b), UMAQ_Q4_HI(a), UMAQ_Q4_HI(b), x.x, x.y);
-          mma_f16_16816(d1[i], UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x.z, x.w);
-        }
-      }
-    }
+    item = k >> 7; t = (k >> 5) & 3; r = (k >> 3) & 3; nr = 4;
+    const int i = k & 7;
+    e = 2 * (i & 3) + (i >> 2);
   } else if (enc == ENC_Q8) {
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-#pragma unroll
-      for (int i = 0; i < N; ++i) {
-        if (i < n) {
-          const uint4 x = xvalid ? load_frag<XG>(xf_lane[i] + 16 * j) : zero;
-          const uint32_t a0 = (j == 0 ? ra[i].x : ra[i].z) ^ 0x80808080u, a1 = (j == 0 ? ra[i].y : ra[i].w) ^ 0x80808080u;
-          const uint32_t b0 = (j == 0 ? rb[i].x : rb[i].z) ^ 0x80808080u, b1 = (j == 0 ? rb[i].y : rb[i].w) ^ 0x80808080u;
-          mma_f16_16816(d0[i], prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
-                        prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x.x, x.y);
-          mma_f16_16816(d1[i], prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
-                        prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x.z, x.w);
-        }
-      }
-    }
+    item = k >> 6; t = (k >> 4) & 3; r = (k >> 2) & 3; nr = 4;
+    const int b = k & 3, n = 2 * b + hi;
+    e = 2 * (n & 3) + (b >> 1);
   } else {
+    item = k >> 5; r = 0; t = (k >> 3) & 3; nr = 1;
+    e = k & 7;
+  }
+  return ((((item * nr + r) * ng + vs) * 4 + t) << 4) + e * 2;
+}
+
+// x[0..n) -> fragments (one slot) and, for quantised rows, the sum of every item's activations.
+// Called by the kConsumers consumer threads; n is a multiple of 256.
+__device__ __forceinline__ void build_x_fragments(int enc, const __nv_bfloat16* __restrict__ x, int n, uint8_t* xf,
+                                                  float* gsum, int tid) {
+  for (int k0 = tid * 8; k0 < n; k0 += kConsumers * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + k0);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-      if (i < n) {
-        const uint4 x = xvalid ? load_frag<XG>(xf_lane[i]) : zero;
-        mma_bf16_16816(d0[i], ra[i].x, rb[i].x, ra[i].y, rb[i].y, x.x, x.y);
-        mma_bf16_16816(d1[i], ra[i].z, rb[i].z, ra[i].w, rb[i].w, x.z, x.w);
+    for (int j = 0; j < 8; ++j) {
+      const uint16_t bits = (uint16_t)(j & 1 ? w[j >> 1] >> 16 : w[j >> 1] & 0xffffu);
+      const float v = __uint_as_float((uint32_t)bits << 16);
+      sum += v;
+      *reinterpret_cast<uint16_t*>(xf + frag_offset(enc, 1, 0, k0 + j, 0)) = bits;
+      if (enc == ENC_Q8)
+        *reinterpret_cast<__nv_bfloat16*>(xf + frag_offset(enc, 1, 0, k0 + j, 1)) = __float2bfloat16_rn(v * 16.f);
+    }
+    if (enc != ENC_BF16) {
+      // an item is 128 (Q4) or 64 (Q8) activations = 16 or 8 neighbouring threads
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      if (enc == ENC_Q4) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+        if ((k0 & 127) == 0) gsum[k0 >> 7] = sum;
+      } else if ((k0 & 63) == 0) {
+        gsum[k0 >> 6] = sum;
       }
     }
   }
-#pragma unroll
-  for (int i = 0; i < N; ++i)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) d[i][e] = d0[i][e] + d1[i][e];
 }
 
-// The same for N complete blocks with the encoding fixed at compile time: no per-block predicates, so the
-// compiler emits straight-line LOP3 / HMMA code without convergence barriers around every warp MMA.
-// Two accumulator elements are returned: lo[i] = tile row q, MMA column 2c; hi[i] = tile row q + 8, column 2c
-// (HI = 2) or 2c + 1 (HI = 3).
-template <int ENC, int N, int HI = 2>
-__device__ __forceinline__ void mma_full(const uint4 (&ra)[N], const uint4 (&rb)[N], const uint8_t* const (&xf_lane)[N],
-                                         float (&lo)[N], float (&hi)[N]) {
-  float d0[N][4], d1[N][4];
+// ---- N items at once: 16 MMA rows x 64 bytes of weights each, against the fragments ---------------------
+// a0[n]: shared address of this lane's 16 bytes of MMA row g of item n, a8off bytes further those of row
+// g + 8; bp[n]: its fragment chunk 0, bstep bytes between chunks (SHARE_B: all items use bp[0]);
+// i0 / i1: start values of the accumulator columns 2t and 2t+1 (-bias * activation sum).
+// c[n][0], c[n][1] = row g, columns 2t, 2t+1; c[n][2], c[n][3] = row g + 8.  The items' MMA chains are
+// independent and issued round-robin, so no warp MMA waits for the one before it.
+template <uint32_t K>
+__device__ __forceinline__ uint32_t nib_bf16(uint32_t w) { return lop3<0x6A>(w, 0x000F000Fu, K); }   // (w & m) ^ K
+
+template <int ENC, int N, bool SHARE_B>
+__device__ __forceinline__ void items_mma(const uint32_t (&a0)[N], uint32_t a8off, const uint32_t (&bp)[N], uint32_t bstep,
+                                          const float (&i0)[N], const float (&i1)[N], float (&c)[N][4]) {
+  uint4 wa[N], wb[N];
 #pragma unroll
-  for (int i = 0; i < N; ++i)
+  for (int n = 0; n < N; ++n) { wa[n] = lds128(a0[n]); wb[n] = lds128(a0[n] + a8off); }
+  if (ENC == ENC_BF16) {
+    float acc[N][2][4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) d0[i][e] = d1[i][e] = 0.f;
-  if (ENC == ENC_Q4) {
+    for (int n = 0; n < N; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[n][0][e] = acc[n][1][e] = 0.f;
+    uint4 b = lds128(bp[0]);
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      if (!SHARE_B && n > 0) b = lds128(bp[n]);
+      mma_bf16_16816(acc[n][0], wa[n].x, wb[n].x, wa[n].y, wb[n].y, b.x, b.y);
+      mma_bf16_16816(acc[n][1], wa[n].z, wb[n].z, wa[n].w, wb[n].w, b.z, b.w);
+    }
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[n][e] = acc[n][0][e] + acc[n][1][e];
+  } else {
+    // BF16 128 + n: Q4 n = code + 8 (two's complement nibble ^ 8); Q8 low nibble as is, high nibble ^ 8
+    constexpr uint32_t kLo = ENC == ENC_Q4 ? 0x43084308u : 0x43004300u, kHi = 0x43084308u;
+    float acc[N][4][4];
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][j][e] = 0.f;
+      acc[n][0][0] = i0[n]; acc[n][0][1] = i1[n]; acc[n][0][2] = i0[n]; acc[n][0][3] = i1[n];
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      uint4 b = lds128(bp[0] + j * bstep);
 #pragma unroll
-      for (int i = 0; i < N; ++i) {
-        const uint4 x = *reinterpret_cast<const uint4*>(xf_lane[i] + 16 * j);
-        const uint32_t a = j == 0 ? ra[i].x : j == 1 ? ra[i].y : j == 2 ? ra[i].z : ra[i].w;
-        const uint32_t b = j == 0 ? rb[i].x : j == 1 ? rb[i].y : j == 2 ? rb[i].z : rb[i].w;
-        const uint32_t ah = a >> 8, bh = b >> 8;
-        mma_f16_16816(d0[i], UMAQ_Q4_LO(a), UMAQ_Q4_LO(b), UMAQ_Q4_HI(a), UMAQ_Q4_HI(b), x.x, x.y);
-        mma_f16_16816(d1[i], UMAQ_Q4_LO(ah), UMAQ_Q4_LO(bh), UMAQ_Q4_HI(ah), UMAQ_Q4_HI(bh), x.z, x.w);
+      for (int n = 0; n < N; ++n) {
+        if (!SHARE_B && n > 0) b = lds128(bp[n] + j * bstep);
+        const uint32_t a = j == 0 ? wa[n].x : j == 1 ? wa[n].y : j == 2 ? wa[n].z : wa[n].w;
+        const uint32_t a8 = j == 0 ? wb[n].x : j == 1 ? wb[n].y : j == 2 ? wb[n].z : wb[n].w;
+        mma_bf16_16816(acc[n][j], nib_bf16<kLo>(a), nib_bf16<kLo>(a8), nib_bf16<kHi>(a >> 4), nib_bf16<kHi>(a8 >> 4), b.x, b.y);
+        mma_bf16_16816(acc[n][j], nib_bf16<kLo>(a >> 8), nib_bf16<kLo>(a8 >> 8), nib_bf16<kHi>(a >> 12),
+                       nib_bf16<kHi>(a8 >> 12), b.z, b.w);
       }
     }
-  } else if (ENC == ENC_Q8) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int n = 0; n < N; ++n)
 #pragma unroll
-      for (int i = 0; i < N; ++i) {
-        const uint4 x = *reinterpret_cast<const uint4*>(xf_lane[i] + 16 * j);
-        const uint32_t a0 = (j == 0 ? ra[i].x : ra[i].z) ^ 0x80808080u, a1 = (j == 0 ? ra[i].y : ra[i].w) ^ 0x80808080u;
-        const uint32_t b0 = (j == 0 ? rb[i].x : rb[i].z) ^ 0x80808080u, b1 = (j == 0 ? rb[i].y : rb[i].w) ^ 0x80808080u;
-        mma_f16_16816(d0[i], prmt(a0, 0x64646464u, 0x4140), prmt(b0, 0x64646464u, 0x4140),
-                      prmt(a0, 0x64646464u, 0x4342), prmt(b0, 0x64646464u, 0x4342), x.x, x.y);
-        mma_f16_16816(d1[i], prmt(a1, 0x64646464u, 0x4140), prmt(b1, 0x64646464u, 0x4140),
-                      prmt(a1, 0x64646464u, 0x4342), prmt(b1, 0x64646464u, 0x4342), x.z, x.w);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-      const uint4 x = *reinterpret_cast<const uint4*>(xf_lane[i]);
-      mma_bf16_16816(d0[i], ra[i].x, rb[i].x, ra[i].y, rb[i].y, x.x, x.y);
-      mma_bf16_16816(d1[i], ra[i].z, rb[i].z, ra[i].w, rb[i].w, x.z, x.w);
-    }
+      for (int e = 0; e < 4; ++e) c[n][e] = (acc[n][0][e] + acc[n][1][e]) + (acc[n][2][e] + acc[n][3][e]);
   }
-#pragma unroll
-  for (int i = 0; i < N; ++i) { lo[i] = d0[i][0] + d1[i][0]; hi[i] = d0[i][HI] + d1[i][HI]; }
 }
 
-// ---- activation fragments ------------------------------------------------------------------------------------
-// Shared memory the gate/up kernel needs for an n-long activation vector: n fp16 fragments (2n bytes) and the
-// bias sums of its 64-byte weight blocks (n/64 floats, padded to a multiple of four).
-__host__ __device__ __forceinline__ int frag_body_bytes(int n) { return n * 2 + (((n >> 6) + 3) & ~3) * 4; }
-// The record the gate/up kernel leaves for quantised down rows: n fp16 fragments in 32-value chunks, each chunk
-// multiplied by its own power-of-two prescale, then the n/32 prescales and the n/32 chunk bias sums (float32).
-__host__ __device__ __forceinline__ int chunk_record_bytes(int n) { return n * 2 + (n >> 5) * 8; }
+// First work unit of gate/up CTA c: units are weighted by their bytes, routed units first, and a CTA
+// owns the units whose cost range starts inside [c, c+1) * total / grid.
+__host__ __device__ __forceinline__ int first_unit(const DecodeKernelPlan& P, int c) {
+  const long long x = ((long long)c * P.total_cost + P.grid - 1) / P.grid;
+  const long long routed = (long long)P.kind[0].units * P.cost[0];
+  if (x <= routed || P.kind[1].units == 0) return (int)min((long long)P.kind[0].units, (x + P.cost[0] - 1) / P.cost[0]);
+  return P.kind[0].units + (int)min((long long)P.kind[1].units, (x - routed + P.cost[1] - 1) / P.cost[1]);
+}
 
-// =====================================================================================================
-// Kernel A: one CTA = 32 features of one slot = four 16-row tiles (rows 0..7 gate rows, 8..15 up rows
-// of 8 features), all of K = H.  Two warps split the 64-byte blocks of a tile's rows; SwiGLU after the
-// cross-warp sum.  The activation fragments are built once per CTA and serve all four tiles (building
-// them costs about as many instructions as one tile's arithmetic, so a CTA per tile spent three
-// quarters of its instructions there).  Weight blocks stream through two register buffers of two
-// blocks each: the loads of group g + 2 are issued as soon as group g has been multiplied.  Every CTA
-// writes its 32 intermediates into the slot's record itself (chunk_record_bytes below).
-// =====================================================================================================
-constexpr int kWarpsA = 8, kThreadsA = kWarpsA * 32, kTilesA = 4, kSplitA = kWarpsA / kTilesA;
-
-struct BlockPair {
-  uint4 wa[2], wb[2];
-  float sa[2], sb[2];
+// Position of a warp in the ring of stages.
+struct Ring {
+  int slot, round, qbase;
+  __device__ __forceinline__ void advance(int stages) { if (++slot == stages) { slot = 0; ++round; } }
 };
 
-__global__ void __launch_bounds__(kThreadsA, 2) decode_gateup_kernel(const DecodeParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ float red[kWarpsA * 16];
-  __shared__ float red2[kWarpsA];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
-  const int H = p.hidden;
-  pdl_launch_dependents();
-
-  constexpr int kFeat = 8 * kTilesA;                           // features per CTA
-  const int ctas_r = (p.inter + kFeat - 1) / kFeat, routed = p.top_k * ctas_r;
-  const bool shared_tile = (int)blockIdx.x >= routed;
-  const int slot = shared_tile ? p.top_k : (int)blockIdx.x / ctas_r;
-  const int islot = shared_tile ? p.shared_inter : p.inter;
-  const int f0 = (shared_tile ? (int)blockIdx.x - routed : (int)blockIdx.x % ctas_r) * kFeat;
-  const int tile = warp / kSplitA, ws = warp % kSplitA;       // this warp: tile `tile`, blocks ws, ws + kSplitA, ...
-  const int ft = f0 + 8 * tile;                                // first feature of the warp's tile
-  const bool live = ft < islot;                                // the last CTA of a slot may have fewer tiles
-  const int enc = shared_tile ? ENC_BF16 : p.enc;
-  const int rb = row_bytes(enc, H), nblk = rb >> 6, gk = H >> 7;
-  const uint8_t *gate = nullptr, *up = nullptr;
-  const float *gate_s = nullptr, *up_s = nullptr;
-  if (shared_tile) {
-    gate = reinterpret_cast<const uint8_t*>(p.sh_gate) + (size_t)ft * rb;
-    up = reinterpret_cast<const uint8_t*>(p.sh_up) + (size_t)ft * rb;
-  } else {
-    long long e = load_index(p.idx, p.idx64, slot);
-    if (e < 0 || e >= p.experts) {
-      if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);
-      return;
-    }
-    const size_t row = (size_t)e * p.inter + ft;
-    gate = p.gate + row * rb; up = p.up + row * rb;
-    if (enc != ENC_BF16) { gate_s = p.gate_s + row * gk; up_s = p.up_s + row * gk; }
-  }
-
-  const int bpw = live ? (nblk - ws + kSplitA - 1) / kSplitA : 0;
-  auto issue = [&](BlockPair& b, int first) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int kb = ws + (first + i) * kSplitA;
-      if (first + i < bpw) {
-        b.wa[i] = ldg_stream(gate + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
-        b.wb[i] = ldg_stream(up + (size_t)q * rb + ((size_t)kb << 6) + (c << 4));
-        if (enc != ENC_BF16) {
-          const int g = enc == ENC_Q4 ? kb : (kb >> 1);
-          b.sa[i] = gate_s[q * gk + g];
-          b.sb[i] = up_s[q * gk + g];
+// ---- gate/up: the units [u0, u1) of one kind (compile-time encoding) -----------------------------------
+// A warp takes the items i0, i0 + 8, ... of every stage, two at a time; i0 rotates with the running item
+// count so that stages whose item count is no multiple of 8 still load the warps evenly.
+template <int ENC>
+__device__ __forceinline__ void gateup_units(const DecodeKernelPlan& P, const DecodeKind& K, int u0, int u1, int ub,
+                                             uint32_t smem_base, uint64_t* full, uint64_t* empty, float* red, Ring& ring,
+                                             volatile int* fail, int warp, int lane, bool skip) {
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t lane_a = g * K.mstride + t * 16, a8off = 8 * K.mstride;
+  const uint32_t xf = smem_base + K.frag_off + t * 16, gs = smem_base + K.gsum_off;
+  constexpr uint32_t kFragItem = ENC == ENC_BF16 ? 64 : 256;        // fragment bytes per item (one slot)
+  const uint32_t sc_g = (uint32_t)g * K.groups * 4, sc_g8 = (uint32_t)(8 + g) * K.groups * 4;
+  const float nbias = -K.bias;
+  for (int u = u0; u < u1; ++u) {
+    float acc0 = 0.f, acc8 = 0.f;
+    for (int ch = 0; ch < K.nch; ++ch) {
+      const int i0 = (warp - ring.qbase) & (kNW - 1);
+      if (i0 < K.ips && wait_or_fail(full + ring.slot, ring.round & 1, fail) && !skip) {
+        const uint32_t st = smem_base + ring.slot * P.stage_bytes, sc = st + P.scale_off;
+        int i = i0;
+        for (; i + kNW < K.ips; i += 2 * kNW) {
+          const int gi = ch * K.ips + i;
+          const uint32_t a0[2] = {st + lane_a + i * 64, st + lane_a + (i + kNW) * 64};
+          const uint32_t bp[2] = {xf + gi * kFragItem, xf + (gi + kNW) * kFragItem};
+          float in0[2] = {0.f, 0.f}, s0[2], s8[2];
+          if (ENC != ENC_BF16) {
+            in0[0] = nbias * lds32(gs + gi * 4); in0[1] = nbias * lds32(gs + (gi + kNW) * 4);
+            const int grp0 = ENC == ENC_Q4 ? gi : gi >> 1, grp1 = ENC == ENC_Q4 ? gi + kNW : (gi + kNW) >> 1;
+            s0[0] = lds32(sc + sc_g + grp0 * 4); s8[0] = lds32(sc + sc_g8 + grp0 * 4);
+            s0[1] = lds32(sc + sc_g + grp1 * 4); s8[1] = lds32(sc + sc_g8 + grp1 * 4);
+          }
+          float c[2][4];
+          items_mma<ENC, 2, false>(a0, a8off, bp, 64, in0, in0, c);
+          if (ENC != ENC_BF16) {
+            acc0 = fmaf(s0[0], c[0][0], acc0); acc8 = fmaf(s8[0], c[0][2], acc8);
+            acc0 = fmaf(s0[1], c[1][0], acc0); acc8 = fmaf(s8[1], c[1][2], acc8);
+          } else { acc0 += c[0][0] + c[1][0]; acc8 += c[0][2] + c[1][2]; }
+        }
+        if (i < K.ips) {
+          const int gi = ch * K.ips + i;
+          const uint32_t a0[1] = {st + lane_a + i * 64};
+          const uint32_t bp[1] = {xf + gi * kFragItem};
+          float in0[1] = {0.f}, s0 = 0.f, s8 = 0.f;
+          if (ENC != ENC_BF16) {
+            in0[0] = nbias * lds32(gs + gi * 4);
+            const int grp = ENC == ENC_Q4 ? gi : gi >> 1;
+            s0 = lds32(sc + sc_g + grp * 4); s8 = lds32(sc + sc_g8 + grp * 4);
+          }
+          float c[1][4];
+          items_mma<ENC, 1, false>(a0, a8off, bp, 64, in0, in0, c);
+          if (ENC != ENC_BF16) { acc0 = fmaf(s0, c[0][0], acc0); acc8 = fmaf(s8, c[0][2], acc8); }
+          else { acc0 += c[0][0]; acc8 += c[0][2]; }
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + ring.slot);
+      ring.qbase = (ring.qbase + K.ips) & (kNW - 1);
+      ring.advance(P.stages);
     }
-  };
-  BlockPair b0, b1;
-  issue(b0, 0);                         // weights are in flight while the activation fragments are built
-  issue(b1, 2);
-
-  // ---- x -> fragments in shared memory (quantised rows: prescaled fp16 + bias sums; BF16 rows: x as is) ---
-  uint8_t* xf = smem;
-  float* bias = reinterpret_cast<float*>(smem + (size_t)H * 2);
-  float x_inv = 1.f;
-  {
-    constexpr int kMaxV = 2;                                 // hidden <= 2 * 256 * 4 in one pass
-    for (int base = 0; base < H; base += kMaxV * kThreadsA * 4) {
-      float vals[kMaxV][4];
-      float am = 0.f;
-#pragma unroll
-      for (int j = 0; j < kMaxV; ++j) {
-        const int k0 = base + tid * 4 + j * kThreadsA * 4;
-        vals[j][0] = vals[j][1] = vals[j][2] = vals[j][3] = 0.f;
-        if (k0 < H) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(p.x + k0);
-          vals[j][0] = __uint_as_float(raw.x << 16); vals[j][1] = __uint_as_float(raw.x & 0xffff0000u);
-          vals[j][2] = __uint_as_float(raw.y << 16); vals[j][3] = __uint_as_float(raw.y & 0xffff0000u);
-          am = fmaxf(am, fmaxf(fmaxf(fabsf(vals[j][0]), fabsf(vals[j][1])), fmaxf(fabsf(vals[j][2]), fabsf(vals[j][3]))));
-        }
-      }
-      float sx = 1.f;
-      if (enc != ENC_BF16) {
-        // hidden sizes up to 2048 are one pass, so the block maximum is the vector maximum; wider
-        // vectors would need the maximum over all passes first
-        sx = prescale_for(block_max<kWarpsA>(am < 3.0e38f ? am : 0.f, red2, tid));
-        x_inv = 1.f / sx;
-      }
-#pragma unroll
-      for (int j = 0; j < kMaxV; ++j) {
-        const int k0 = base + tid * 4 + j * kThreadsA * 4;
-        if (k0 < H) {
-          const float v[4] = {vals[j][0] * sx, vals[j][1] * sx, vals[j][2] * sx, vals[j][3] * sx};
-          store_frag4(enc, xf, k0, v);
-        }
-      }
-    }
-    __syncthreads();
-    if (enc != ENC_BF16) { build_bias<kThreadsA>(enc, xf, bias, H, tid); __syncthreads(); }
-  }
-  const int fb = frag_block_bytes(enc);
-  float acc_lo = 0.f, acc_hi = 0.f;
-  auto multiply = [&](const BlockPair& b, int first) {
-    const int n = min(2, bpw - first);
-    const uint8_t* xp[2];
-    float bs[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int kb = ws + (first + min(i, n - 1)) * kSplitA;
-      xp[i] = xf + (size_t)kb * fb + c * (fb >> 2);
-      bs[i] = enc == ENC_BF16 ? 0.f : bias[kb];
-    }
-    if (n == 2) {                        // complete pair: straight-line code per encoding
-      float lo[2], hi[2];
-      if (enc == ENC_Q4) mma_full<ENC_Q4, 2>(b.wa, b.wb, xp, lo, hi);
-      else if (enc == ENC_Q8) mma_full<ENC_Q8, 2>(b.wa, b.wb, xp, lo, hi);
-      else mma_full<ENC_BF16, 2>(b.wa, b.wb, xp, lo, hi);
-      if (enc == ENC_BF16) { acc_lo += lo[0] + lo[1]; acc_hi += hi[0] + hi[1]; }
-      else {
-        acc_lo = fmaf(b.sa[0], lo[0] - bs[0], acc_lo); acc_hi = fmaf(b.sb[0], hi[0] - bs[0], acc_hi);
-        acc_lo = fmaf(b.sa[1], lo[1] - bs[1], acc_lo); acc_hi = fmaf(b.sb[1], hi[1] - bs[1], acc_hi);
-      }
-      return;
-    }
-    float d[2][4];
-    mma_blocks4<false, 2>(enc, n, b.wa, b.wb, xp, true, d);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (i < n) {
-        if (enc == ENC_BF16) { acc_lo += d[i][0]; acc_hi += d[i][2]; }
-        else { acc_lo = fmaf(b.sa[i], d[i][0] - bs[i], acc_lo); acc_hi = fmaf(b.sb[i], d[i][2] - bs[i], acc_hi); }
-      }
-    }
-  };
-  for (int first = 0; first < bpw; first += 4) {
-    multiply(b0, first);
-    if (first + 4 < bpw) issue(b0, first + 4);
-    if (first + 2 < bpw) {
-      multiply(b1, first + 2);
-      if (first + 6 < bpw) issue(b1, first + 6);
+    if (t == 0) {
+      float* r = red + ((size_t)(u - ub) * kNW + warp) * 16;
+      r[g] = acc0; r[8 + g] = acc8;
     }
   }
-  if (c == 0) { red[warp * 16 + q] = acc_lo; red[warp * 16 + 8 + q] = acc_hi; }
-  __syncthreads();
-  // ---- SwiGLU, then this CTA's 32 intermediates go straight into the slot's record for the down kernel ------
-  // Quantised down rows: fp16 fragments of the chunk with the chunk's own power-of-two prescale, the prescale
-  // and the chunk's bias sum (the down kernel brings the chunks of one weight block to a common scale).
-  // BF16 down rows: the BF16 values.  No CTA waits for another one.
-  const int ioff = shared_tile ? p.top_k * p.inter : slot * p.inter;
-  if (warp == 0 && f0 + lane < islot) {           // islot is a multiple of 32: the whole warp or none of it
-    const int t = lane >> 3, j = lane & 7;
-    float g = 0.f, u = 0.f;
-#pragma unroll
-    for (int w = 0; w < kSplitA; ++w) { g += red[(t * kSplitA + w) * 16 + j]; u += red[(t * kSplitA + w) * 16 + 8 + j]; }
-    float v;
-    if (shared_tile) {                  // Qwen2MoeMLP in BF16: every linear / activation output is rounded
-      g = bf16_round(g); u = bf16_round(u);
-      v = bf16_round(bf16_round(silu_f32(g)) * u);
-    } else {
-      g *= x_inv; u *= x_inv;
-      v = silu_f32(g) * u;
-    }
-    const int enc_b = shared_tile ? ENC_BF16 : p.enc;          // encoding of the down rows that read it
-    uint8_t* recp = reinterpret_cast<uint8_t*>(p.inter_buf + ioff);
-    const int k = f0 + lane;
-    if (enc_b == ENC_BF16) {
-      reinterpret_cast<__nv_bfloat16*>(recp)[k] = __float2bfloat16_rn(v);
-    } else {
-      float am = fabsf(v);
-      am = am < 3.0e38f ? am : 0.f;
-#pragma unroll
-      for (int o = 16; o; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-      const float sc = prescale_for(am);
-      const int r = k & 7;
-      int pos = k;
-      float val = v * sc, coef = 1152.f;
-      if (enc_b == ENC_Q4) {            // run order [k0,k4,k1/16,k5/16,k2,k6,k3/16,k7/16], see store_frag4
-        pos = (k & ~7) + (r < 4 ? 2 * r : 2 * (r - 4) + 1);
-        if (r & 1) val *= 0.0625f; else coef = 1032.f;
-      }
-      const __half h = __float2half_rn(val);
-      reinterpret_cast<__half*>(recp)[pos] = h;
-      float bsum = coef * __half2float(h);
-#pragma unroll
-      for (int o = 16; o; o >>= 1) bsum += __shfl_xor_sync(0xffffffffu, bsum, o);
-      if (lane == 0) {
-        float* tail = reinterpret_cast<float*>(recp + (size_t)islot * 2);
-        tail[k >> 5] = sc;
-        tail[(islot >> 5) + (k >> 5)] = bsum;
-      }
-    }
-  }
-  (void)x_inv;
 }
 
 // =====================================================================================================
-// Kernel B: one CTA = 8 output rows.  Slots are walked in ascending expert order, two per MMA tile
-// (tile rows 0..7: row n0+q of the first slot, rows 8..15: the same row of the second; the slots'
-// intermediate vectors are MMA columns 0 and 1).  The Qwen shared expert is a last, half-filled tile.
-// A warp owns the 64-byte blocks warp, warp + 4, ... of every tile and walks (tile, pair of blocks)
-// through four register buffers: their loads go out before griddepcontrol.wait, and every buffer is
-// refilled as soon as it has been multiplied.
+// Kernel A: gate/up + SwiGLU.  Work unit = 8 features of one slot: MMA rows 0..7 their gate rows,
+// 8..15 their up rows, all of K = hidden, in nch ring stages of 16 rows x ch bytes.
 // =====================================================================================================
-struct DownTile {
-  const uint8_t* wa; const uint8_t* wb;        // row n0 + q of the two slots' experts (wb null: no second slot)
-  const float* sa; const float* sb;            // their scale rows
-  int rec_a, rec_b;                            // byte offsets of the slots' records in shared memory
-  int slot_a, slot_b;
-};
-
-__global__ void __launch_bounds__(kThreads) decode_down_kernel(const DecodeParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ int s_order[kMaxSlots];
+__global__ void __launch_bounds__(kThreadsD, 2) decode_gateup_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_expert[kMaxSlots];
-  __shared__ float s_weight[kMaxSlots];
-  __shared__ float s_red[5][kWarps][16];
-  __shared__ float s_tmp[kWarps];
-  __shared__ float s_gate;
-  __shared__ int s_bad;
-  __shared__ __align__(16) uint8_t s_zero[256];         // fragment block of the lanes that feed no MMA column
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, q = lane >> 2, c = lane & 3;
-  const int H = p.hidden, I = p.inter, S = p.sh_gate ? p.shared_inter : 0;
-  const int n0 = blockIdx.x * 8;
-  // shared memory: the published records of the routed slots (fragments + bias), then the shared
-  // expert's BF16 vector
-  const int enc = p.enc;
-  const int rec = enc == ENC_BF16 ? I * 2 : chunk_record_bytes(I);     // bytes copied per routed slot
-  uint8_t* recs = smem;
-  uint8_t* xs = smem + (size_t)p.top_k * rec;
-  // per (slot, 64-byte weight block): bias sum and inverse of the common prescale of the block's chunks
-  const int nblk_all = row_bytes(enc, I) >> 6;
-  float* s_bbias = reinterpret_cast<float*>(xs + (size_t)(p.sh_gate ? p.shared_inter : 0) * 2);
-  float* s_binv = s_bbias + (size_t)p.top_k * nblk_all;
-
-  // ---- routes: order by expert (stable), shared expert last ----------------------------------------------
-  if (tid == 0) s_bad = 0;
-  if (tid < 64) reinterpret_cast<uint32_t*>(s_zero)[tid] = 0u;
-  __syncthreads();
+  __shared__ int s_fail;
+  const DecodeKernelPlan& P = p.g;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + P.bar_off);
+  uint64_t* empty = full + P.stages;
+  if (tid == 0) {
+    for (int s = 0; s < P.stages; ++s) { mbar_init(full + s, 1 + 32); mbar_init(empty + s, kNW); }
+    s_fail = 0;
+    fence_barrier_init();
+  }
+  stamp(p, 0, 0);
+  pdl_wait();                    // the routes and the activation vector come from the kernels before this one
+  stamp(p, 1, 0);
+  pdl_launch_dependents();       // the down kernel may become resident and stream its weights from here on
   if (tid < p.top_k) {
-    const long long e = load_index(p.idx, p.idx64, tid);
-    if (e < 0 || e >= p.experts) s_bad = 1;
+    long long e = load_index(p.idx, p.idx64, tid);
+    if (e < 0 || e >= p.experts) {          // the reference skips such a route; here its weight becomes 0 in the
+      atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);     // down kernel and the status word records it
+      e = 0;
+    }
     s_expert[tid] = (int)e;
-    s_weight[tid] = p.w[tid];
   }
   __syncthreads();
-  if (s_bad) {
-    if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_BAD_ARGUMENT);
+
+  stamp(p, 2, 0);
+  const int H = p.hidden;
+  const int U0 = P.kind[0].units, upr = p.inter >> 3;
+  const int ub = first_unit(P, blockIdx.x), ue = first_unit(P, blockIdx.x + 1);
+  volatile int* fail = &s_fail;
+
+  if (warp == kNW) {
+    // ---- producer: rows and scales of every stage, in order ------------------------------------------------
+    int slot = 0, round = 0;
+    for (int u = ub; u < ue && !*fail; ++u) {
+      const int k = u < U0 ? 0 : 1;
+      const DecodeKind& K = P.kind[k];
+      const uint8_t *gsrc, *usrc;
+      const float *gs = nullptr, *us = nullptr;
+      if (k == 0) {
+        const int sl = u / upr, f0 = (u - sl * upr) << 3;
+        const size_t row = (size_t)s_expert[sl] * p.inter + f0;
+        gsrc = p.gate + row * K.row_bytes; usrc = p.up + row * K.row_bytes;
+        if (K.groups) { gs = p.gate_s + row * K.groups; us = p.up_s + row * K.groups; }
+      } else {
+        const size_t row = (size_t)(u - U0) << 3;
+        gsrc = reinterpret_cast<const uint8_t*>(p.sh_gate) + row * K.row_bytes;
+        usrc = reinterpret_cast<const uint8_t*>(p.sh_up) + row * K.row_bytes;
+      }
+      for (int ch = 0; ch < K.nch; ++ch) {
+        if (round > 0 && !wait_or_fail(empty + slot, (round - 1) & 1, fail)) break;
+        uint8_t* st = smem + (size_t)slot * P.stage_bytes;
+        if (lane == 0) mbar_expect_tx(full + slot, (p.debug & 2) ? 0u : 16u * K.ch);
+        __syncwarp();
+        if (lane < 16 && !(p.debug & 2))
+          bulk_g2s(st + lane * K.mstride, (lane < 8 ? gsrc : usrc) + (size_t)(lane & 7) * K.row_bytes + (size_t)ch * K.ch,
+                   K.ch, full + slot);
+        if (K.groups) {              // [16 MMA rows][groups] floats: 8 gate rows then 8 up rows, 16-byte pieces
+          const int pieces = 2 * K.groups;
+          for (int i = lane; i < 2 * pieces; i += 32) {
+            const int up_half = i >= pieces, j = i - up_half * pieces;
+            cp_async16(st + P.scale_off + (size_t)i * 16, (up_half ? us : gs) + j * 4);
+          }
+        }
+        cp_async_arrive(full + slot);
+        if (++slot == P.stages) { slot = 0; ++round; }
+      }
+    }
+    stamp(p, 8, kNW * 32);
+  } else {
+    // ---- consumers ---------------------------------------------------------------------------------------------
+    build_x_fragments(P.kind[0].enc, p.x, H, smem + P.kind[0].frag_off, reinterpret_cast<float*>(smem + P.kind[0].gsum_off), tid);
+    if (P.kind[1].units && P.kind[1].frag_off != P.kind[0].frag_off)
+      build_x_fragments(ENC_BF16, p.x, H, smem + P.kind[1].frag_off, nullptr, tid);
+    named_bar_sync(1, kConsumers);
+    stamp(p, 3, 0);
+    if (warp == 0) { wait_or_fail(full, 0, fail); stamp(p, 4, 0); }
+    float* red = reinterpret_cast<float*>(smem + P.red_off);
+    const uint32_t smem_base = smem_u32(smem);
+    Ring ring{0, 0, 0};
+    const int um = min(max(ub, U0), ue);        // routed units [ub, um), shared-expert units [um, ue)
+    if (ub < um) {
+      if (P.kind[0].enc == ENC_Q4) gateup_units<ENC_Q4>(P, P.kind[0], ub, um, ub, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+      else if (P.kind[0].enc == ENC_Q8) gateup_units<ENC_Q8>(P, P.kind[0], ub, um, ub, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+      else gateup_units<ENC_BF16>(P, P.kind[0], ub, um, ub, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+    }
+    if (um < ue) gateup_units<ENC_BF16>(P, P.kind[1], um, ue, ub, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+    stamp(p, 5, 0);
+  }
+  __syncthreads();
+  stamp(p, 6, 0);
+  if (s_fail) {
+    if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_DEVICE_TIMEOUT);
+    __nanosleep(100000);           // copies still in flight land before the shared memory is given back
     return;
   }
-  if (tid < p.top_k) {
-    int rank = 0;
-    for (int j = 0; j < p.top_k; ++j) rank += (s_expert[j] < s_expert[tid]) || (s_expert[j] == s_expert[tid] && j < tid);
-    s_order[rank] = tid;
-  }
-  __syncthreads();
 
-  const int rb = row_bytes(enc, I), nblk = rb >> 6, gk = I >> 7;
-  const int rtiles = (p.top_k + 1) >> 1;
-  const int bpw = (nblk - warp + kWarps - 1) / kWarps;           // blocks of a routed tile this warp owns
-  const int ppw = (bpw + 1) >> 1;                                // pairs of blocks per tile
-  const int npairs = rtiles * ppw;
-  const int fb = frag_block_bytes(enc);
-  auto tile_of = [&](int t) {
-    DownTile d;
-    const int a = s_order[2 * t], b = 2 * t + 1 < p.top_k ? s_order[2 * t + 1] : -1;
-    const size_t ra = (size_t)s_expert[a] * H + n0 + q;
-    d.wa = p.down + ra * rb + (c << 4);
-    d.sa = enc != ENC_BF16 ? p.down_s + ra * gk : nullptr;
-    d.rec_a = a * rec; d.slot_a = a;
-    if (b >= 0) {
-      const size_t rbw = (size_t)s_expert[b] * H + n0 + q;
-      d.wb = p.down + rbw * rb + (c << 4);
-      d.sb = enc != ENC_BF16 ? p.down_s + rbw * gk : nullptr;
-      d.rec_b = b * rec; d.slot_b = b;
-    } else { d.wb = nullptr; d.sb = nullptr; d.rec_b = d.rec_a; d.slot_b = a; }
-    return d;
-  };
-  // (tile, first block of the pair) walked in order; one iterator for the loads, one for the arithmetic
-  struct Walk { int t, first, left; };
-  auto advance = [&](Walk& w) { w.first += 2; if (w.first >= bpw) { w.first = 0; ++w.t; } --w.left; };
-  auto issue = [&](BlockPair& b, const Walk& w) {
-    if (w.left <= 0) return;
-    const DownTile d = tile_of(w.t);
+  // ---- SwiGLU; every value goes where the down kernel's fragments expect it ----------------------------------
+  if (tid < (ue - ub) * 8) {
+    const int ul = tid >> 3, f = tid & 7, u = ub + ul;
+    const float* r = reinterpret_cast<const float*>(smem + P.red_off) + (size_t)ul * kNW * 16;
+    float gv = 0.f, uv = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (w.first + i < bpw) {
-        const int kb = warp + (w.first + i) * kWarps;
-        const int g = enc == ENC_Q4 ? kb : (kb >> 1);
-        b.wa[i] = ldg_stream(d.wa + ((size_t)kb << 6));
-        if (enc != ENC_BF16) b.sa[i] = d.sa[g];
-        if (d.wb) {
-          b.wb[i] = ldg_stream(d.wb + ((size_t)kb << 6));
-          if (enc != ENC_BF16) b.sb[i] = d.sb[g];
-        } else { b.wb[i] = make_uint4(0, 0, 0, 0); b.sb[i] = 0.f; }
-      }
-    }
-  };
-  float acc_lo = 0.f, acc_hi = 0.f;
-  auto multiply = [&](const BlockPair& b, const Walk& w) {
-    const DownTile d = tile_of(w.t);
-    const int n = min(2, bpw - w.first);
-    const uint8_t* xp[2];
-    float bsa[2], bsb[2], iva[2], ivb[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int kb = warp + (w.first + min(i, n - 1)) * kWarps;
-      // MMA column 0 <- first slot's vector (lanes of quad 0), column 1 <- second slot's (quad 1), others zero
-      const uint8_t* base = q == 0 ? recs + d.rec_a : recs + d.rec_b;
-      xp[i] = q < 2 ? base + (size_t)kb * fb + c * (fb >> 2) : s_zero + c * (fb >> 2);
-      if (enc != ENC_BF16) {
-        bsa[i] = s_bbias[d.slot_a * nblk_all + kb]; bsb[i] = s_bbias[d.slot_b * nblk_all + kb];
-        iva[i] = s_binv[d.slot_a * nblk_all + kb]; ivb[i] = s_binv[d.slot_b * nblk_all + kb];
-      } else { bsa[i] = bsb[i] = 0.f; iva[i] = ivb[i] = 1.f; }
-    }
-    float lo[2], hi[2];
-    if (n == 2) {
-      if (enc == ENC_Q4) mma_full<ENC_Q4, 2, 3>(b.wa, b.wb, xp, lo, hi);
-      else if (enc == ENC_Q8) mma_full<ENC_Q8, 2, 3>(b.wa, b.wb, xp, lo, hi);
-      else mma_full<ENC_BF16, 2, 3>(b.wa, b.wb, xp, lo, hi);
+    for (int w = 0; w < kNW; ++w) { gv += r[w * 16 + f]; uv += r[w * 16 + 8 + f]; }
+    if (u < U0) {
+      const int sl = u / upr, k = ((u - sl * upr) << 3) + f;
+      const DecodeKind& D = p.d.kind[0];
+      const float v = silu_f32(gv) * uv;
+      uint8_t* dst = p.inter_buf + D.ws_off;
+      *reinterpret_cast<__nv_bfloat16*>(dst + frag_offset(D.enc, D.ng, sl, k, 0)) = __float2bfloat16_rn(v);
+      if (D.enc == ENC_Q8)
+        *reinterpret_cast<__nv_bfloat16*>(dst + frag_offset(D.enc, D.ng, sl, k, 1)) =
+            __float2bfloat16_rn(bf16_round(v) * 16.f);
     } else {
-      float dd[2][4];
-      mma_blocks4<false, 2>(enc, n, b.wa, b.wb, xp, true, dd);
-      lo[0] = dd[0][0]; hi[0] = dd[0][3]; lo[1] = hi[1] = 0.f;
+      // Qwen2MoeMLP in BF16: every linear / activation output is rounded
+      const DecodeKind& D = p.d.kind[1];
+      gv = bf16_round(gv); uv = bf16_round(uv);
+      const float v = bf16_round(bf16_round(silu_f32(gv)) * uv);
+      const int k = ((u - U0) << 3) + f, kseg = p.shared_inter / D.nvs, seg = k / kseg;
+      *reinterpret_cast<__nv_bfloat16*>(p.inter_buf + D.ws_off + frag_offset(ENC_BF16, D.ng, seg, k - seg * kseg, 0)) =
+          __float2bfloat16_rn(v);
     }
+  }
+  stamp(p, 7, 0);
+}
+
+// ---- down: the stages of one kind (compile-time encoding), two row pairs at a time --------------------
+// The two stages of a round hold the same columns of different output rows, so they share the fragments
+// and the start values; a warp takes the items i0, i0 + 8, ... of both.
+template <int ENC>
+__device__ __forceinline__ void down_stages(const DecodeKernelPlan& P, const DecodeKind& K, int npairs, uint32_t smem_base,
+                                            uint64_t* full, uint64_t* empty, float* red, Ring& ring, volatile int* fail,
+                                            int warp, int lane, bool skip) {
+  const int g = lane >> 2, t = lane & 3;
+  const int ga = g < K.nvs ? g : 0, gb = g & (K.ng - 1), c0 = (2 * t) & (K.ng - 1);
+  const uint32_t lane_a = ga * K.mstride + t * 16, a8off = K.row_bytes;
+  constexpr uint32_t kChunks = ENC == ENC_BF16 ? 1 : 4;
+  const uint32_t frag_item = kChunks * K.ng * 64, bstep = K.ng * 64;
+  const uint32_t fr = smem_base + K.frag_off + (gb * 4 + t) * 16;
+  const uint32_t gs = smem_base + K.gsum_off + c0 * 4;
+  const uint32_t sc_lane = P.scale_off + (uint32_t)ga * 2 * K.groups * 4;
+  const bool odd = g & 1, diag = t == (g >> 1);
+  const float nbias = -K.bias;
+  for (int ul = 0; ul < npairs; ul += 2) {
+    const bool two = ul + 1 < npairs;
+    const int slot_a = ring.slot, round_a = ring.round;
+    ring.advance(P.stages);
+    const int slot_b = two ? ring.slot : slot_a, round_b = two ? ring.round : round_a;
+    if (two) ring.advance(P.stages);
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    const int i0 = (warp - ring.qbase) & (kNW - 1);
+    if (i0 < K.ips && wait_or_fail(full + slot_a, round_a & 1, fail) && wait_or_fail(full + slot_b, round_b & 1, fail) && !skip) {
+      const uint32_t st_a = smem_base + slot_a * P.stage_bytes, st_b = smem_base + slot_b * P.stage_bytes;
+      for (int i = i0; i < K.ips; i += kNW) {
+        const uint32_t a0[2] = {st_a + lane_a + i * 64, st_b + lane_a + i * 64};
+        const uint32_t bp[2] = {fr + i * frag_item, fr + i * frag_item};
+        float in0[2] = {0.f, 0.f}, in1[2] = {0.f, 0.f}, s[2][2];
+        if (ENC != ENC_BF16) {
+          const float2 sums = lds64(gs + i * K.ng * 4);
+          in0[0] = in0[1] = nbias * sums.x; in1[0] = in1[1] = nbias * sums.y;
+          const int grp = ENC == ENC_Q4 ? i : i >> 1;
+          s[0][0] = lds32(st_a + sc_lane + grp * 4); s[0][1] = lds32(st_a + sc_lane + (K.groups + grp) * 4);
+          s[1][0] = lds32(st_b + sc_lane + grp * 4); s[1][1] = lds32(st_b + sc_lane + (K.groups + grp) * 4);
+        }
+        float c[2][4];
+        items_mma<ENC, 2, true>(a0, a8off, bp, bstep, in0, in1, c);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      if (i < n) {
-        if (enc == ENC_BF16) { acc_lo += lo[i]; acc_hi += hi[i]; }
-        else {
-          acc_lo = fmaf(b.sa[i] * iva[i], lo[i] - bsa[i], acc_lo);
-          acc_hi = fmaf(b.sb[i] * ivb[i], hi[i] - bsb[i], acc_hi);
+        for (int n = 0; n < 2; ++n) {
+          const float v0 = odd ? c[n][1] : c[n][0], v8 = odd ? c[n][3] : c[n][2];     // column g of rows g, g + 8
+          if (ENC != ENC_BF16) { acc[n][0] = fmaf(s[n][0], v0, acc[n][0]); acc[n][1] = fmaf(s[n][1], v8, acc[n][1]); }
+          else { acc[n][0] += v0; acc[n][1] += v8; }
         }
       }
     }
-    if (w.first + 2 >= bpw) {              // last pair of the tile for this warp: park the partial sums
-      if (c == 0) { s_red[w.t][warp][q] = acc_lo; s_red[w.t][warp][8 + q] = acc_hi; }
-      acc_lo = acc_hi = 0.f;
+    __syncwarp();
+    if (lane == 0) { mbar_arrive(empty + slot_a); if (two) mbar_arrive(empty + slot_b); }
+    ring.qbase = (ring.qbase + K.ips) & (kNW - 1);
+    if (diag) {                      // the lane that holds column g
+      float* r = red + ((size_t)ul * kNW + warp) * 16;
+      r[2 * g] = acc[0][0]; r[2 * g + 1] = acc[0][1];
+      if (two) { r[kNW * 16 + 2 * g] = acc[1][0]; r[kNW * 16 + 2 * g + 1] = acc[1][1]; }
     }
-  };
-  Walk wi{0, 0, npairs}, wm{0, 0, npairs};
-  BlockPair b0, b1, b2, b3;
-  issue(b0, wi); advance(wi);            // weights do not depend on kernel A: in flight before the wait
-  issue(b1, wi); advance(wi);
-  issue(b2, wi); advance(wi);
-  issue(b3, wi); advance(wi);
-
-  // sigmoid gate of the shared expert: bf16(sigmoid(bf16(x . wg)))
-  if (S) {
-    float acc = 0.f;
-    for (int k = tid * 2; k < H; k += kThreads * 2) {
-      const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(p.x + k);
-      const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.sh_gatevec + k);
-      acc += __low2float(xv) * __low2float(gv) + __high2float(xv) * __high2float(gv);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) s_tmp[warp] = acc;
-    __syncthreads();
-    if (tid == 0) {
-      float t = 0.f;
-      for (int i = 0; i < kWarps; ++i) t += s_tmp[i];
-      t = bf16_round(t);
-      s_gate = bf16_round(1.f / (1.f + expf(-t)));
-    }
-    __syncthreads();
   }
+}
 
-  pdl_wait();                           // kernel A's records are complete and visible from here on
+// =====================================================================================================
+// Kernel B: down + ordered combine.  Work unit = a pair of output rows (n, n+1): one ring stage holds,
+// per routed slot, those two rows of the slot's expert (MMA rows g and g + 8 for slot g); with a shared
+// expert a second series of stages holds the two rows cut into K segments.
+// =====================================================================================================
+__global__ void __launch_bounds__(kThreadsD, 2) decode_down_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ int s_expert[kMaxSlots], s_order[kMaxSlots];
+  __shared__ float s_weight[kMaxSlots];
+  __shared__ float s_tmp[kNW];
+  __shared__ float s_gate;
+  __shared__ int s_fail, s_present;
+  const DecodeKernelPlan& P = p.d;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.hidden, S = P.kind[1].nvs ? p.shared_inter : 0;
+  const int kinds = S ? 2 : 1;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + P.bar_off);
+  uint64_t* empty = full + P.stages;
+  uint64_t* inter_bar = empty + P.stages;
+  if (tid == 0) {
+    for (int s = 0; s < P.stages; ++s) { mbar_init(full + s, 1 + 32); mbar_init(empty + s, kNW); }
+    mbar_init(inter_bar, 1);
+    s_fail = 0;
+    fence_barrier_init();
+  }
+  // Every gate/up CTA has passed its own dependency wait before this kernel could start, so the routes and
+  // the activation vector are final; only the intermediate must be waited for.
+  stamp(p, 16, 0);
+  pdl_launch_dependents();
+  if (tid < kMaxSlots) {
+    long long e = -1;
+    float w = 0.f;
+    if (tid < p.top_k) { e = load_index(p.idx, p.idx64, tid); w = p.w[tid]; }
+    const bool ok = e >= 0 && e < p.experts;
+    s_expert[tid] = ok ? (int)e : 0;            // invalid routes read expert 0's rows and contribute nothing
+    s_weight[tid] = ok ? w : 0.f;
+    const unsigned present = __ballot_sync(0xffu, ok);
+    // rank among the valid routes by (expert, slot): the accumulation order of the reference's CPU path
+    int rank = 0;
+    for (int j = 0; j < p.top_k; ++j) {
+      const long long ej = load_index(p.idx, p.idx64, j);
+      rank += ((present >> j) & 1u) && (ej < e || (ej == e && j < tid));
+    }
+    if (ok) s_order[rank] = tid;
+    if (tid == 0) s_present = __popc(present);
+  }
+  __syncthreads();
 
-  // ---- copy the records into shared memory -------------------------------------------------------------------
-  // Quantised rows: first the chunk prescales and bias sums; every weight block then gets the smallest prescale
-  // of its chunks (powers of two, so rescaling a chunk is exact), its bias sum and the inverse prescale; the
-  // fragments are copied with their chunk's ratio applied.  BF16 rows: straight 16-byte copies.
-  if (enc != ENC_BF16) {
-    const int chunks = I >> 5, cpb = enc == ENC_Q4 ? 4 : 2;           // 32-value chunks; chunks per weight block
-    const int tailw = (chunks * 8) >> 4;                              // 16-byte words of {prescales, bias sums}
-    const int fragw = (I * 2) >> 4;                                   // 16-byte words of fragments per slot
-    // all loads of this thread go out together (one L2 round trip): its words of the chunk tables and its
-    // first kHold fragment words, which wait in registers until the ratios are known
-    constexpr int kHold = 8;
-    uint4 held[kHold];
-#pragma unroll
-    for (int j = 0; j < kHold; ++j) {
-      const int w = tid + j * kThreads;                               // word index over all slots
-      if (w < p.top_k * fragw) {
-        const int s = w / fragw, i = w - s * fragw;
-        held[j] = __ldcg(reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I) + i);
+  const int pairs = H >> 1;
+  const int rp0 = (int)((long long)blockIdx.x * pairs / gridDim.x), rp1 = (int)((long long)(blockIdx.x + 1) * pairs / gridDim.x);
+  const int npairs = rp1 - rp0;
+  volatile int* fail = &s_fail;
+  stamp(p, 17, 0);
+
+  if (warp == kNW) {
+    // ---- producer: the routed stages of every row pair, then the shared expert's ----------------------------
+    if (p.down_delay_ns > 0) {                 // lets the gate/up kernel's own loads go first
+      const uint64_t t0 = global_ns();
+      while (global_ns() - t0 < (uint64_t)p.down_delay_ns) __nanosleep(200);
+    }
+    int slot = 0, round = 0;
+    for (int k = 0; k < kinds && !*fail; ++k) {
+      const DecodeKind& K = P.kind[k];
+      for (int rp = rp0; rp < rp1; ++rp) {
+        if (round > 0 && !wait_or_fail(empty + slot, (round - 1) & 1, fail)) break;
+        uint8_t* st = smem + (size_t)slot * P.stage_bytes;
+        if (lane == 0) mbar_expect_tx(full + slot, (p.debug & 2) ? 0u : (uint32_t)(K.nvs * 2 * K.row_bytes));
+        __syncwarp();
+        if (k == 0) {
+          if (lane < K.nvs && !(p.debug & 2))          // rows n and n+1 of the slot's expert are adjacent: one copy
+            bulk_g2s(st + lane * K.mstride, p.down + ((size_t)s_expert[lane] * H + 2 * rp) * K.row_bytes,
+                     2u * K.row_bytes, full + slot);
+          if (K.groups) {            // [slot][2 rows][groups] floats in 8-byte pieces
+            for (int i = lane; i < K.nvs * K.groups; i += 32) {
+              const int vs = i / K.groups, j = i - vs * K.groups;
+              cp_async8(st + P.scale_off + (size_t)i * 8,
+                        p.down_s + ((size_t)s_expert[vs] * H + 2 * rp) * K.groups + 2 * j);
+            }
+          }
+        } else if (lane < 2 * K.nvs && !(p.debug & 2)) {   // segment `seg` of rows n, n+1 of the shared expert's down matrix
+          const int seg = lane >> 1, row = lane & 1;
+          bulk_g2s(st + seg * K.mstride + row * K.row_bytes,
+                   reinterpret_cast<const uint8_t*>(p.sh_down) + ((size_t)(2 * rp + row) * K.nvs + seg) * K.row_bytes,
+                   (uint32_t)K.row_bytes, full + slot);
+        }
+        cp_async_arrive(full + slot);
+        if (++slot == P.stages) { slot = 0; ++round; }
       }
     }
-    for (int w = tid; w < p.top_k * tailw; w += kThreads) {
-      const int s = w / tailw, i = w - s * tailw;
-      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.inter_buf + (size_t)s * I) + (size_t)I * 2);
-      reinterpret_cast<uint4*>(recs + (size_t)s * rec + (size_t)I * 2)[i] = __ldcg(src + i);
-    }
-    __syncthreads();
-    for (int it = tid; it < p.top_k * nblk_all; it += kThreads) {
-      const int s = it / nblk_all, kb = it - s * nblk_all;
-      float* sc = reinterpret_cast<float*>(recs + (size_t)s * rec + (size_t)I * 2);
-      const float* cb = sc + chunks;
-      float m = sc[kb * cpb];
-      for (int c2 = 1; c2 < cpb; ++c2) m = fminf(m, sc[kb * cpb + c2]);
-      float bsum = 0.f;
-      for (int c2 = 0; c2 < cpb; ++c2) {
-        const float ratio = m / sc[kb * cpb + c2];                    // a power of two <= 1
-        bsum += cb[kb * cpb + c2] * ratio;
-        sc[kb * cpb + c2] = ratio;                                    // the fragment copy below reads the ratio
-      }
-      s_bbias[it] = bsum;
-      s_binv[it] = 1.f / m;
-    }
-    __syncthreads();
-    auto scaled_store = [&](uint4 w, int s, int i) {
-      const float* ratio = reinterpret_cast<const float*>(recs + (size_t)s * rec + (size_t)I * 2);
-      const __half2 r2 = __float2half2_rn(ratio[i >> 2]);             // 8 values per word, 32 per chunk
-      __half2* h = reinterpret_cast<__half2*>(&w);
-      h[0] = __hmul2(h[0], r2); h[1] = __hmul2(h[1], r2); h[2] = __hmul2(h[2], r2); h[3] = __hmul2(h[3], r2);
-      reinterpret_cast<uint4*>(recs + (size_t)s * rec)[i] = w;
-    };
-#pragma unroll
-    for (int j = 0; j < kHold; ++j) {
-      const int w = tid + j * kThreads;
-      if (w < p.top_k * fragw) { const int s = w / fragw; scaled_store(held[j], s, w - s * fragw); }
-    }
-    for (int w = tid + kHold * kThreads; w < p.top_k * fragw; w += kThreads) {     // shapes with more words
-      const int s = w / fragw, i = w - s * fragw;
-      scaled_store(__ldcg(reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I) + i), s, i);
-    }
+    stamp(p, 25, kNW * 32);
   } else {
-    for (int s = 0; s < p.top_k; ++s) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)s * I);
-      uint4* dst = reinterpret_cast<uint4*>(recs + (size_t)s * rec);
-      for (int i = tid; i < (rec >> 4); i += kThreads) dst[i] = __ldcg(src + i);
-    }
-  }
-  if (S) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.inter_buf + (size_t)p.top_k * I);
-    uint4* dst = reinterpret_cast<uint4*>(xs);
-    for (int i = tid; i < (S * 2) >> 4; i += kThreads) dst[i] = __ldcg(src + i);
-  }
-  __syncthreads();
-
-  // ---- routed tiles: pairs of blocks through the four buffers, four MMA chains per pair ---------------------
-  while (wm.left > 0) {
-    multiply(b0, wm); advance(wm); issue(b0, wi); advance(wi);
-    if (wm.left > 0) { multiply(b1, wm); advance(wm); issue(b1, wi); advance(wi); }
-    if (wm.left > 0) { multiply(b2, wm); advance(wm); issue(b2, wi); advance(wi); }
-    if (wm.left > 0) { multiply(b3, wm); advance(wm); issue(b3, wi); advance(wi); }
-  }
-  if (bpw == 0 && c == 0)
-    for (int t = 0; t < rtiles; ++t) { s_red[t][warp][q] = 0.f; s_red[t][warp][8 + q] = 0.f; }
-
-  // ---- shared expert: one half-filled BF16 tile, K = S, blocks split over the warps in groups of four ------
-  if (S) {
-    const int rbs = 2 * S, nb = rbs >> 6;
-    const uint8_t* rowp = reinterpret_cast<const uint8_t*>(p.sh_down) + (size_t)(n0 + q) * rbs;
-    const uint4 zero4[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-    float acc = 0.f;
-    for (int first = warp; first < nb; first += kWarps * 4) {
-      uint4 w[4];
-      const uint8_t* xp[4];
-      int n = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int kb = first + i * kWarps;
-        if (kb < nb) { w[i] = ldg_stream(rowp + ((size_t)kb << 6) + (c << 4)); n = i + 1; }
-        else w[i] = make_uint4(0, 0, 0, 0);
-        xp[i] = xs + (size_t)min(kb, nb - 1) * 64 + c * 16;
+    // ---- consumers ---------------------------------------------------------------------------------------------
+    if (S) {                       // sigmoid gate of the shared expert: bf16(sigmoid(bf16(x . wg)))
+      float acc = 0.f;
+      for (int k = tid * 2; k < H; k += kConsumers * 2) {
+        const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(p.x + k);
+        const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(p.sh_gatevec + k);
+        acc += __low2float(xv) * __low2float(gv) + __high2float(xv) * __high2float(gv);
       }
-      float d[4][4];
-      mma_blocks4<false>(ENC_BF16, n, w, zero4, xp, true, d);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (i < n) acc += d[i][0];
+      for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) s_tmp[warp] = acc;
+      named_bar_sync(1, kConsumers);
+      if (tid == 0) {
+        float sum = 0.f;
+        for (int i = 0; i < kNW; ++i) sum += s_tmp[i];
+        sum = bf16_round(sum);
+        s_gate = bf16_round(1.f / (1.f + expf(-sum)));
+      }
     }
-    if (c == 0) { s_red[4][warp][q] = acc; s_red[4][warp][8 + q] = 0.f; }
+    stamp(p, 18, 0);
+    pdl_wait();                    // the gate/up kernel's intermediate is complete and visible from here on
+    stamp(p, 19, 0);
+    if (tid == 0) {
+      mbar_expect_tx(inter_bar, (uint32_t)(P.kind[0].frag_bytes + (S ? P.kind[1].frag_bytes : 0)));
+      bulk_g2s(smem + P.kind[0].frag_off, p.inter_buf + P.kind[0].ws_off, (uint32_t)P.kind[0].frag_bytes, inter_bar);
+      if (S) bulk_g2s(smem + P.kind[1].frag_off, p.inter_buf + P.kind[1].ws_off, (uint32_t)P.kind[1].frag_bytes, inter_bar);
+    }
+    const bool have_inter = wait_or_fail(inter_bar, 0, fail);
+    stamp(p, 20, 0);
+    // activation sums per (item, slot) of the quantised rows: the bias every accumulator starts from
+    if (have_inter && P.kind[0].groups) {
+      const DecodeKind& K = P.kind[0];
+      float* gsum = reinterpret_cast<float*>(smem + K.gsum_off);
+      const int total = K.ips * K.ng * 4;
+      for (int base = 0; base < total; base += kConsumers) {
+        const int idx = base + tid;
+        float sum = 0.f;
+        if (idx < total) {
+          const int tt = idx & 3, vs = (idx >> 2) & (K.ng - 1), item = idx / (4 * K.ng);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const uint4 v = *reinterpret_cast<const uint4*>(smem + K.frag_off + ((((item * 4 + r) * K.ng + vs) * 4 + tt) << 4));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q)       // Q8 fragments hold x in words 0 and 2 and 16 x in words 1 and 3
+              if (K.enc == ENC_Q4 || !(q & 1)) sum += __uint_as_float(w[q] << 16) + __uint_as_float(w[q] & 0xffff0000u);
+          }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (idx < total && (idx & 3) == 0) gsum[idx >> 2] = sum;
+      }
+    }
+    named_bar_sync(1, kConsumers);
+    stamp(p, 21, 0);
+
+    const uint32_t smem_base = smem_u32(smem);
+    Ring ring{0, 0, 0};
+    float* red = reinterpret_cast<float*>(smem + P.red_off);
+    if (P.kind[0].enc == ENC_Q4) down_stages<ENC_Q4>(P, P.kind[0], npairs, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+    else if (P.kind[0].enc == ENC_Q8) down_stages<ENC_Q8>(P, P.kind[0], npairs, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+    else down_stages<ENC_BF16>(P, P.kind[0], npairs, smem_base, full, empty, red, ring, fail, warp, lane, (p.debug & 1) != 0);
+    if (S) down_stages<ENC_BF16>(P, P.kind[1], npairs, smem_base, full, empty, reinterpret_cast<float*>(smem + P.red2_off), ring, fail, warp, lane, (p.debug & 1) != 0);
+    stamp(p, 22, 0);
   }
   __syncthreads();
+  stamp(p, 23, 0);
+  if (s_fail) {
+    if (tid == 0) atomicExch(p.sync + 2, (unsigned)ERR_DEVICE_TIMEOUT);
+    __nanosleep(100000);
+    return;
+  }
 
-  // ---- ordered combine: ascending expert, BF16 rounding of every contribution and partial sum --------------
-  if (tid < 8 && n0 + tid < H) {
-    float run = 0.f;
-    for (int r = 0; r < p.top_k; ++r) {
-      const int t = r >> 1, half = r & 1, slot = s_order[r];
-      float y = 0.f;
+  // ---- sums over the warps, then the ordered combine: ascending expert, BF16 rounding of every
+  //      contribution and partial sum ----------------------------------------------------------------------------
+  float* ysum = reinterpret_cast<float*>(smem + P.ysum_off);
+  for (int idx = tid; idx < npairs * kinds * 16; idx += kThreadsD) {
+    const int e = idx & 15, k = (idx >> 4) % kinds, ul = idx / (16 * kinds);
+    const float* r = reinterpret_cast<const float*>(smem + (k ? P.red2_off : P.red_off)) + (size_t)ul * kNW * 16 + e;
+    float y = 0.f;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) y += s_red[t][w][half * 8 + tid];
-      run = bf16_round(run + bf16_round(y * s_weight[slot]));
+    for (int w = 0; w < kNW; ++w) y += r[w * 16];
+    ysum[(ul * 2 + k) * 16 + e] = y;
+  }
+  __syncthreads();
+  if (tid < npairs * 2) {
+    const int ul = tid >> 1, row = tid & 1;
+    const float* y = ysum + (size_t)ul * 32;
+    float run = 0.f;
+    for (int r = 0; r < s_present; ++r) {
+      const int slot = s_order[r];
+      run = bf16_round(run + bf16_round(y[2 * slot + row] * s_weight[slot]));
     }
     if (S) {
-      float y = 0.f;
-#pragma unroll
-      for (int w = 0; w < kWarps; ++w) y += s_red[4][w][tid];
-      run = bf16_round(run + bf16_round(s_gate * bf16_round(y)));
+      float ys = 0.f;
+      for (int seg = 0; seg < P.kind[1].nvs; ++seg) ys += y[16 + 2 * seg + row];
+      run = bf16_round(run + bf16_round(s_gate * bf16_round(ys)));
     }
-    p.out[n0 + tid] = __float2bfloat16_rn(run);
+    p.out[2 * (rp0 + ul) + row] = __float2bfloat16_rn(run);
   }
+  stamp(p, 24, 0);
 }
 
-size_t gateup_smem(const DecodeParams& p) {
-  return (size_t)frag_body_bytes(p.hidden) + 64;                 // x fragments and their bias sums
+// ---- host: plans -------------------------------------------------------------------------------------------
+int pow2_at_least(int v) { int n = 1; while (n < v) n <<= 1; return n; }
+int align_up(int v, int a) { return (v + a - 1) / a * a; }
+
+void describe_kind(DecodeKind& K, int enc, int k) {
+  K.enc = enc;
+  K.row_bytes = row_bytes(enc, k);
+  K.item_bytes = 64;
+  K.r16 = enc == ENC_BF16 ? 1 : 4;
+  K.groups = enc == ENC_BF16 ? 0 : k / 128;
+  K.bias = enc == ENC_Q4 ? 136.f : (enc == ENC_Q8 ? 2304.f : 0.f);
 }
-size_t down_smem(const DecodeParams& p) {
-  const size_t rec = p.enc == ENC_BF16 ? (size_t)p.inter * 2 : (size_t)chunk_record_bytes(p.inter);
-  const size_t blocks = (size_t)p.top_k * (row_bytes(p.enc, p.inter) >> 6);
-  return (size_t)p.top_k * rec + (p.sh_gate ? (size_t)p.shared_inter * 2 : 0) + blocks * 8 + 64;
+
+bool plan_gateup(DecodeParams& p, int sms, int budget) {
+  DecodeKernelPlan& P = p.g;
+  P = DecodeKernelPlan{};
+  const int H = p.hidden;
+  const int S = p.sh_gate ? p.shared_inter : 0;
+  int cursor = 0;
+  for (int k = 0; k < 2; ++k) {
+    DecodeKind& K = P.kind[k];
+    if (k == 1 && !S) break;
+    describe_kind(K, k ? ENC_BF16 : p.enc, H);
+    K.units = k ? S / 8 : p.top_k * (p.inter / 8);
+    // the largest part of a row that is a whole number of items, divides the row and stays <= 1 KB
+    K.ch = 0;
+    for (int c = std::min(K.row_bytes, 1024) / K.item_bytes * K.item_bytes; c >= K.item_bytes; c -= K.item_bytes)
+      if (K.row_bytes % c == 0) { K.ch = c; break; }
+    if (!K.ch) return false;
+    K.nch = K.row_bytes / K.ch;
+    K.ips = K.ch / K.item_bytes;
+    K.mstride = K.ch + 64;
+    P.cost[k] = K.row_bytes;
+  }
+  P.total_cost = (long long)P.kind[0].units * P.cost[0] + (long long)P.kind[1].units * P.cost[1];
+  P.grid = std::min(sms, P.kind[0].units + P.kind[1].units);
+  // fragments: one buffer per encoding
+  for (int k = 0; k < 2; ++k) {
+    DecodeKind& K = P.kind[k];
+    if (k == 1 && !S) break;
+    if (k == 1 && P.kind[0].enc == ENC_BF16) { K.frag_off = P.kind[0].frag_off; K.gsum_off = P.kind[0].gsum_off; K.frag_bytes = P.kind[0].frag_bytes; continue; }
+    K.frag_bytes = K.enc == ENC_Q8 ? H * 4 : H * 2;        // items x chunks x 4 lanes x 16 bytes
+    K.frag_off = cursor; cursor += align_up(K.frag_bytes, 128);
+    K.gsum_off = cursor; cursor += align_up((H / 64) * 4, 128);
+  }
+  int max_units = 0, max_stages = 0;
+  for (int c = 0; c < P.grid; ++c) {
+    const int ub = first_unit(P, c), ue = first_unit(P, c + 1);
+    max_units = std::max(max_units, ue - ub);
+    int st = 0;
+    for (int u = ub; u < ue; ++u) st += P.kind[u < P.kind[0].units ? 0 : 1].nch;
+    max_stages = std::max(max_stages, st);
+  }
+  P.max_units = max_units;
+  P.red_off = cursor; cursor += align_up(max_units * kNW * 16 * 4, 128);
+  const int fixed = cursor;
+  const int mmax = std::max(P.kind[0].mstride, P.kind[1].mstride);
+  P.scale_off = 16 * mmax;
+  P.stage_bytes = align_up(P.scale_off + 16 * P.kind[0].groups * 4, 128);
+  const int room = budget - fixed - 256;
+  P.stages = std::min(max_stages, room / (P.stage_bytes + 16));
+  if (P.stages < 2 && max_stages >= 2) return false;
+  if (P.stages < 1) return false;
+  // stages first (128-byte aligned), then the fixed part, then the barriers
+  const int stage_total = P.stages * P.stage_bytes;
+  for (int k = 0; k < 2; ++k) { P.kind[k].frag_off += stage_total; P.kind[k].gsum_off += stage_total; }
+  P.red_off += stage_total;
+  P.bar_off = stage_total + fixed;
+  P.smem_bytes = P.bar_off + 2 * P.stages * 8 + 16;
+  return P.smem_bytes <= budget;
+}
+
+bool plan_down(DecodeParams& p, int sms) {
+  DecodeKernelPlan& P = p.d;
+  P = DecodeKernelPlan{};
+  const int H = p.hidden, I = p.inter;
+  const int S = p.sh_gate ? p.shared_inter : 0;
+  int cursor = 0, ws = 0;
+  {
+    DecodeKind& K = P.kind[0];
+    describe_kind(K, p.enc, I);
+    K.nvs = p.top_k;
+    K.ng = pow2_at_least(std::max(2, p.top_k));
+    if (K.row_bytes > 4096) return false;
+    K.ips = K.row_bytes / K.item_bytes;
+    K.mstride = 2 * K.row_bytes + 64;
+    K.frag_bytes = K.ips * K.r16 * K.ng * 64;
+    K.ws_off = ws; ws += align_up(K.frag_bytes, 256);
+    K.frag_off = cursor; cursor += align_up(K.frag_bytes, 128);
+    K.gsum_off = cursor; cursor += align_up(K.ips * K.ng * 4, 128);
+  }
+  if (S) {
+    DecodeKind& K = P.kind[1];
+    int nseg = 0;
+    for (int n = 8; n >= 1; n >>= 1)
+      if (S % (n * 32) == 0 && 2 * (S / n) <= 4096) { nseg = n; break; }
+    if (!nseg) return false;
+    describe_kind(K, ENC_BF16, S / nseg);
+    K.nvs = nseg; K.ng = nseg;
+    K.ips = K.row_bytes / K.item_bytes;
+    K.mstride = 2 * K.row_bytes + 64;
+    K.frag_bytes = K.ips * K.r16 * K.ng * 64;
+    K.ws_off = ws; ws += align_up(K.frag_bytes, 256);
+    K.frag_off = cursor; cursor += align_up(K.frag_bytes, 128);
+    K.gsum_off = cursor;
+  }
+  const int pairs = H / 2;
+  P.grid = std::min(sms, pairs);
+  P.max_units = (pairs + P.grid - 1) / P.grid;
+  P.red_off = cursor; cursor += align_up(P.max_units * kNW * 16 * 4, 128);
+  P.red2_off = cursor; if (S) cursor += align_up(P.max_units * kNW * 16 * 4, 128);
+  P.ysum_off = cursor; cursor += align_up(P.max_units * 32 * 4, 128);
+  const int fixed = cursor;
+  const int body = std::max(P.kind[0].nvs * P.kind[0].mstride, P.kind[1].nvs * P.kind[1].mstride);
+  P.scale_off = align_up(body, 16);
+  P.stage_bytes = align_up(P.scale_off + P.kind[0].nvs * 2 * P.kind[0].groups * 4, 128);
+  const int want = P.max_units * (S ? 2 : 1);
+  const int room = kDownSmemMax - fixed - 256;
+  P.stages = std::min(want, room / (P.stage_bytes + 16));
+  if (P.stages < 1 || (P.stages < 2 && want >= 2)) return false;
+  const int stage_total = P.stages * P.stage_bytes;
+  for (int k = 0; k < 2; ++k) { P.kind[k].frag_off += stage_total; P.kind[k].gsum_off += stage_total; }
+  P.red_off += stage_total; P.red2_off += stage_total; P.ysum_off += stage_total;
+  P.bar_off = stage_total + fixed;
+  P.smem_bytes = P.bar_off + (2 * P.stages + 1) * 8 + 16;
+  return P.smem_bytes <= kDownSmemMax;
+}
+
+bool plan_both(DecodeParams& p, int sms) {
+  if (!plan_down(p, sms)) return false;
+  return plan_gateup(p, sms, kPairSmemBudget - align_up(p.d.smem_bytes, 1024));
+}
+
+int down_delay_from_env() {
+  static const int value = [] {
+    const char* s = std::getenv("UMAQ_DECODE_DOWN_DELAY_NS");
+    return s ? std::max(0, std::atoi(s)) : 0;
+  }();
+  return value;
+}
+
+int debug_from_env() {
+  static const int value = [] {
+    const char* s = std::getenv("UMAQ_DECODE_DEBUG");
+    return s ? std::atoi(s) : 0;
+  }();
+  return value;
 }
 
 }  // namespace
 
 size_t decode_workspace_bytes(int top_k, int inter, int shared_inter) {
-  return kDecodeWsHeader + ((size_t)top_k * inter + shared_inter) * sizeof(float);
+  // four bytes per intermediate value cover every encoding's fragments (Q8 keeps x and 16 x); the slot
+  // dimension of the routed fragments is top_k rounded up to a power of two
+  const size_t slots = (size_t)pow2_at_least(std::max(2, top_k));
+  return kDecodeWsHeader + (slots * (size_t)std::max(inter, 0) + (size_t)std::max(shared_inter, 0)) * sizeof(float) + 512;
 }
 
 int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
-  if (p.top_k < 1 || p.top_k > 8 || p.hidden % 512 || p.inter % 128 || p.hidden < 512 || p.inter < 128 ||
-      p.hidden > 2048 || p.inter > 6144 || (p.sh_gate && (p.shared_inter % 128 || p.shared_inter < 128 || p.shared_inter > 6144)) ||
-      p.enc < 0 || p.enc > 2) {
+  const int S = p.sh_gate ? p.shared_inter : 0;
+  if (p.top_k < 1 || p.top_k > kMaxSlots || p.hidden % 256 || p.inter % 128 || p.hidden < 256 || p.inter < 128 ||
+      p.hidden > 8192 || p.inter > 8192 || (S && (S % 64 || S < 64 || S > 32768)) || p.enc < 0 || p.enc > 2) {
     set_error("decode: unsupported shape (hidden %d, intermediate %d, top_k %d, shared %d, encoding %d)", p.hidden,
               p.inter, p.top_k, p.shared_inter, p.enc);
     return ERR_BAD_ARGUMENT;
@@ -801,37 +877,57 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
     set_error("decode: quantised layer without scales");
     return ERR_BAD_ARGUMENT;
   }
-  const size_t smem_a = gateup_smem(p), smem_b = down_smem(p);
+  const uintptr_t all = reinterpret_cast<uintptr_t>(p.gate) | reinterpret_cast<uintptr_t>(p.up) |
+                        reinterpret_cast<uintptr_t>(p.down) | reinterpret_cast<uintptr_t>(p.gate_s) |
+                        reinterpret_cast<uintptr_t>(p.up_s) | reinterpret_cast<uintptr_t>(p.down_s) |
+                        reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.sh_gate) |
+                        reinterpret_cast<uintptr_t>(p.sh_up) | reinterpret_cast<uintptr_t>(p.sh_down) |
+                        reinterpret_cast<uintptr_t>(p.inter_buf);
+  if (all & 15) {
+    set_error("decode: weight, scale, activation and workspace pointers must be 16-byte aligned");
+    return ERR_BAD_ARGUMENT;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) { set_error("decode: no CUDA device"); return ERR_LAUNCH; }
+  if (!plan_both(p, sms)) {
+    set_error("decode: shape needs more shared memory than an SM has (hidden %d, intermediate %d, top_k %d, shared %d, "
+              "encoding %d)", p.hidden, p.inter, p.top_k, p.shared_inter, p.enc);
+    return ERR_UNSUPPORTED;
+  }
+  p.down_delay_ns = down_delay_from_env();
+  p.debug = debug_from_env();
   static thread_local int configured_device = -1;
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(decode_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBudget);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDownSmemMax);
+    // both kernels live on an SM at the same time: ask for the largest shared-memory carve-out
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(decode_gateup_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) { set_error("decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
     configured_device = dev;
   }
-  if (smem_b > 100 * 1024 || smem_a > 48 * 1024) {
-    set_error("decode: shape needs more shared memory than planned");
-    return ERR_UNSUPPORTED;
-  }
-  cudaLaunchConfig_t cfg{};
-  cfg.blockDim = dim3(kThreadsA);
-  cfg.stream = stream;
-  constexpr int kFeat = 8 * kTilesA;
-  cfg.gridDim = dim3(p.top_k * ((p.inter + kFeat - 1) / kFeat) + (p.sh_gate ? (p.shared_inter + kFeat - 1) / kFeat : 0));
-  cfg.dynamicSmemBytes = smem_a;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gateup_kernel, p);
-  if (e != cudaSuccess) { set_error("decode: gate/up launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
-  // The down kernel is chained by programmatic stream serialisation: its CTAs may start while the
-  // gate/up kernel drains, issue their weight loads, and wait on-device before reading its records.
+  // Both kernels are chained to their predecessor by programmatic stream serialisation: their CTAs may
+  // become resident while the kernel before them drains, and wait on the device before they read what
+  // it wrote.
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreadsD);
+  cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cfg.blockDim = dim3(kThreads);
-  cfg.gridDim = dim3((p.hidden + 7) / 8);
-  cfg.dynamicSmemBytes = smem_b;
+  cfg.gridDim = dim3(p.g.grid);
+  cfg.dynamicSmemBytes = p.g.smem_bytes;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_gateup_kernel, p);
+  if (e != cudaSuccess) { set_error("decode: gate/up launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+  cfg.gridDim = dim3(p.d.grid);
+  cfg.dynamicSmemBytes = p.d.smem_bytes;
   e = cudaLaunchKernelEx(&cfg, decode_down_kernel, p);
   if (e != cudaSuccess) { set_error("decode: down launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
   return ERR_NONE;
@@ -839,10 +935,31 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
 
 }  // namespace umaq
 
+// Launch geometry of the two decode kernels for a shape, without launching anything (host arithmetic only).
+extern "C" int umaq_decode_plan(int encoding, int hidden, int intermediate, int top_k, int shared_intermediate, int sms,
+                                int* out, int out_len) {
+  using namespace umaq;
+  if (!out || out_len < 12 || sms < 1) { set_error("umaq_decode_plan: bad argument"); return ERR_BAD_ARGUMENT; }
+  DecodeParams p{};
+  p.enc = encoding; p.hidden = hidden; p.inter = intermediate; p.top_k = top_k;
+  p.shared_inter = shared_intermediate;
+  p.sh_gate = shared_intermediate ? reinterpret_cast<const __nv_bfloat16*>(uintptr_t(16)) : nullptr;   // presence flag only
+  if (top_k < 1 || top_k > kMaxSlots || hidden % 256 || intermediate % 128 || hidden < 256 || intermediate < 128 ||
+      encoding < 0 || encoding > 2 || (shared_intermediate && shared_intermediate % 64)) {
+    set_error("umaq_decode_plan: unsupported shape");
+    return ERR_BAD_ARGUMENT;
+  }
+  if (!plan_both(p, sms)) { set_error("umaq_decode_plan: shape does not fit an SM"); return ERR_UNSUPPORTED; }
+  const int v[12] = {p.g.grid, p.g.stages, p.g.stage_bytes, p.g.smem_bytes, p.g.max_units, p.g.kind[0].ips,
+                     p.d.grid, p.d.stages, p.d.stage_bytes, p.d.smem_bytes, p.d.max_units, p.d.kind[0].ips};
+  for (int i = 0; i < 12; ++i) out[i] = v[i];
+  return ERR_NONE;
+}
+
 // ---- decode without a caller-provided workspace ---------------------------------------------------
 // Scratch of the entry point below: one fixed block per device that loads this library, held until
-// the process exits.  It has the layout of the decode workspace (control words, diagnostics, float32
-// intermediate) and therefore bounds the shapes the entry point accepts.
+// the process exits.  It has the layout of the decode workspace (control words, then the intermediate
+// fragments) and therefore bounds the shapes the entry point accepts.
 namespace {
 constexpr size_t kStaticScratchBytes = 64 * 1024;
 }
@@ -893,17 +1010,18 @@ extern "C" int umaq_moe_decode_static(const umaq_layer* layer, const umaq_shared
   }
   const size_t need = decode_workspace_bytes(top_k, layer->intermediate, s_inter);
   if (need > kStaticScratchBytes) {
-    set_error("umaq_moe_decode_static: top_k * intermediate + shared intermediate = %lld float32 values need %zu bytes "
-              "of scratch, the built-in block holds %zu; use umaq_moe_decode with a caller workspace",
-              (long long)top_k * layer->intermediate + s_inter, need, kStaticScratchBytes);
+    set_error("umaq_moe_decode_static: top_k (rounded up to a power of two) * intermediate + shared intermediate = "
+              "%lld float32 values need %zu bytes of scratch, the built-in block holds %zu; use umaq_moe_decode with a "
+              "caller workspace",
+              (long long)pow2_at_least(std::max(2, top_k)) * layer->intermediate + s_inter, need, kStaticScratchBytes);
     return ERR_WORKSPACE;
   }
   void* scratch = nullptr;
   const int rc = static_scratch_for_current_device(&scratch);
   if (rc != ERR_NONE) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // The block keeps whatever the previous call left.  The control words (status, barrier counter)
-  // must start from zero; the intermediate area is fully rewritten before it is read.
+  // The block keeps whatever the previous call left.  The control words (status) must start from
+  // zero; the intermediate area is fully rewritten before it is read.
   cudaError_t e = cudaMemsetAsync(scratch, 0, 64, st);
   if (e != cudaSuccess) { set_error("umaq_moe_decode_static: cudaMemsetAsync: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
   DecodeParams p{};
@@ -929,6 +1047,6 @@ extern "C" int umaq_moe_decode_static(const umaq_layer* layer, const umaq_shared
   p.out = static_cast<__nv_bfloat16*>(out_bf16);
   uint8_t* ws = static_cast<uint8_t*>(scratch);
   p.sync = reinterpret_cast<unsigned*>(ws);
-  p.inter_buf = reinterpret_cast<float*>(ws + kDecodeWsHeader);
+  p.inter_buf = ws + kDecodeWsHeader;
   return launch_moe_decode(p, st);
 }

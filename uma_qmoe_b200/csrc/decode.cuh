@@ -1,4 +1,4 @@
-// Parameter block and host launcher of the batch-1 decode kernels (decode.cu).
+// Parameter block, launch plan and host launcher of the batch-1 decode kernels (decode.cu).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -9,11 +9,48 @@
 namespace umaq {
 
 // Workspace layout (bytes): [0,1024) header -- the uint32 at byte 8 is the sticky status word;
-// [1024,...) 4 * intermediate bytes per slot (routed slots in route order, then the shared expert) that
-// hold the record the gate/up kernel leaves for the down kernel (fp16 fragments in 32-value chunks with
-// their prescales and bias sums, or the BF16 vector for BF16 rows).  The header must be zero before the
-// first use.
+// [1024,...) the intermediate vectors the gate/up kernel leaves for the down kernel, already in the
+// order of the down kernel's MMA fragments (BF16; Q8 rows hold every value twice, as x and 16 x).
+// The header must be zero before the first use.
 constexpr size_t kDecodeWsHeader = 1024;
+
+// One kind of weight rows a decode kernel streams: the routed experts of the layer, or the Qwen
+// shared expert (always BF16).
+struct DecodeKind {
+  int enc;          // ENC_*
+  int units;        // gate/up kernel: work units of 8 features (8 gate rows + 8 up rows)
+  int row_bytes;    // gate/up: bytes of a weight row; down: bytes of one slot's part of a row
+  int ch;           // gate/up: row bytes per ring stage (row_bytes = nch * ch)
+  int nch;          // gate/up: ring stages per unit
+  int ips;          // items per stage; an item = 16 MMA rows x item_bytes
+  int item_bytes;   // 64 (Q4, Q8) or 128 (BF16)
+  int r16;          // 16-byte activation-fragment chunks per lane and item: 4 (Q4, Q8) or 2 (BF16)
+  int groups;       // float32 scales per weight row (K / 128); 0 for BF16
+  int nvs;          // down: slots of an MMA tile (top_k routed slots, or K segments of the shared expert)
+  int ng;           // down: slot dimension of the fragment layout (power of two >= nvs)
+  int mstride;      // shared-memory stride: gate/up between MMA rows (ch + 64); down between slots (2 row_bytes + 64)
+  int frag_off;     // shared-memory offset of the activation fragments
+  int gsum_off;     // shared-memory offset of the per-item activation sums (bias correction)
+  int frag_bytes;   // bytes of the activation fragments
+  int ws_off;       // byte offset (after the header) of this kind's intermediate fragments in the workspace
+  float bias;       // the constant every decoded code carries: 136 (Q4), 2304 (Q8), 0 (BF16)
+};
+
+struct DecodeKernelPlan {
+  DecodeKind kind[2];       // [0] routed experts, [1] shared expert (units / nvs 0 when absent)
+  long long cost[2];        // gate/up: bytes per unit and MMA row, the weight of a unit when CTAs split the work
+  long long total_cost;
+  int grid;                 // CTAs (<= one per SM)
+  int stages;               // ring depth
+  int stage_bytes;
+  int scale_off;            // offset of the scale area inside a stage
+  int red_off;              // per-warp partial sums [unit][warp][16]
+  int red2_off;             // down: the same for the shared expert
+  int ysum_off;             // down: per (row pair, kind, row, slot) sums over the warps
+  int bar_off;              // mbarriers: full[stages], empty[stages], (down) one for the intermediate copy
+  int smem_bytes;
+  int max_units;            // most units (gate/up) or row pairs (down) any CTA gets
+};
 
 struct DecodeParams {
   // routed experts of one layer, all experts concatenated per projection (expert stride =
@@ -42,11 +79,16 @@ struct DecodeParams {
   __nv_bfloat16* out;         // [hidden]
   // workspace
   unsigned* sync;             // header words; sync[2] is the status word
-  float* inter_buf;           // the slots' records (4 * intermediate bytes apart)
+  uint8_t* inter_buf;         // intermediate fragments (after the header)
+  // launch plans, filled by launch_moe_decode
+  DecodeKernelPlan g;         // gate/up + SwiGLU kernel
+  DecodeKernelPlan d;         // down + combine kernel
+  int down_delay_ns;          // the down kernel's producer waits this long before its first copy
+  int debug;                  // measurement switches: 1 = consumers skip the arithmetic, 2 = producers skip the weight copies
 };
 
 size_t decode_workspace_bytes(int top_k, int inter, int shared_inter);
-// Checks the shapes and launches the two kernels on `stream`.
+// Checks the shapes, plans both kernels and launches them on `stream`.
 int launch_moe_decode(DecodeParams p, cudaStream_t stream);
 
 }  // namespace umaq

@@ -87,8 +87,9 @@ int launch_ep_local_ids(const void* indices, int idx64, long long n, int ranks, 
 int launch_ep_pack(const __nv_bfloat16* x, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                    const int* offsets, int routes, int top_k, int hidden, int ranks, int per_rank, int capacity,
                    __nv_bfloat16* send_rows, int* send_meta, int* route_slot, int* overflow, cudaStream_t stream);
+// experts: ids outside [0, experts) are treated as absent routes
 int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
-                   int top_k, int hidden, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
+                   int top_k, int hidden, int experts, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
                    const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream);
 
 }  // namespace umaq

@@ -416,6 +416,8 @@ __global__ void __launch_bounds__(kSortThreads) route_sort_kernel(const SortArgs
       a.sorted_route[pos] = (int)i;
       a.route_pos[i] = pos;
       a.sorted_weight[pos] = a.weights[i];
+    } else if (live) {
+      a.route_pos[i] = -1;                       // absent or invalid route: no row, the combine skips it
     }
     __syncwarp();
     if (e >= 0 && rank == 0) hist[warp][e] += __popc(peers);
@@ -498,6 +500,8 @@ __global__ void __launch_bounds__(kSortThreads) route_place_kernel(const SortArg
       a.sorted_route[pos] = (int)i;
       a.route_pos[i] = pos;
       a.sorted_weight[pos] = a.weights[i];
+    } else if (live) {
+      a.route_pos[i] = -1;                       // absent or invalid route: no row, the combine skips it
     }
     __syncwarp();
     if (e >= 0 && rank == 0) hist[warp][e] += __popc(peers);
@@ -579,9 +583,9 @@ __global__ void ep_pack_kernel(const __nv_bfloat16* __restrict__ x, const int* _
 // (src/uma_qmoe/qwen_compressed_loader.py:82-85).
 __global__ void __launch_bounds__(256, 4)
 combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restrict__ indices, int idx64,
-               const int* __restrict__ route_pos, int top_k, int hidden, const __nv_bfloat16* __restrict__ shared_out,
-               const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate_vec,
-               __nv_bfloat16* __restrict__ out) {
+               const int* __restrict__ route_pos, int top_k, int hidden, int experts,
+               const __nv_bfloat16* __restrict__ shared_out, const __nv_bfloat16* __restrict__ x,
+               const __nv_bfloat16* __restrict__ gate_vec, __nv_bfloat16* __restrict__ out) {
   __shared__ int order_pos[8];
   __shared__ int present;
   __shared__ float red[8];
@@ -595,12 +599,13 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
   __syncthreads();
   if (tid < 8) {
     // rank of every present route among the present ones by (expert, slot): a stable sort by counting.
-    // Absent routes (expert -1) and routes without a row (position -1) contribute nothing.
-    const bool valid = tid < top_k && raw_e[tid] != -1 && raw_q[tid] >= 0;
+    // Absent routes (expert -1), expert ids outside [0, experts) and routes without a row (position -1)
+    // contribute nothing, as in the reference's kernels (src/uma_qmoe/native/packed_q4_kernel.cu:176).
+    const bool valid = tid < top_k && raw_e[tid] >= 0 && raw_e[tid] < experts && raw_q[tid] >= 0;
     int rank = 0;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const bool vj = j < top_k && raw_e[j] != -1 && raw_q[j] >= 0;
+      const bool vj = j < top_k && raw_e[j] >= 0 && raw_e[j] < experts && raw_q[j] >= 0;
       rank += vj && (raw_e[j] < raw_e[tid] || (raw_e[j] == raw_e[tid] && j < tid));
     }
     if (valid) order_pos[rank] = raw_q[tid];
@@ -739,10 +744,10 @@ int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_
 }
 
 int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
-                   int top_k, int hidden, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
+                   int top_k, int hidden, int experts, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
                    const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream) {
   if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 8) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
-  combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, shared_out, x, gate_vec, out);
+  combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, experts, shared_out, x, gate_vec, out);
   return check_launch("combine");
 }
 

@@ -24,7 +24,6 @@ from __future__ import annotations
 import itertools
 import threading
 from contextlib import contextmanager
-from dataclasses import dataclass
 from typing import Any, Callable, Iterator
 
 from .formats import ContractError
@@ -33,112 +32,146 @@ PLATFORM = "cuda_sm100"
 _KNOWN_PLATFORMS = {"cpu", "cuda_sm121", "hip_gfx1151", PLATFORM}
 
 
-@dataclass
-class _PackState:
-    reader: Any
-    active_calls: int = 0
-    closing: bool = False
+class _Entry:
+    """One registered pack: its reader, how many threads are inside a call on it, and whether it is being closed."""
+
+    __slots__ = ("reader", "in_flight", "closing")
+
+    def __init__(self, reader: Any) -> None:
+        self.reader = reader
+        self.in_flight = 0
+        self.closing = False
 
 
-_PACKS: dict[int, _PackState] = {}
-_PACK_CONDITION = threading.Condition()
-_PACK_IDS = itertools.count(1)
-_PACK_LEASES = threading.local()
+class PackRegistry:
+    """Handles for pack readers, leases for the calls that use them, and the installed backends.
+
+    A lease keeps a pack open from the moment a call looks it up until its kernels are submitted.
+    Leases are counted per thread, so a call may take the lease again further down (the backend
+    does, to reach the reader); only a thread's outermost lease counts as a call in flight.
+    Closing a handle refuses new calls at once and returns when the calls in flight have left.
+    One condition variable guards everything; nothing is held while a backend releases its copies.
+    """
+
+    def __init__(self) -> None:
+        self._cv = threading.Condition()
+        self._entries: dict[int, _Entry] = {}
+        self._handles = itertools.count(1)
+        self._thread = threading.local()
+        self._backends: dict[str, Callable[..., Any]] = {}
+
+    # -- this thread's lease depth per handle
+    def _depths(self) -> dict[int, int]:
+        try:
+            return self._thread.depths
+        except AttributeError:
+            self._thread.depths = {}
+            return self._thread.depths
+
+    def add(self, reader: Any) -> int:
+        if getattr(reader, "mapping_count", None) != 1:
+            raise ContractError("custom operator requires exactly one ExpertPack mapping")
+        with self._cv:
+            handle = next(self._handles)
+            self._entries[handle] = _Entry(reader)
+        return handle
+
+    def remove(self, handle: int) -> None:
+        if self._depths().get(handle):
+            raise ContractError("cannot unregister an ExpertPack from its active call")
+        with self._cv:
+            entry = self._entries.get(handle)
+            if entry is None:
+                return
+            if entry.closing:                       # another thread is closing it: leave when it is gone
+                self._cv.wait_for(lambda: handle not in self._entries)
+                return
+            entry.closing = True
+            self._cv.wait_for(lambda: entry.in_flight == 0)
+            del self._entries[handle]
+            listeners = [b for b in self._backends.values() if callable(getattr(b, "release_pack", None))]
+            self._cv.notify_all()
+        for backend in listeners:
+            backend.release_pack(handle)
+
+    @contextmanager
+    def lease(self, handle: int) -> Iterator[Any]:
+        depths = self._depths()
+        outermost = depths.get(handle, 0) == 0
+        with self._cv:
+            entry = self._entries.get(handle)
+            if entry is None or (entry.closing and outermost):
+                raise RuntimeError(f"unknown or closed ExpertPack handle {handle}")
+            if outermost:
+                entry.in_flight += 1
+        depths[handle] = depths.get(handle, 0) + 1
+        try:
+            yield entry.reader
+        finally:
+            depths[handle] -= 1
+            if depths[handle] == 0:
+                del depths[handle]
+                with self._cv:
+                    entry.in_flight -= 1
+                    self._cv.notify_all()
+
+    def reader(self, handle: int) -> Any:
+        if not self._depths().get(handle):
+            raise RuntimeError("ExpertPack access requires an active operator lease")
+        with self._cv:
+            entry = self._entries.get(handle)
+        if entry is None:
+            raise RuntimeError(f"unknown or closed ExpertPack handle {handle}")
+        return entry.reader
+
+    def set_backend(self, platform: str, implementation: Callable[..., Any]) -> None:
+        if platform not in _KNOWN_PLATFORMS:
+            raise ContractError(f"unsupported custom operator platform {platform!r}")
+        if not callable(implementation):
+            raise ContractError("custom operator backend must be callable")
+        with self._cv:
+            self._backends[platform] = implementation
+
+    def backend(self, platform: str) -> Any:
+        with self._cv:
+            return self._backends.get(platform)
+
+
+_REGISTRY = PackRegistry()
 _LIBRARIES: list[Any] = []
 _REGISTERED = False
-_PERFORMANCE_BACKENDS: dict[str, Callable[..., Any]] = {}
+_REGISTER_LOCK = threading.Lock()
 
+
+# The reference's public functions (src/uma_qmoe/custom_op.py:51-146), same names, arguments and errors.
 
 def register_expert_pack(reader: Any) -> int:
-    if getattr(reader, "mapping_count", None) != 1:
-        raise ContractError("custom operator requires exactly one ExpertPack mapping")
-    with _PACK_CONDITION:
-        handle = next(_PACK_IDS)
-        _PACKS[handle] = _PackState(reader=reader)
-    return handle
+    return _REGISTRY.add(reader)
 
 
 def register_target_pack(reader: Any) -> int:
     """A TargetPack registers exactly like an ExpertPack (one mapping, one handle)."""
-    return register_expert_pack(reader)
-
-
-def _lease_counts() -> dict[int, int]:
-    counts = getattr(_PACK_LEASES, "counts", None)
-    if counts is None:
-        counts = {}
-        _PACK_LEASES.counts = counts
-    return counts
+    return _REGISTRY.add(reader)
 
 
 def unregister_expert_pack(handle: int) -> None:
     """Close a handle: new calls are refused at once, the call returns when the
     calls in flight have drained, then every backend drops its device copies."""
-    if _lease_counts().get(handle, 0):
-        raise ContractError("cannot unregister an ExpertPack from its active call")
-    with _PACK_CONDITION:
-        state = _PACKS.get(handle)
-        if state is None:
-            return
-        if state.closing:
-            while handle in _PACKS:
-                _PACK_CONDITION.wait()
-            return
-        state.closing = True
-        while state.active_calls:
-            _PACK_CONDITION.wait()
-        _PACKS.pop(handle, None)
-        backends = tuple(_PERFORMANCE_BACKENDS.values())
-        _PACK_CONDITION.notify_all()
-    for backend in backends:
-        release = getattr(backend, "release_pack", None)
-        if callable(release):
-            release(handle)
+    _REGISTRY.remove(handle)
 
 
 def register_performance_backend(platform: str, implementation: Callable[..., Any]) -> None:
     """Install an explicit backend for a platform; never used as an implicit fallback."""
-    if platform not in _KNOWN_PLATFORMS:
-        raise ContractError(f"unsupported custom operator platform {platform!r}")
-    if not callable(implementation):
-        raise ContractError("custom operator backend must be callable")
-    with _PACK_CONDITION:
-        _PERFORMANCE_BACKENDS[platform] = implementation
+    _REGISTRY.set_backend(platform, implementation)
 
 
-@contextmanager
-def acquire_expert_pack(handle: int) -> Iterator[Any]:
-    """Hold one pack open across staging and asynchronous kernel submission."""
-    counts = _lease_counts()
-    nested = counts.get(handle, 0) > 0
-    with _PACK_CONDITION:
-        state = _PACKS.get(handle)
-        if state is None or (state.closing and not nested):
-            raise RuntimeError(f"unknown or closed ExpertPack handle {handle}")
-        if not nested:
-            state.active_calls += 1
-        counts[handle] = counts.get(handle, 0) + 1
-    try:
-        yield state.reader
-    finally:
-        with _PACK_CONDITION:
-            left = counts[handle] - 1
-            if left:
-                counts[handle] = left
-            else:
-                del counts[handle]
-                state.active_calls -= 1
-                _PACK_CONDITION.notify_all()
+def acquire_expert_pack(handle: int):
+    """Context manager that holds one pack open across staging and asynchronous kernel submission."""
+    return _REGISTRY.lease(handle)
 
 
 def expert_pack_for_handle(handle: int) -> Any:
-    if _lease_counts().get(handle, 0) == 0:
-        raise RuntimeError("ExpertPack access requires an active operator lease")
-    with _PACK_CONDITION:
-        state = _PACKS.get(handle)
-        if state is None:
-            raise RuntimeError(f"unknown or closed ExpertPack handle {handle}")
-        return state.reader
+    return _REGISTRY.reader(handle)
 
 
 def platform_of(torch: Any, hidden_states: Any) -> str:
@@ -156,8 +189,7 @@ def platform_of(torch: Any, hidden_states: Any) -> str:
 
 
 def _backend_for(platform: str) -> Any:
-    with _PACK_CONDITION:
-        return _PERFORMANCE_BACKENDS.get(platform)
+    return _REGISTRY.backend(platform)
 
 
 def _dispatch(hidden_states, expert_indices, routing_weights, layer_index: int, pack_handle: int,
@@ -201,7 +233,7 @@ def register_moe_forward() -> None:
     ``uma_qmoe`` namespace in this process (the reference itself), its
     definitions are kept and the CUDA entries are replaced by this package's."""
     global _REGISTERED
-    with _PACK_CONDITION:
+    with _REGISTER_LOCK:
         if _REGISTERED:
             return
         import torch

@@ -25,8 +25,13 @@ def random_layer(shape: ModelShape, encoding: str, seed: int, device: torch.devi
     n = len(experts)
 
     def projection(tag: int, rows: int, k: int):
-        gen.manual_seed(seed * 1000003 + tag * 7919 + experts.start)
-        w = (torch.randn(n * rows * k, device=device, generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        # every expert's weights depend only on (seed, projection, GLOBAL expert id): a rank that holds a
+        # subset of the experts holds exactly the bytes the full layer has for them
+        w = torch.empty(n * rows * k, device=device, dtype=torch.bfloat16)
+        for j, e in enumerate(experts):
+            gen.manual_seed(seed * 1000003 + tag * 7919 + e * 104729)
+            w[j * rows * k:(j + 1) * rows * k] = (
+                torch.randn(rows * k, device=device, generator=gen, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         if encoding == "bf16_le":
             return w.view(torch.uint8), None
         return ops.quantize_groups(w, encoding)
