@@ -211,6 +211,42 @@ int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long lo
 int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                  const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
                  void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream);
+/* ---- expert-parallel exchange over peer memory (no counterpart in the reference) -----------------
+ * One process per GPU; every rank holds a buffer of the same layout that all ranks have mapped
+ * (torch.distributed._symmetric_memory or any other peer mapping).  base[p] is rank p's buffer as seen
+ * from this process.  The kernels use plain loads and stores on those addresses (no multicast, no TMA
+ * on peer memory, no library call that is handed a peer pointer). */
+typedef struct umaq_ep_peers {
+  void* base[8];
+  int32_t ranks;
+  int32_t rank;
+} umaq_ep_peers;
+/* Dispatch: for every local token i and every rank p, the token's top_k expert ids (as int32) and routing
+ * weights go to rows rank*tokens + i of p's id / weight tables (at ids_offset / weights_offset in p's
+ * buffer); the activation row goes to the same row of p's row table (rows_offset) only when p owns at
+ * least one of the token's experts (placement as in umaq_ep_local_ids).  present[i*ranks + p] = p if the
+ * row was sent, else -1: the table the final combine uses to skip ranks that hold none of a token's
+ * experts.  Replaces an all-gather of rows, ids and weights. */
+int umaq_ep_push(const void* hidden_bf16 /* device [tokens, hidden] */, const void* expert_indices, int indices_are_int64,
+                 const float* routing_weights, int tokens, int top_k, int hidden, int experts_per_rank, int placement,
+                 const umaq_ep_peers* peers, size_t rows_offset, size_t ids_offset, size_t weights_offset,
+                 int* present /* device [tokens, ranks] */, void* stream);
+/* Barrier across the ranks' streams: writes the next epoch number into every peer's flag word for this
+ * rank (at flags_offset, one uint32 per rank, zero at start) and waits until every peer's word for this
+ * rank has reached it.  *epoch (device, this rank's own, zero at start) counts the barriers.  The wait is
+ * bounded (about two seconds); if it gives up, *status becomes UMAQ_ERR_DEVICE_TIMEOUT and the kernel
+ * returns, so a missing peer costs an error, not a hang. */
+int umaq_ep_barrier(const umaq_ep_peers* peers, size_t flags_offset, unsigned* epoch /* device */,
+                    unsigned* status /* device */, void* stream);
+/* umaq_moe_prefill over the rows every rank pushed (tokens = ranks * segment_rows, expert ids local to
+ * this rank, -1 for routes other ranks own), with the combine writing token (p, i)'s ordered partial sum
+ * straight into row rank*segment_rows + i of rank p's parts table (parts_offset) instead of a local
+ * tensor followed by an all-to-all.  Tokens without a route on this rank are not written; the reader
+ * skips them through the `present` table of umaq_ep_push. */
+int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, const void* expert_indices,
+                              int indices_are_int64, const float* routing_weights, long long tokens, int top_k,
+                              const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, void* workspace,
+                              size_t workspace_bytes, void* stream);
 /* out[t] = BF16 running sum of weighted[route_pos[t*top_k+s]] over the token's routes in
  * ascending expert order: the accumulation order of the reference's CPU path
  * (src/uma_qmoe/custom_op.py:312-338), in place of

@@ -23,6 +23,10 @@ class Layer(C.Structure):
                 ("intermediate", C.c_int32)]
 
 
+class EpPeers(C.Structure):
+    _fields_ = [("base", C.c_void_p * 8), ("ranks", C.c_int32), ("rank", C.c_int32)]
+
+
 class SharedExpert(C.Structure):
     _fields_ = [("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p), ("gate_vec", C.c_void_p),
                 ("intermediate", C.c_int32)]
@@ -55,6 +59,12 @@ SIGNATURES = {
                                     C.c_void_p]),
     "umaq_ep_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "umaq_ep_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                               C.POINTER(EpPeers), C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "umaq_ep_barrier": (C.c_int, [C.POINTER(EpPeers), C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "umaq_moe_prefill_to_peers": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_longlong,
+                                            C.c_int, C.POINTER(EpPeers), C.c_size_t, C.c_int, C.c_void_p, C.c_size_t,
+                                            C.c_void_p]),
     "umaq_combine_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                       C.c_void_p, C.c_void_p]),
     "umaq_quantize_groups": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -180,6 +180,23 @@ int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long lo
                              static_cast<cudaStream_t>(stream));
 }
 
+int umaq_ep_push(const void* hidden_bf16, const void* expert_indices, int indices_are_int64, const float* routing_weights,
+                 int tokens, int top_k, int hidden, int experts_per_rank, int placement, const umaq_ep_peers* peers,
+                 size_t rows_offset, size_t ids_offset, size_t weights_offset, int* present, void* stream) {
+  if (!hidden_bf16 || !expert_indices || !routing_weights || !peers || !present) {
+    set_error("umaq_ep_push: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  return launch_ep_push(static_cast<const __nv_bfloat16*>(hidden_bf16), expert_indices, indices_are_int64, routing_weights,
+                        tokens, top_k, hidden, experts_per_rank, placement, *peers, rows_offset, ids_offset, weights_offset,
+                        present, static_cast<cudaStream_t>(stream));
+}
+
+int umaq_ep_barrier(const umaq_ep_peers* peers, size_t flags_offset, unsigned* epoch, unsigned* status, void* stream) {
+  if (!peers || !epoch || !status) { set_error("umaq_ep_barrier: null argument"); return ERR_BAD_ARGUMENT; }
+  return launch_ep_barrier(*peers, flags_offset, epoch, status, static_cast<cudaStream_t>(stream));
+}
+
 int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                  const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
                  void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream) {
@@ -249,10 +266,11 @@ size_t umaq_prefill_workspace_bytes(long long tokens, int top_k, int num_experts
   return prefill_plan(tokens, top_k, num_experts, hidden, intermediate, shared_intermediate).total;
 }
 
-int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, const void* hidden_bf16,
-                     const void* expert_indices, int indices_are_int64, const float* routing_weights, long long tokens,
-                     int top_k, void* out_bf16, void* workspace, size_t workspace_bytes, void* stream_) {
-  if (!layer || !hidden_bf16 || !expert_indices || !routing_weights || !out_bf16 || !workspace || tokens <= 0) {
+static int prefill_impl(const umaq_layer* layer, const umaq_shared_expert* shared, const void* hidden_bf16,
+                        const void* expert_indices, int indices_are_int64, const float* routing_weights, long long tokens,
+                        int top_k, void* out_bf16, void* workspace, size_t workspace_bytes, void* stream_,
+                        const SegmentedOut* segments) {
+  if (!layer || !hidden_bf16 || !expert_indices || !routing_weights || (!out_bf16 && !segments) || !workspace || tokens <= 0) {
     set_error("umaq_moe_prefill: null argument");
     return ERR_BAD_ARGUMENT;
   }
@@ -332,7 +350,35 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, 
   return launch_combine(reinterpret_cast<const __nv_bfloat16*>(at(pl.yw)), expert_indices, indices_are_int64, sa.route_pos,
                         (int)tokens, top_k, H, E, shared_out, static_cast<const __nv_bfloat16*>(hidden_bf16),
                         shared ? static_cast<const __nv_bfloat16*>(shared->gate_vec) : nullptr,
-                        static_cast<__nv_bfloat16*>(out_bf16), stream);
+                        static_cast<__nv_bfloat16*>(out_bf16), stream, segments);
+}
+
+int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, const void* hidden_bf16,
+                     const void* expert_indices, int indices_are_int64, const float* routing_weights, long long tokens,
+                     int top_k, void* out_bf16, void* workspace, size_t workspace_bytes, void* stream_) {
+  return prefill_impl(layer, shared, hidden_bf16, expert_indices, indices_are_int64, routing_weights, tokens, top_k,
+                      out_bf16, workspace, workspace_bytes, stream_, nullptr);
+}
+
+int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, const void* expert_indices,
+                              int indices_are_int64, const float* routing_weights, long long tokens, int top_k,
+                              const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, void* workspace,
+                              size_t workspace_bytes, void* stream_) {
+  if (!peers || peers->ranks < 1 || peers->ranks > kMaxPeers || peers->rank < 0 || peers->rank >= peers->ranks ||
+      segment_rows < 1 || tokens != (long long)segment_rows * peers->ranks || !layer) {
+    set_error("umaq_moe_prefill_to_peers: bad peer table or segment size");
+    return ERR_BAD_ARGUMENT;
+  }
+  SegmentedOut seg{};
+  for (int p = 0; p < peers->ranks; ++p) {
+    if (!peers->base[p]) { set_error("umaq_moe_prefill_to_peers: null peer buffer"); return ERR_BAD_ARGUMENT; }
+    seg.ptr[p] = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(peers->base[p]) + parts_offset);
+  }
+  seg.rows = segment_rows;
+  seg.row0 = peers->rank * segment_rows;
+  seg.skip_empty = 1;
+  return prefill_impl(layer, nullptr, hidden_bf16, expert_indices, indices_are_int64, routing_weights, tokens, top_k,
+                      nullptr, workspace, workspace_bytes, stream_, &seg);
 }
 
 }  // extern "C"

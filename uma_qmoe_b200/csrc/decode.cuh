@@ -22,13 +22,14 @@ struct DecodeKind {
   int row_bytes;    // gate/up: bytes of a weight row; down: bytes of one slot's part of a row
   int ch;           // gate/up: row bytes per ring stage (row_bytes = nch * ch)
   int nch;          // gate/up: ring stages per unit
-  int ips;          // items per stage; an item = 16 MMA rows x item_bytes
-  int item_bytes;   // 64 (Q4, Q8) or 128 (BF16)
-  int r16;          // 16-byte activation-fragment chunks per lane and item: 4 (Q4, Q8) or 2 (BF16)
+  int ips;          // items per stage; an item = 64 bytes of each of the 16 MMA rows
+  int item_bytes;   // 64
+  int r16;          // 16-byte activation-fragment chunks per lane and item: 4 (Q4, Q8) or 1 (BF16)
   int groups;       // float32 scales per weight row (K / 128); 0 for BF16
   int nvs;          // down: slots of an MMA tile (top_k routed slots, or K segments of the shared expert)
   int ng;           // down: slot dimension of the fragment layout (power of two >= nvs)
-  int mstride;      // shared-memory stride: gate/up between MMA rows (ch + 64); down between slots (2 row_bytes + 64)
+  int mstride;      // shared-memory stride: gate/up from the gate block to the up block of a stage (8 ch + 64);
+                    // down between the slots' row blocks
   int frag_off;     // shared-memory offset of the activation fragments
   int gsum_off;     // shared-memory offset of the per-item activation sums (bias correction)
   int frag_bytes;   // bytes of the activation fragments
@@ -47,7 +48,13 @@ struct DecodeKernelPlan {
   int red_off;              // per-warp partial sums [unit][warp][16]
   int red2_off;             // down: the same for the shared expert
   int ysum_off;             // down: per (row pair, kind, row, slot) sums over the warps
-  int bar_off;              // mbarriers: full[stages], empty[stages], (down) one for the intermediate copy
+  int bar_off;              // mbarriers: full[stages], empty[stages]
+  int bulk_scales;          // scales travel as bulk copies (sizes and offsets are multiples of 16 bytes), else as 8-byte cp.async
+  int resident;             // down: the CTA's whole share is loaded at once, slot by slot (no ring)
+  int pair_stride;          // down: bytes from one row pair's weights to the next (ring: stage_bytes)
+  int sc_base;              // down: offset of the scales (ring: inside a stage)
+  int sc_pair_stride;       // down: bytes from one row pair's scales to the next
+  int sc_slot_stride;       // down: bytes from one slot's scales to the next
   int smem_bytes;
   int max_units;            // most units (gate/up) or row pairs (down) any CTA gets
 };
@@ -78,7 +85,8 @@ struct DecodeParams {
   int shared_inter;
   __nv_bfloat16* out;         // [hidden]
   // workspace
-  unsigned* sync;             // header words; sync[2] is the status word
+  unsigned* sync;             // header words; sync[2] is the status word, sync[4] counts finished gate/up CTAs,
+                              // sync[5] finished down CTAs (both return to zero at the end of a call)
   uint8_t* inter_buf;         // intermediate fragments (after the header)
   // launch plans, filled by launch_moe_decode
   DecodeKernelPlan g;         // gate/up + SwiGLU kernel

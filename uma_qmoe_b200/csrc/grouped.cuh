@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "../../include/umaq_b200.h"
+
 namespace umaq {
 
 // Device-side view handed to the grouped GEMM kernel.
@@ -84,12 +86,30 @@ int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_
                        int permute, __nv_bfloat16* out, const int* valid_rows, cudaStream_t stream);
 int launch_ep_local_ids(const void* indices, int idx64, long long n, int ranks, int rank, int per_rank, int placement,
                         int* out, cudaStream_t stream);
+// expert-parallel exchange over peer memory (ep_peer.cu)
+int launch_ep_push(const __nv_bfloat16* x, const void* indices, int idx64, const float* weights, int tokens, int top_k,
+                   int hidden, int per_rank, int placement, const umaq_ep_peers& peers, size_t rows_offset,
+                   size_t ids_offset, size_t weights_offset, int* present, cudaStream_t stream);
+int launch_ep_barrier(const umaq_ep_peers& peers, size_t flags_offset, unsigned* epoch, unsigned* status,
+                      cudaStream_t stream);
 int launch_ep_pack(const __nv_bfloat16* x, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                    const int* offsets, int routes, int top_k, int hidden, int ranks, int per_rank, int capacity,
                    __nv_bfloat16* send_rows, int* send_meta, int* route_slot, int* overflow, cudaStream_t stream);
+// Where the combine writes: by default row t of `out`.  With rows > 0 the tokens come in segments of `rows`
+// (one per source rank of an expert-parallel exchange) and token t goes to row row0 + t % rows of
+// ptr[t / rows] -- a buffer that may live on another GPU (plain peer stores); skip_empty leaves the rows
+// of tokens without any present route unwritten.
+constexpr int kMaxPeers = 8;
+struct SegmentedOut {
+  __nv_bfloat16* ptr[kMaxPeers];
+  int rows;
+  int row0;
+  int skip_empty;
+};
 // experts: ids outside [0, experts) are treated as absent routes
 int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
                    int top_k, int hidden, int experts, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
-                   const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream);
+                   const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream,
+                   const SegmentedOut* segments = nullptr);
 
 }  // namespace umaq

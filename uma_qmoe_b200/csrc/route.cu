@@ -585,7 +585,7 @@ __global__ void __launch_bounds__(256, 4)
 combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restrict__ indices, int idx64,
                const int* __restrict__ route_pos, int top_k, int hidden, int experts,
                const __nv_bfloat16* __restrict__ shared_out, const __nv_bfloat16* __restrict__ x,
-               const __nv_bfloat16* __restrict__ gate_vec, __nv_bfloat16* __restrict__ out) {
+               const __nv_bfloat16* __restrict__ gate_vec, __nv_bfloat16* __restrict__ out, const SegmentedOut seg) {
   __shared__ int order_pos[8];
   __shared__ int present;
   __shared__ float red[8];
@@ -630,6 +630,11 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
   __syncthreads();
   // all of a column pair's contributions are loaded first (independent loads), then summed in order
   const int n = present;
+  __nv_bfloat16* dst = out + (size_t)t * hidden;
+  if (seg.rows > 0) {                              // segmented output, possibly in a peer GPU's memory
+    if (seg.skip_empty && n == 0) return;
+    dst = seg.ptr[t / seg.rows] + (size_t)(seg.row0 + t % seg.rows) * hidden;
+  }
   unsigned rows[8];                               // row starts in 16-byte words (fewer registers than pointers)
 #pragma unroll
   for (int s = 0; s < 8; ++s) rows[s] = (unsigned)(((size_t)order_pos[s < n ? s : 0] * hidden) >> 3);
@@ -667,7 +672,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
     __nv_bfloat162 p2 = __floats2bfloat162_rn(r[4], r[5]), p3 = __floats2bfloat162_rn(r[6], r[7]);
     o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
     o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + c) = o;
+    *reinterpret_cast<uint4*>(dst + c) = o;
   }
 }
 
@@ -745,9 +750,12 @@ int launch_gather_rows(const __nv_bfloat16* x, const int* sorted_route, int top_
 
 int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64, const int* route_pos, int tokens,
                    int top_k, int hidden, int experts, const __nv_bfloat16* shared_out, const __nv_bfloat16* x,
-                   const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream) {
+                   const __nv_bfloat16* gate_vec, __nv_bfloat16* out, cudaStream_t stream,
+                   const SegmentedOut* segments) {
   if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 8) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
-  combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, experts, shared_out, x, gate_vec, out);
+  SegmentedOut seg{};
+  if (segments) seg = *segments;
+  combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, experts, shared_out, x, gate_vec, out, seg);
   return check_launch("combine");
 }
 

@@ -83,6 +83,14 @@ class CudaKernels:
     def local_ids(self, indices: torch.Tensor, ranks: int, rank: int, per_rank: int, interleaved: bool) -> torch.Tensor:
         return self.ops.ep_local_ids(indices, ranks, rank, per_rank, interleaved)
 
+    def local_moe_to_peers(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor, ex: Any) -> None:
+        """Like :meth:`local_moe`, but every token's partial sum goes straight into its owner rank's buffer."""
+        n, top_k = local_indices.shape
+        if self._ws_moe is None or self._ws_moe_shape != (n, top_k):
+            self._ws_moe = self.ops.prefill_workspace(self.layer, n, top_k, None, x.device)
+            self._ws_moe_shape = (n, top_k)
+        self.ops.moe_prefill_to_peers(self.layer, x, local_indices, weights, ex.peers, ex.off_parts, ex.tokens, self._ws_moe)
+
     def local_moe(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """This rank's experts over all rows of x; local_indices -1 = the route belongs to another rank."""
         n, top_k = local_indices.shape
@@ -90,6 +98,64 @@ class CudaKernels:
             self._ws_moe = self.ops.prefill_workspace(self.layer, n, top_k, None, x.device)
             self._ws_moe_shape = (n, top_k)
         return self.ops.moe_prefill(self.layer, x, local_indices, weights, self._ws_moe)
+
+
+class PeerExchange:
+    """One buffer per rank that every rank can address, and this rank's view of all of them.
+
+    Layout (the same on every rank; t = tokens per rank, G ranks): rows ``[G*t, H]`` BF16, ids ``[G*t, k]``
+    int32 and weights ``[G*t, k]`` float32 pushed by the ranks, ``parts [G*t, H]`` BF16 written by the ranks'
+    combine kernels (row ``p*t + i`` = rank p's partial sum for local token i), and one flag word per rank for
+    the barrier.  ``buffers`` may be given (one CUDA byte tensor per rank, all on one device) to run several
+    ranks in one process; otherwise the buffer comes from ``torch.distributed._symmetric_memory`` and is
+    mapped by all ranks of ``group``.
+    """
+
+    def __init__(self, tokens: int, hidden: int, top_k: int, rank: int, world: int, device: torch.device,
+                 group: Any = None, buffers: Optional[list] = None) -> None:
+        from . import ops
+        align = lambda n: (n + 255) // 256 * 256
+        rows = world * tokens
+        self.tokens, self.hidden, self.top_k, self.rank, self.world = tokens, hidden, top_k, rank, world
+        self.off_rows = 0
+        self.off_ids = align(rows * hidden * 2)
+        self.off_w = self.off_ids + align(rows * top_k * 4)
+        self.off_parts = self.off_w + align(rows * top_k * 4)
+        self.off_flags = self.off_parts + align(rows * hidden * 2)
+        self.nbytes = self.off_flags + 256
+        if buffers is not None:
+            self.buffer = buffers[rank]
+            pointers = [b.data_ptr() for b in buffers]
+            self.handle = None
+        else:
+            import torch.distributed._symmetric_memory as symm
+            self.buffer = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.buffer.zero_()
+            self.handle = symm.rendezvous(self.buffer, dist.group.WORLD if group is None else group)
+            pointers = [int(p) for p in self.handle.buffer_ptrs]
+        if self.buffer.numel() < self.nbytes:
+            raise RuntimeError("exchange buffer too small")
+        self.peers = ops.ep_peers(pointers, rank)
+        view = lambda off, n, dtype: self.buffer[off:off + n].view(dtype)
+        self.all_x = view(self.off_rows, rows * hidden * 2, torch.bfloat16).view(rows, hidden)
+        self.all_idx = view(self.off_ids, rows * top_k * 4, torch.int32).view(rows, top_k)
+        self.all_w = view(self.off_w, rows * top_k * 4, torch.float32).view(rows, top_k)
+        self.parts = view(self.off_parts, rows * hidden * 2, torch.bfloat16).view(rows, hidden)
+        self.present = torch.empty((tokens, world), dtype=torch.int32, device=device)
+        self.part_pos = (torch.arange(world, dtype=torch.int32, device=device)[None, :] * tokens +
+                         torch.arange(tokens, dtype=torch.int32, device=device)[:, None]).contiguous()
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    @staticmethod
+    def nbytes_for(tokens: int, hidden: int, top_k: int, world: int) -> int:
+        align = lambda n: (n + 255) // 256 * 256
+        rows = world * tokens
+        return 2 * align(rows * hidden * 2) + 2 * align(rows * top_k * 4) + 256
+
+    def timed_out(self) -> bool:
+        """True if a barrier gave up waiting for a peer (synchronises)."""
+        return int(self.status.item()) != 0
 
 
 @dataclass
@@ -198,6 +264,34 @@ class ExpertParallelMoE:
         partial = k.local_moe(all_x, local, all_w)
         dist.all_to_all_single(parts, partial, group=self.group)      # parts[r * t + i] = rank r's sum for my token i
         return k.combine(parts, rank_ids, part_pos)
+
+    # ---- exchange over peer memory: no collective library on the data path --------------------------------
+    def peer_push(self, ex: PeerExchange, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> None:
+        """Phase 1: this rank's rows (to the ranks that own one of the token's experts) and routes (to all)."""
+        self.kernels.ops.ep_push(x, indices, weights, self.per_rank, self.placement == "interleaved", ex.peers,
+                                 ex.off_rows, ex.off_ids, ex.off_w, ex.present)
+
+    def peer_compute(self, ex: PeerExchange) -> None:
+        """Phase 2: this rank's experts over everything that was pushed to it; the combine writes every token's
+        partial sum into its owner's buffer."""
+        k = self.kernels
+        local = k.local_ids(ex.all_idx, self.world, self.rank, self.per_rank, self.placement == "interleaved")
+        k.local_moe_to_peers(ex.all_x, local, ex.all_w, ex)
+
+    def peer_combine(self, ex: PeerExchange) -> torch.Tensor:
+        """Phase 3: the partial sums of the ranks that worked on a token, added in rank order."""
+        return self.kernels.combine(ex.parts, ex.present, ex.part_pos)
+
+    def forward_peer(self, ex: PeerExchange, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """Same result contract as :meth:`forward_gather`, with the two exchanges done by this library's own
+        kernels over peer memory: rows travel only to ranks that own one of the token's experts, partial sums
+        only back from ranks that did some work, and the only synchronisation is a flag barrier per phase."""
+        ops = self.kernels.ops
+        self.peer_push(ex, x, indices, weights)
+        ops.ep_barrier(ex.peers, ex.off_flags, ex.epoch, ex.status)
+        self.peer_compute(ex)
+        ops.ep_barrier(ex.peers, ex.off_flags, ex.epoch, ex.status)
+        return self.peer_combine(ex)
 
     def plan(self, counts: torch.Tensor) -> ExchangePlan:
         """Rows this rank sends to / receives from every rank (one small collective + one host read)."""

@@ -258,6 +258,52 @@ def ep_pack(hidden: torch.Tensor, routes: SortedRoutes, sorted_key: torch.Tensor
     return route_slot
 
 
+def ep_peers(pointers: list[int], rank: int) -> _native.EpPeers:
+    """Table of the ranks' exchange buffers as seen from this process (see ``umaq_ep_peers``)."""
+    if not 1 <= len(pointers) <= 8 or not 0 <= rank < len(pointers):
+        raise RuntimeError("between 1 and 8 ranks, and a rank inside that range")
+    table = _native.EpPeers()
+    for i, ptr in enumerate(pointers):
+        table.base[i] = ptr
+    table.ranks, table.rank = len(pointers), rank
+    return table
+
+
+def ep_push(hidden: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, experts_per_rank: int, interleaved: bool,
+            peers: _native.EpPeers, rows_offset: int, ids_offset: int, weights_offset: int, present: torch.Tensor) -> None:
+    """Rows and routes of the local tokens into every rank's buffer (see ``umaq_ep_push``)."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    tokens, top_k = indices.shape
+    if weights.dtype != torch.float32 or weights.shape != indices.shape or indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("routes must be int32/int64 indices and float32 weights of one shape")
+    if present.dtype != torch.int32 or present.numel() != tokens * peers.ranks:
+        raise RuntimeError("present must be int32 [tokens, ranks]")
+    code = _native.lib().umaq_ep_push(hidden.data_ptr(), indices.contiguous().data_ptr(), int(indices.dtype == torch.int64),
+                                      weights.contiguous().data_ptr(), tokens, top_k, hidden.shape[1], experts_per_rank,
+                                      0 if interleaved else 1, C.byref(peers), rows_offset, ids_offset, weights_offset,
+                                      present.data_ptr(), _stream(hidden.device))
+    _native.check(code, "umaq_ep_push")
+
+
+def ep_barrier(peers: _native.EpPeers, flags_offset: int, epoch: torch.Tensor, status: torch.Tensor) -> None:
+    """Barrier across the ranks' streams (bounded device-side wait; see ``umaq_ep_barrier``)."""
+    code = _native.lib().umaq_ep_barrier(C.byref(peers), flags_offset, epoch.data_ptr(), status.data_ptr(),
+                                         _stream(epoch.device))
+    _native.check(code, "umaq_ep_barrier")
+
+
+def moe_prefill_to_peers(layer: DeviceLayer, hidden: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor,
+                         peers: _native.EpPeers, parts_offset: int, segment_rows: int, workspace: torch.Tensor) -> None:
+    """This rank's experts over the pushed rows of all ranks, partial sums written into the owners' buffers."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    tokens, top_k = local_indices.shape
+    code = _native.lib().umaq_moe_prefill_to_peers(
+        C.byref(layer.struct()), hidden.data_ptr(), local_indices.data_ptr(), int(local_indices.dtype == torch.int64),
+        weights.data_ptr(), tokens, top_k, C.byref(peers), parts_offset, segment_rows, workspace.data_ptr(),
+        workspace.numel(), _stream(hidden.device))
+    _native.check(code, "umaq_moe_prefill_to_peers")
+
+
 def combine_routes(weighted: torch.Tensor, indices: torch.Tensor, route_pos: torch.Tensor,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ordered BF16 top-k combine of per-route weighted outputs."""
