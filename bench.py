@@ -275,7 +275,9 @@ def native_arm(args) -> None:
     shape = syn.OLMOE
     mine = range(rank, shape.experts, world)      # interleaved expert placement (ExpertParallelMoE's default)
     backend = native_backend.install_mixed_target_backend()
-    stack = MoEStack.build(shape, "q4_group128", LAYERS, SEED, dev, renormalize=True, skew=1.0, experts=mine)
+    # with several ranks the experts of every layer are relabelled so that the interleaved placement is balanced
+    stack = MoEStack.build(shape, "q4_group128", LAYERS, SEED, dev, renormalize=True, skew=1.0, experts=mine,
+                           balance_ranks=world if os.environ.get("UMAQ_EP_BALANCE", "1") == "1" else 0)
     share = TOKENS // world
     x_host = syn.activations(SEED, TOKENS)[rank * share:(rank + 1) * share].contiguous().pin_memory()
     x_dev = x_host.to(dev)
@@ -296,17 +298,36 @@ def native_arm(args) -> None:
             return x
         launches_per_step = LAYERS * 7          # router, sort (2 kernels), gather, 2 grouped GEMMs, combine
     else:
-        from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE
+        from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE, PeerExchange
+        dist = torch.distributed
         eps = [ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k) for layer in stack.layers]
+        # Exchange over peer memory (this library's own push / combine kernels on buffers every rank has mapped) when
+        # all ranks can map them; otherwise the collective-library exchange (all-gather + all-to-all).
+        ex, why = None, ""
+        if os.environ.get("UMAQ_EP_EXCHANGE", "peer") == "peer":
+            try:
+                ex = PeerExchange(share, shape.hidden, shape.top_k, rank, world, dev)
+            except Exception as exc:
+                why = f"{type(exc).__name__}: {exc}"[:160]
+        ok = torch.tensor([1 if ex is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if not int(ok.item()):
+            ex = None
+        exchange_name = ("peer memory: rows pushed to the ranks that own one of the token's experts, partial sums written "
+                         "into the owner's buffer by the combine kernel, flag barriers (no collective on the data path)"
+                         if ex is not None else "all_gather rows + all_to_all partial sums (NCCL)" + (f"; peer mapping failed: {why}" if why else ""))
+        dist.barrier()
 
-        exchange = {"mode": "gather"}           # all-gather rows, local experts over all tokens, all-to-all partial sums
+        def layer_forward(l, x, w, idx):
+            return eps[l].forward_peer(ex, x, idx, w) if ex is not None else eps[l].forward_gather(x, idx, w)
 
         def run_stack(x):
             for l in range(LAYERS):
                 w, idx = stack.route(l, x)
-                x = rms_renorm(eps[l].forward_gather(x, idx, w))
+                x = rms_renorm(layer_forward(l, x, w, idx))
             return x
-        launches_per_step = LAYERS * 8          # router; sort (2 kernels), gather, 2 GEMMs, combine over all tokens; sum of the partials
+        # router; push, barrier, routing table, sort (2), gather, 2 GEMMs, combine to peers, barrier, final combine
+        launches_per_step = LAYERS * (12 if ex is not None else 8)
 
     def step_resident():
         run_stack(x_dev)
@@ -329,7 +350,7 @@ def native_arm(args) -> None:
             "e2e": {"value": TOKENS / (ms_e2e / 1e3), "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2 * world},
             "gpu_launches": launches, "clocks": clocks.summary(),
-            **({"exchange": "all_gather rows + all_to_all partial sums (NCCL)"} if world > 1 else {}),
+            **({"exchange": exchange_name} if world > 1 else {}),
             "tflops_step": 65536 * 12_582_912 * LAYERS / (ms / 1e3) / 1e12 / world}
 
     if rank == 0 and world == 1:
@@ -374,10 +395,81 @@ def native_arm(args) -> None:
                           "status": ops.workspace_status(wsd)}
         line["gpu_launches"] += 13 + 2 * (20 + 3) * LAYERS      # roofline leg + two decode kernels per layer and pass
         line["cpu_baseline"] = cpu_baseline_subprocess()
+    if world > 1:
+        line["ep_check"] = ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world)
+        line["phases_us"] = ep_phases(stack, eps, ex, x_dev, shape, dev, world)
+        if ex is not None:
+            line["ep_check"]["barrier_timed_out"] = ex.timed_out()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        torch.distributed.barrier()
         torch.distributed.destroy_process_group()
+
+
+def ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world) -> dict:
+    """Outside the timed region: layer 0 over this rank's tokens through the measured exchange and through the
+    exact-count exchange, against the one-GPU operator on the same tokens with the full layer 0 (every rank builds
+    it from the same seeds).  Worst case over the ranks."""
+    from oracle import moe_oracle as orc
+    from uma_qmoe_b200 import ops
+    from uma_qmoe_b200.stack import random_layer
+    dist = torch.distributed
+    full = random_layer(shape, "q4_group128", SEED, dev, stack.orders[0])      # the whole layer 0, same labels
+    w, idx = stack.route(0, x_dev)
+    ws = ops.prefill_workspace(full, x_dev.shape[0], shape.top_k, None, dev)
+    want = ops.moe_prefill(full, x_dev, idx, w, ws)
+    got = layer_forward(0, x_dev, w, idx)
+    exact = eps[0].forward(x_dev, idx, w)
+    torch.cuda.synchronize()
+    m = orc.compare(got.cpu(), want.cpu())
+    stats = torch.tensor([m["max_abs"], -m["cosine"], 0.0 if torch.equal(exact, want) else 1.0], device=dev, dtype=torch.float64)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    del full, ws
+    return {"max_abs": float(stats[0]), "cosine": float(-stats[1]), "bit_equal_exact_path": bool(stats[2] == 0),
+            "tolerance": "max_abs <= 2e-2, cosine >= 0.9999 against the one-GPU operator", "layer": 0,
+            "pass": bool(stats[0] <= 2e-2 and -stats[1] >= 0.9999 and stats[2] == 0)}
+
+
+def ep_phases(stack, eps, ex, x_dev, shape, dev, world) -> dict:
+    """CUDA-event time of every phase of one layer's expert-parallel step (layer 0, median of 5, max over ranks)."""
+    from uma_qmoe_b200.stack import rms_renorm
+    dist = torch.distributed
+    ep = eps[0]
+    ops = ep.kernels.ops
+    w, idx = stack.route(0, x_dev)
+    if ex is not None:
+        phases = [("router", lambda: stack.route(0, x_dev)),
+                  ("push", lambda: ep.peer_push(ex, x_dev, idx, w)),
+                  ("barrier_1", lambda: ops.ep_barrier(ex.peers, ex.off_flags, ex.epoch, ex.status)),
+                  ("local_experts_and_combine_to_peers", lambda: ep.peer_compute(ex)),
+                  ("barrier_2", lambda: ops.ep_barrier(ex.peers, ex.off_flags, ex.epoch, ex.status)),
+                  ("final_combine", lambda: ep.peer_combine(ex)),
+                  ("rms_norm", lambda: rms_renorm(x_dev))]
+    else:
+        phases = [("router", lambda: stack.route(0, x_dev)),
+                  ("whole_layer_all_gather_local_experts_all_to_all_combine", lambda: ep.forward_gather(x_dev, idx, w)),
+                  ("rms_norm", lambda: rms_renorm(x_dev))]
+    times = {name: [] for name, _ in phases}
+    for rep in range(6):
+        dist.barrier()
+        torch.cuda.synchronize()
+        for name, fn in phases:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            if rep:
+                times[name].append(a.elapsed_time(b) * 1e3)
+    med = torch.tensor([statistics.median(times[name]) for name, _ in phases], device=dev, dtype=torch.float64)
+    dist.all_reduce(med, op=dist.ReduceOp.MAX)
+    out = {name: round(float(v), 1) for (name, _), v in zip(phases, med)}
+    if ex is not None:
+        # bytes this rank writes into other ranks' buffers per layer: rows to owners of the token's experts + routes
+        sent = int((ex.present >= 0).sum().item()) - int((ex.present[:, ep.rank] >= 0).sum().item())
+        out["push_bytes"] = sent * shape.hidden * 2 + (world - 1) * x_dev.shape[0] * shape.top_k * 8
+        out["push_gbs"] = round(out["push_bytes"] / (out["push"] * 1e-6) / 1e9, 1) if out["push"] else None
+        out["nvlink_peak_gbs_per_direction"] = 900
+    return out
 
 
 def kernel_case(args) -> None:

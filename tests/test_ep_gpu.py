@@ -95,3 +95,124 @@ def test_overflow_sets_the_flag_and_drops_only_the_extra_routes(one_rank_group):
     changed = (y != want).any(dim=1).sum().item()
     assert 0 < changed <= 40
     assert torch.isfinite(y.float()).all()
+
+
+# ---- exchange over peer memory ------------------------------------------------------------------------------
+
+def _rank_layers(ranks, placement, experts=8):
+    """The full layer and every rank's slice of it (the same expert bytes)."""
+    src = expert_source(SEED, 7, "olmoe", "q4_group128")
+    full = stage_layer({e: src(e) for e in range(experts)}, experts, 2048, 1024, "q4_group128", DEV)
+    per = experts // ranks
+    owned = [list(range(r, experts, ranks)) if placement == "interleaved" else list(range(r * per, (r + 1) * per))
+             for r in range(ranks)]
+    slices = [stage_layer({i: src(e) for i, e in enumerate(own)}, per, 2048, 1024, "q4_group128", DEV) for own in owned]
+    return full, slices
+
+
+@pytest.mark.parametrize("ranks,placement", [(2, "interleaved"), (4, "interleaved"), (4, "contiguous")])
+def test_peer_exchange_with_every_rank_on_one_gpu(ranks, placement):
+    """The push / compute / combine kernels of the peer-memory exchange, with all ranks' buffers on one device and
+    the phases run rank after rank (no barrier kernel: the loop order is the barrier).  Buffers start as NaN
+    patterns, so a row that was not pushed, or a partial sum that was not written, would poison the result."""
+    from uma_qmoe_b200 import ops
+    from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE, PeerExchange
+    top_k, t = 4, 50
+    full, slices = _rank_layers(ranks, placement)
+    gen = torch.Generator().manual_seed(SEED + 93)
+    pop = 1.0 / torch.arange(1, 9, dtype=torch.float64)
+    idx = torch.multinomial(pop.expand(ranks * t, 8), top_k, replacement=False, generator=gen).to(DEV)
+    w = (torch.rand((ranks * t, top_k), generator=gen, dtype=torch.float32) / top_k).to(DEV)
+    x = syn.activations(SEED + 94, ranks * t).to(DEV)
+    want = _plain(full, x, idx, w)
+    nbytes = PeerExchange.nbytes_for(t, 2048, top_k, ranks)
+    buffers = [torch.full((nbytes,), 0xFF, dtype=torch.uint8, device=DEV) for _ in range(ranks)]
+    eps, exs = [], []
+    for r in range(ranks):
+        eps.append(ExpertParallelMoE(CudaKernels(slices[r], top_k), 8, top_k, placement=placement, world=ranks, rank=r))
+        exs.append(PeerExchange(t, 2048, top_k, r, ranks, torch.device(DEV), buffers=buffers))
+    rows = lambda r: slice(r * t, (r + 1) * t)
+    for r in range(ranks):
+        eps[r].peer_push(exs[r], x[rows(r)].contiguous(), idx[rows(r)].contiguous(), w[rows(r)].contiguous())
+    for r in range(ranks):
+        eps[r].peer_compute(exs[r])
+    got = torch.cat([eps[r].peer_combine(exs[r]) for r in range(ranks)])
+    torch.cuda.synchronize()
+    assert torch.isfinite(got.float()).all()
+    # a BF16 sum over ranks of BF16 ordered sums: inside the operator's tolerance of the one-GPU result, not bit-equal
+    from oracle import moe_oracle as orc
+    m = orc.compare(got.cpu(), want.cpu())
+    assert m["max_abs"] <= 2e-2 and m["cosine"] >= 0.9999, m
+    # the table of who holds part of a token: rank p is present iff it owns one of the token's experts
+    owner = (idx % ranks) if placement == "interleaved" else (idx // (8 // ranks))
+    for r in range(ranks):
+        expect = torch.stack([(owner[rows(r)] == p).any(dim=1) for p in range(ranks)], dim=1)
+        assert torch.equal(exs[r].present >= 0, expect)
+
+
+def _peer_worker(rank, world, port, results):
+    import traceback
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from oracle import moe_oracle as orc
+        from uma_qmoe_b200 import ops
+        from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE, PeerExchange
+        from uma_qmoe_b200.stack import random_layer
+        shape, t = syn.OLMOE, 256
+        mine = range(rank, shape.experts, world)
+        layer = random_layer(shape, "q4_group128", SEED, dev, mine)
+        full = random_layer(shape, "q4_group128", SEED, dev)
+        x_all = syn.activations(SEED + 95, world * t).to(dev)
+        wr = syn.router_weight(SEED, 0, shape, skew=1.0).to(dev)
+        w_all, idx_all = ops.route_topk(x_all, wr, shape.top_k, True)
+        mine_rows = slice(rank * t, (rank + 1) * t)
+        x, w, idx = x_all[mine_rows].contiguous(), w_all[mine_rows].contiguous(), idx_all[mine_rows].contiguous()
+        ws = ops.prefill_workspace(full, t, shape.top_k, None, dev)
+        want = ops.moe_prefill(full, x, idx, w, ws)
+        ep = ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k)
+        out = {"exact_equal": bool(torch.equal(ep.forward(x, idx, w), want))}
+        out["gather"] = orc.compare(ep.forward_gather(x, idx, w).cpu(), want.cpu())
+        try:
+            ex = PeerExchange(t, shape.hidden, shape.top_k, rank, world, dev)
+            dist.barrier()
+            for _ in range(2):                               # twice: the second call reuses every buffer
+                got = ep.forward_peer(ex, x, idx, w)
+            torch.cuda.synchronize()
+            out["peer"] = orc.compare(got.cpu(), want.cpu())
+            out["peer_timed_out"] = ex.timed_out()
+        except Exception as exc:                              # no peer mapping on this machine: say so, NCCL paths stand
+            out["peer_unavailable"] = f"{type(exc).__name__}: {exc}"[:200]
+        results[rank] = out
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        results[rank] = {"error": traceback.format_exc()[-1500:]}
+
+
+def test_two_gpu_exchanges_match_the_one_gpu_result():
+    """Two real ranks: the exact-count exchange is bit-identical to the one-GPU operator, the gather exchange and the
+    peer-memory exchange stay inside the operator's tolerance of it.  Needs two GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    procs = [ctx.Process(target=_peer_worker, args=(r, 2, port, results)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=600)
+    for r in range(2):
+        out = results.get(r)
+        assert out is not None and "error" not in out, out
+        assert out["exact_equal"], out
+        assert out["gather"]["max_abs"] <= 2e-2 and out["gather"]["cosine"] >= 0.9999, out
+        if "peer" in out:
+            assert not out["peer_timed_out"], out
+            assert out["peer"]["max_abs"] <= 2e-2 and out["peer"]["cosine"] >= 0.9999, out

@@ -166,7 +166,9 @@ class ExchangePlan:
 
 class ExpertParallelMoE:
     def __init__(self, kernels: Any, num_experts: int, top_k: int, group: Optional[dist.ProcessGroup] = None,
-                 placement: str = "interleaved") -> None:
+                 placement: str = "interleaved", world: Optional[int] = None, rank: Optional[int] = None) -> None:
+        """``world`` / ``rank`` default to the process group's; given explicitly they let one process stand for
+        several ranks (only the peer-memory exchange, which needs no collective, can be driven that way)."""
         if placement not in ("interleaved", "contiguous"):
             raise RuntimeError(f"unknown expert placement {placement!r}")
         self.placement = placement
@@ -176,8 +178,8 @@ class ExpertParallelMoE:
         self._overflow: Optional[torch.Tensor] = None
         self.kernels = kernels
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group) if world is None else world
+        self.rank = dist.get_rank(group) if rank is None else rank
         if num_experts % self.world:
             raise RuntimeError(f"{num_experts} experts do not divide over {self.world} ranks")
         self.num_experts = num_experts

@@ -8,7 +8,7 @@ under a second; nothing here reads a checkpoint.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -17,9 +17,28 @@ from .ops import DeviceLayer, DeviceSharedExpert
 from .synthetic import ModelShape, router_weight
 
 
+def balanced_order(router: torch.Tensor, ranks: int) -> list[int]:
+    """A relabelling of the experts for expert parallelism: position n of the result is the expert that gets the
+    new id n, chosen so that the interleaved placement (new id n on rank n % ranks) spreads the expected load
+    evenly.  The load estimate is static and needs no data: an expert's logit scales with the norm of its router
+    row, so rows are ranked by norm and dealt to the ranks in serpentine order.  Relabelling changes nothing about
+    the model (the router rows move with the experts)."""
+    norms = router.float().norm(dim=1)
+    by_load = torch.argsort(norms, descending=True).tolist()
+    per_rank: list[list[int]] = [[] for _ in range(ranks)]
+    for i, e in enumerate(by_load):
+        lap, pos = divmod(i, ranks)
+        per_rank[pos if lap % 2 == 0 else ranks - 1 - pos].append(e)
+    order = [0] * len(by_load)
+    for r, mine in enumerate(per_rank):
+        for j, e in enumerate(mine):
+            order[j * ranks + r] = e
+    return order
+
+
 def random_layer(shape: ModelShape, encoding: str, seed: int, device: torch.device,
-                 experts: Optional[range] = None) -> DeviceLayer:
-    """One layer of `shape` with experts `experts` (default: all) in `encoding`."""
+                 experts: Optional[Sequence[int]] = None) -> DeviceLayer:
+    """One layer of `shape` with experts `experts` (default: all, in id order) in `encoding`."""
     experts = range(shape.experts) if experts is None else experts
     gen = torch.Generator(device=device)
     n = len(experts)
@@ -62,13 +81,26 @@ class MoEStack:
     layers: list[DeviceLayer]
     routers: list[torch.Tensor]
     renormalize: bool
+    orders: Optional[list] = None      # per layer: original expert id behind every (new) id
 
     @classmethod
     def build(cls, shape: ModelShape, encoding: str, num_layers: int, seed: int, device: torch.device,
-              renormalize: bool, skew: float = 1.0, experts: Optional[range] = None) -> "MoEStack":
-        layers = [random_layer(shape, encoding, seed + l, device, experts) for l in range(num_layers)]
-        routers = [router_weight(seed, l, shape, skew=skew).to(device) for l in range(num_layers)]
-        return cls(shape, layers, routers, renormalize)
+              renormalize: bool, skew: float = 1.0, experts: Optional[Sequence[int]] = None,
+              balance_ranks: int = 0) -> "MoEStack":
+        """``experts``: the (new) expert ids this rank holds, default all.  ``balance_ranks`` > 1 relabels the
+        experts of every layer with :func:`balanced_order` first; ``orders[l][n]`` is then the original expert
+        behind new id n (the weights of an expert depend only on its original id and the seeds)."""
+        routers, layers, orders = [], [], []
+        for l in range(num_layers):
+            wr = router_weight(seed, l, shape, skew=skew)
+            order = balanced_order(wr, balance_ranks) if balance_ranks > 1 else list(range(shape.experts))
+            held = order if experts is None else [order[n] for n in experts]
+            routers.append(wr[order].contiguous().to(device))
+            layers.append(random_layer(shape, encoding, seed + l, device, held))
+            orders.append(order)
+        stack = cls(shape, layers, routers, renormalize)
+        stack.orders = orders
+        return stack
 
     def route(self, layer: int, x: torch.Tensor):
         return ops.route_topk(x, self.routers[layer], self.shape.top_k, self.renormalize)
