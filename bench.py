@@ -456,6 +456,7 @@ def ep_phases(stack, eps, ex, x_dev, shape, dev, world) -> dict:
         torch.cuda.synchronize()
         for name, fn in phases:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(400_000)          # ~0.2 ms of device idle time, so the host's launch calls are not in the figure
             a.record(); fn(); b.record()
             torch.cuda.synchronize()
             if rep:
@@ -481,6 +482,8 @@ def kernel_case(args) -> None:
     torch.cuda.set_device(dev)
     if args.only == "model":
         return model_case(args, dev)
+    if args.only == "phases":
+        return prefill_phases_case(args, dev)
     qwen = args.only == "decode" and args.model == "qwen"
     shape = syn.QWEN if qwen else syn.OLMOE
     stack = MoEStack.build(shape, "q8_group128" if qwen else "q4_group128", args.layers, SEED, dev,
@@ -524,6 +527,38 @@ def kernel_case(args) -> None:
         print(json.dumps({"case": "gemm", "tokens": args.tokens, "variant": args.variant, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
                           "tflops": flops / (ms / 1e3) / 1e12, "tflops_gate_up": flops * 2 / 3 / (ms1 / 1e3) / 1e12,
                           "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
+
+
+def prefill_phases_case(args, dev) -> None:
+    """Device time of every kernel of one prefill layer (OLMoE Q4, layer 0, --tokens tokens), each replayed from a
+    CUDA graph of 8 back-to-back launches so that no launch gap is inside the figure."""
+    from uma_qmoe_b200 import ops, synthetic as syn
+    from uma_qmoe_b200.stack import MoEStack, rms_renorm
+    shape = syn.OLMOE
+    stack = MoEStack.build(shape, "q4_group128", 1, SEED, dev, renormalize=True, skew=1.0)
+    layer = stack.layers[0]
+    x = syn.activations(SEED, args.tokens).to(dev)
+    w, idx = stack.route(0, x)
+    routes = ops.route_sort(idx, w, shape.experts)
+    xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)
+    inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
+    yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
+    ws = ops.prefill_workspace(layer, args.tokens, shape.top_k, None, dev)
+    phases = [("router", lambda: stack.route(0, x)),
+              ("route_sort", lambda: ops.route_sort(idx, w, shape.experts)),
+              ("gather_rows", lambda: ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)),
+              ("gemm_gate_up", lambda: ops.grouped_gemm(layer, 0, xs, routes, permute_out=True, out=inter)),
+              ("gemm_down", lambda: ops.grouped_gemm(layer, 1, inter, routes, route_weight=routes.sorted_weight, out=yw)),
+              ("combine", lambda: ops.combine_routes(yw, idx, routes.route_pos)),
+              ("rms_norm", lambda: rms_renorm(x)),
+              ("whole_operator", lambda: ops.moe_prefill(layer, x, idx, w, ws))]
+    out = {}
+    for name, fn in phases:
+        def eight(fn=fn):
+            for _ in range(8):
+                fn()
+        out[name] = round(timed(graphed(eight), args.steps, args.warmup, 1) / 8 * 1e3, 2)
+    print(json.dumps({"case": "phases", "tokens": args.tokens, "us": out}))
 
 
 def model_case(args, dev) -> None:
@@ -576,7 +611,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
     ap.add_argument("--cpu-tokens", type=int, default=TOKENS, help="tokens of the CPU arm's layer-0 call")
     ap.add_argument("--cpu-budget", type=float, default=240.0, help="seconds the CPU arm may spend on timed calls")
-    ap.add_argument("--only", choices=("all", "decode", "gemm", "model"), default="all",
+    ap.add_argument("--only", choices=("all", "decode", "gemm", "model", "phases"), default="all",
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")

@@ -62,10 +62,14 @@ namespace {
 // Registers are split over the SM's four schedulers, 16384 each: 4 x 2048 + 2 x 3072 fits, one warp more of
 // either kernel on a scheduler does not, and then the two kernels cannot share the SM.  So there is no extra
 // producer warp: when a CTA's whole share fits its shared memory (OLMoE) all warps issue the copies up front
-// and all of them compute; otherwise the last warp produces and the others compute.
+// and all of them compute; otherwise the last warps produce (issuing a bulk copy costs its warp about 100 ns
+// and a ring stage of row pieces takes up to 18 of them, so the stages go round several producer warps) and
+// the others compute.
 constexpr int kNW = 8;                        // down kernel
 constexpr int kThreadsD = kNW * 32;
 constexpr int kGW = 16;                       // gate/up kernel
+constexpr int kGProducers = 4;                // warps that feed the ring when a CTA's share does not fit it at once
+constexpr int kDProducers = 2;
 constexpr int kThreadsG = kGW * 32;
 constexpr int kMaxSlots = 8;
 // The two kernels share an SM: their dynamic shared memory together stays under kPairSmemBudget (228 KB per SM
@@ -589,10 +593,10 @@ __global__ void __maxnreg__(64) decode_gateup_kernel(const DecodeParams p) {
   const int U0 = P.kind[0].units, upr = p.inter >> 3;
   const int ub = first_unit(P, blockIdx.x), ue = first_unit(P, blockIdx.x + 1);
   // all_at_once: the CTA's whole share fits the ring, every warp issues copies and computes; otherwise the
-  // last warp produces and the other 15 compute
+  // last kGProducers warps produce and the others compute
   const bool whole_rows = P.kind[0].nch == 1 && (P.kind[1].units == 0 || P.kind[1].nch == 1);
   const bool all_at_once = whole_rows && ue - ub <= P.stages;
-  const int ncons = all_at_once ? kGW : kGW - 1;
+  const int ncons = all_at_once ? kGW : kGW - kGProducers;
   const bool consumer = warp < ncons;
   // resident Q4 fast path: every unit of this CTA is a routed one, a stage has one item per warp
   const bool fast = all_at_once && P.kind[0].enc == ENC_Q4 && P.kind[0].ips == kGW && ue <= U0 && ue - ub <= 8;
@@ -675,7 +679,9 @@ __global__ void __maxnreg__(64) decode_gateup_kernel(const DecodeParams p) {
     // ---- producer (when the CTA's share does not fit the ring at once): one stage = 8 gate rows, 8 up rows
     //      (one bulk copy each when the stage takes whole rows) and their scales ----------------------------
     if (!all_at_once) {
-    int slot = 0, round = 0;
+    // Issuing a bulk copy costs a warp about 100 ns, so the stages go round the producer warps.
+    const int pj = warp - ncons;
+    int n = 0;                                 // running stage number: slot n % stages, round n / stages
     for (int u = ub; u < ue && !*fail; ++u) {
       const int k = u < U0 ? 0 : 1;
       const DecodeKind& K = P.kind[k];
@@ -692,7 +698,9 @@ __global__ void __maxnreg__(64) decode_gateup_kernel(const DecodeParams p) {
         usrc = reinterpret_cast<const uint8_t*>(p.sh_up) + row * K.row_bytes;
       }
       const uint32_t scale_bytes = 8u * K.groups * 4;              // per projection
-      for (int ch = 0; ch < K.nch; ++ch) {
+      for (int ch = 0; ch < K.nch; ++ch, ++n) {
+        if (n % kGProducers != pj) continue;
+        const int slot = n % P.stages, round = n / P.stages;
         if (round > 0 && !wait_or_fail(empty + slot, (round - 1) & 1, fail)) break;
         uint8_t* st = smem + (size_t)slot * P.stage_bytes;
         if (lane == 0) mbar_expect_tx(full + slot, ((p.debug & 2) ? 0u : 16u * K.ch) + 2 * scale_bytes);
@@ -707,7 +715,6 @@ __global__ void __maxnreg__(64) decode_gateup_kernel(const DecodeParams p) {
         }
         if (K.groups && lane >= 16 && lane < 18)
           bulk_g2s(st + P.scale_off + (lane - 16) * scale_bytes, lane == 16 ? gs : us, scale_bytes, full + slot);
-        if (++slot == P.stages) { slot = 0; ++round; }
       }
     }
     }
@@ -951,9 +958,9 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + P.bar_off);
   uint64_t* empty = full + P.stages;
   const uint32_t full_count = P.bulk_scales ? 1 : 1 + 32;
-  // with the whole share issued up front by all warps every warp computes; otherwise the last one produces
+  // with the whole share issued up front by all warps every warp computes; otherwise the last kDProducers produce
   const bool all_at_once = P.resident && P.bulk_scales;
-  const int ncons = all_at_once ? kNW : kNW - 1;
+  const int ncons = all_at_once ? kNW : kNW - kDProducers;
   const bool consumer = warp < ncons;
   // resident fast path: quantised rows, one item per warp
   const bool fast = all_at_once && P.kind[0].groups && P.kind[0].ips == kNW && !P.kind[1].nvs && P.max_units <= 8;
@@ -1028,9 +1035,10 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
       while (global_ns() - t0 < (uint64_t)p.down_delay_ns) __nanosleep(200);
     }
     const DecodeKind& K0 = P.kind[0];
+    const int pj = warp - ncons;
     if (P.resident) {
       // (with 16-byte scale rows the copies were issued above by all warps)
-      if (!P.bulk_scales) {
+      if (!P.bulk_scales && pj == 0) {
         const uint32_t wbytes = (uint32_t)npairs * 2 * K0.row_bytes;
         if (lane == 0) mbar_expect_tx(full, (p.debug & 2) ? 0u : K0.nvs * wbytes);
         __syncwarp();
@@ -1045,11 +1053,13 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
         cp_async_arrive(full);
       }
     } else {
-      int slot = 0, round = 0;
+      int n = 0;                               // running stage number; the stages go round the producer warps
       for (int k = 0; k < kinds && !*fail; ++k) {
         const DecodeKind& K = P.kind[k];
         const uint32_t sbytes = 2u * K.groups * 4;
-        for (int rp = rp0; rp < rp1; ++rp) {
+        for (int rp = rp0; rp < rp1; ++rp, ++n) {
+          if (n % kDProducers != pj) continue;
+          const int slot = n % P.stages, round = n / P.stages;
           if (round > 0 && !wait_or_fail(empty + slot, (round - 1) & 1, fail)) break;
           uint8_t* st = smem + (size_t)slot * P.stage_bytes;
           if (lane == 0)
@@ -1077,7 +1087,6 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
                      (uint32_t)K.row_bytes, full + slot);
           }
           if (!P.bulk_scales) cp_async_arrive(full + slot);
-          if (++slot == P.stages) { slot = 0; ++round; }
         }
       }
     }

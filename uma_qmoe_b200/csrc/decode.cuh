@@ -85,14 +85,16 @@ struct DecodeParams {
   int shared_inter;
   __nv_bfloat16* out;         // [hidden]
   // workspace
-  unsigned* sync;             // header words; sync[2] is the status word, sync[4] counts finished gate/up CTAs,
-                              // sync[5] finished down CTAs (both return to zero at the end of a call)
+  unsigned* sync;             // header words; sync[2] is the status word, sync[4] counts the gate/up CTAs that have
+                              // finished, over all calls, and sync[6] is the count the current call's down kernel
+                              // waits for (every call adds its grid size; the words are never reset)
   uint8_t* inter_buf;         // intermediate fragments (after the header)
   // launch plans, filled by launch_moe_decode
   DecodeKernelPlan g;         // gate/up + SwiGLU kernel
   DecodeKernelPlan d;         // down + combine kernel
   int down_delay_ns;          // the down kernel's producer waits this long before its first copy
-  int debug;                  // measurement switches: 1 = consumers skip the arithmetic, 2 = producers skip the weight copies
+  int debug;                  // measurement switches: 1 = consumers skip the arithmetic, 2 = producers skip the weight
+                              // copies, 4 = CTA 0 writes %globaltimer stamps into the header (bytes 128 and up)
 };
 
 size_t decode_workspace_bytes(int top_k, int inter, int shared_inter);

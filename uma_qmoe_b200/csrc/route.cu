@@ -139,6 +139,57 @@ __device__ __forceinline__ void softmax_topk_warp(float* probs, int E, int top_k
   }
 }
 
+// The same softmax / top-k for E <= 64 and top_k <= 8 with eight lanes per token, so that a warp handles four
+// tokens at once: lane s of a token's group keeps experts s, s + 8, ... in registers.  Ties go to the lower expert.
+__device__ __forceinline__ void softmax_topk_oct(const float* logits, bool live, int E, int top_k, int renormalize, int lane,
+                                                 float* out_w, long long* out_i) {
+  const int s = lane & 7;
+  float v[8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = s + 8 * j;
+    v[j] = (live && e < E) ? logits[e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+#pragma unroll
+  for (int o = 4; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[j] = (s + 8 * j < E) ? expf(v[j] - mx) : 0.f;
+    sum += v[j];
+  }
+#pragma unroll
+  for (int o = 4; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = (s + 8 * j < E) ? v[j] / sum : -2.f;
+  float topsum = 0.f, myval = 0.f;
+  int myidx = 0;
+  for (int it = 0; it < top_k; ++it) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (v[j] > best) { best = v[j]; bi = s + 8 * j; }
+#pragma unroll
+    for (int o = 4; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (s == it) { myval = best; myidx = bi; }
+    topsum += best;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (bi == s + 8 * j) v[j] = -2.f;
+  }
+  if (live && s < top_k) {
+    out_w[s] = renormalize ? myval / topsum : myval;
+    out_i[s] = myidx;
+  }
+}
+
 // Tiled router for E <= 64: a CTA takes 32 tokens and all experts, stages 128-wide k chunks of x and
 // Wr in shared memory (rows padded by 16 bytes against bank conflicts); thread (ty, tx) accumulates
 // tokens {ty, ty+16} x experts {tx, tx+16, tx+32, tx+48}.  The BF16 products are exact in float32;
@@ -227,13 +278,13 @@ __global__ void __launch_bounds__(256) router_tiled_kernel(const RouterArgs a) {
 }
 
 // Tensor-core router for batches (E <= 64, tokens >= 128): a CTA takes 64 tokens and all experts.
-// x and Wr stream through a 3-stage cp.async ring of 128-wide k chunks (16-byte chunks XOR-swizzled by
+// x and Wr stream through a 6-stage cp.async ring of 128-wide k chunks (16-byte chunks XOR-swizzled by
 // row against bank conflicts); warp (g, h) = (token group of 16, expert half of 32) runs
 // mma.sync.m16n8k16 BF16 with ldmatrix fragments.  The BF16 products are exact in the FP32 accumulator;
 // a chunk's 128 products are summed by the tensor core in float32, the chunk sums in float64, so the
 // BF16 rounding of the logit equals that of an exactly rounded dot product in all but about one logit
 // in 10^4 (the same bound as the tiled kernel).  The logits then go through the same softmax / top-k.
-constexpr int kRmTokens = 64, kRmChunk = 128, kRmStages = 3;
+constexpr int kRmTokens = 64, kRmChunk = 128, kRmStages = 6;
 constexpr int kRmTile = 64 * kRmChunk * 2;                 // 16 KiB: 64 rows x 256 bytes
 constexpr int kRmSmem = kRmStages * 2 * kRmTile;
 
@@ -321,6 +372,15 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
       if (a.out_logits && t < a.tokens && e < E) a.out_logits[(size_t)t * E + e] = __float2bfloat16_rn(l);
     }
   __syncthreads();
+  if (a.top_k <= 8) {
+    for (int r = warp * 4 + (lane >> 3); r < kRmTokens; r += 32) {     // the loop count is the same for every lane
+      const int t = token0 + r;
+      const bool live = t < a.tokens;
+      softmax_topk_oct(logit[r], live, E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)(live ? t : 0) * a.top_k,
+                       a.out_indices + (size_t)(live ? t : 0) * a.top_k);
+    }
+    return;
+  }
   for (int r = warp; r < kRmTokens; r += 8) {
     const int t = token0 + r;
     if (t < a.tokens)
