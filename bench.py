@@ -38,13 +38,25 @@ sys.path.insert(0, str(ROOT))
 SEED = 20260917
 TOKENS, LAYERS = 8192, 16
 DECODE_BYTES = 8 * 3_342_336 + 8_192          # selected experts' codes + scales, x in, y out
-# DRAM bytes per launch from ncu (dram__bytes_read.sum + dram__bytes_write.sum), see profiles/:
-# decode pair 17.88 MB + 9.01 MB measured directly; gate/up GEMM measured at 2048 tokens (196.5 MB read of
-# which 138 MB are the layer's gate/up codes and scales, the rest the gathered activations) and scaled by
-# routes to 8192 tokens: 138 MB weights + 268 MB activations + 134 MB intermediate written.
-DECODE_TRAFFIC_BYTES = 26_886_000
-GEMM_TRAFFIC_BYTES = 540_000_000
+QWEN_DECODE_BYTES = 4 * 8_921_088 + 69_206_016 + 4_096 + 8_192     # 4 Q8 experts, the BF16 shared expert + gate, x, y
 METRIC, UNIT = "prefill_tokens_per_s", "tokens/s"
+
+# One ncu capture per kernel (dram__bytes_read.sum, dram__bytes_write.sum per launch).  The decode pair was captured
+# on the benchmark's own layer; the grouped GEMMs on 2048 tokens of it (a full-size capture would hold more than a
+# gigabyte through ~40 replay passes), so their traffic is scaled to the benchmark's token count below: the weights
+# of all 64 experts are read once whatever the token count, everything else grows with the routes.
+CAPTURES = {
+    "decode_pair": {"read": 17.86e6 + 9.01e6, "write": 0.0},
+    "gemm_gate_up": {"tokens": 2048, "read": 196.6e6, "write": 22.3e6, "weights": 64 * 2 * (1024 * 1024 + 1024 * 16 * 4)},
+    "gemm_down": {"tokens": 2048, "read": 98.4e6, "write": 28.5e6, "weights": 64 * (2048 * 512 + 2048 * 8 * 4)},
+}
+
+
+def gemm_traffic(name: str, tokens: int) -> int:
+    """DRAM bytes of one grouped-GEMM launch on `tokens` tokens, from the capture of that kernel."""
+    c = CAPTURES[name]
+    grow = tokens / c["tokens"]
+    return int(c["weights"] + (c["read"] - c["weights"]) * grow + c["write"] * grow)
 
 
 def peaks() -> tuple[dict, str]:
@@ -337,6 +349,12 @@ def native_arm(args) -> None:
         out_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
+    # The batch-1 decode legs come first: a call is a few microseconds, and right after the long tensor-bound legs
+    # the same kernels measured 10 % slower.
+    decode_objects, decode_launches = {}, 0
+    if rank == 0 and world == 1:
+        decode_objects, decode_launches = decode_legs(stack, x_dev, shape, dev)
+
     with ClockSampler(local) as clocks:
         ms = timed(step_resident, args.steps, args.warmup, world)
         ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2), world)
@@ -354,46 +372,40 @@ def native_arm(args) -> None:
             "tflops_step": 65536 * 12_582_912 * LAYERS / (ms / 1e3) / 1e12 / world}
 
     if rank == 0 and world == 1:
-        # ---- roofline of the dominant kernel: the gate/up grouped GEMM of layer 0 ------------------
+        # ---- roofline of the dominant kernel (the gate/up grouped GEMM of layer 0) and of the down GEMM ----
         w, idx = stack.route(0, x_dev)
         routes = ops.route_sort(idx, w, shape.experts)
         xs = ops.gather_rows(x_dev, routes.sorted_route, shape.top_k, permute=True)
         inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
+        yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-        times = []
-        for i in range(3 + 10):
-            flush.zero_()                                            # weights leave L2 between launches
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter)
-            b.record()
-            torch.cuda.synchronize()
-            if i >= 3:
-                times.append(a.elapsed_time(b))
-        gemm_ms = statistics.mean(times)
-        flops = 2.0 * xs.shape[0] * shape.hidden * 2 * shape.intermediate
-        line["roofline"] = {"bound": "tensor", "kernel": "grouped_gemm_kernel<Q4, gate/up+SwiGLU>",
-                            "achieved": flops / (gemm_ms / 1e3) / 1e12, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                            "frac": flops / (gemm_ms / 1e3) / 1e12 / pk["bf16_tflops"], "traffic": GEMM_TRAFFIC_BYTES,
-                            "peak_source": f"{pk_kind} (burst)", "ms_per_launch": gemm_ms,
-                            "flops_per_launch": flops}
-        # ---- batch-1 decode: the fused kernel over the 16 layers in rotation (428 MB > L2) -----------
-        xd = x_dev[:1].contiguous()
-        routes1 = [stack.route(l, xd) for l in range(LAYERS)]
-        wsd = ops.decode_workspace(stack.layers[0], shape.top_k, None, dev)
-        outd = torch.empty_like(xd)
 
-        def decode_pass():
-            for l in range(LAYERS):
-                ops.moe_decode(stack.layers[l], xd, routes1[l][1], routes1[l][0], wsd, out=outd)
-        dms = timed(graphed(decode_pass), 20, 3, 1) / LAYERS
-        line["decode"] = {"metric": "decode_hbm_gbs", "us_per_layer": dms * 1e3,
-                          "roofline": {"bound": "hbm", "kernel": "decode_gateup_kernel + decode_down_kernel", "achieved": DECODE_BYTES / (dms / 1e3) / 1e9,
-                                       "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                       "frac": DECODE_BYTES / (dms / 1e3) / 1e9 / pk["hbm_gbs"], "traffic": DECODE_TRAFFIC_BYTES,
-                                       "peak_source": pk_kind, "bytes_per_launch": DECODE_BYTES},
-                          "status": ops.workspace_status(wsd)}
-        line["gpu_launches"] += 13 + 2 * (20 + 3) * LAYERS      # roofline leg + two decode kernels per layer and pass
+        def cold(fn):
+            times = []
+            for i in range(3 + 10):
+                flush.zero_()                                        # weights leave L2 between launches
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); fn(); b.record()
+                torch.cuda.synchronize()
+                if i >= 3:
+                    times.append(a.elapsed_time(b))
+            return statistics.mean(times)
+        gemm_ms = cold(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter))
+        down_ms = cold(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw))
+        flops = 2.0 * xs.shape[0] * shape.hidden * 2 * shape.intermediate
+
+        def tensor_roofline(kernel, fl, ms_, capture):
+            return {"bound": "tensor", "kernel": kernel, "achieved": fl / (ms_ / 1e3) / 1e12, "peak": pk["bf16_tflops"],
+                    "unit": "TFLOP/s", "frac": fl / (ms_ / 1e3) / 1e12 / pk["bf16_tflops"],
+                    "traffic": gemm_traffic(capture, TOKENS), "traffic_source": f"ncu capture at {CAPTURES[capture]['tokens']} tokens, "
+                    "scaled by routes (weights fixed)", "peak_source": f"{pk_kind} (burst)", "ms_per_launch": ms_,
+                    "flops_per_launch": fl}
+        line["roofline"] = tensor_roofline("grouped_gemm_kernel<Q4, gate/up+SwiGLU>", flops, gemm_ms, "gemm_gate_up")
+        line["roofline_down"] = tensor_roofline("grouped_gemm_kernel<Q4, down x route weight>", flops / 2, down_ms, "gemm_down")
+        line["kernels_us"] = prefill_kernel_times(stack, x_dev, shape, dev)
+        del xs, inter, yw, flush
+        line.update(decode_objects)
+        line["gpu_launches"] += 26 + decode_launches              # the roofline legs and the decode legs
         line["cpu_baseline"] = cpu_baseline_subprocess()
     if world > 1:
         line["ep_check"] = ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world)
@@ -407,11 +419,110 @@ def native_arm(args) -> None:
         torch.distributed.destroy_process_group()
 
 
+def decode_legs(stack, x_dev, shape, dev) -> tuple[dict, int]:
+    """The batch-1 decode kernels on the stack's own layers (OLMoE Q4, 16 layers in rotation = 428 MB > L2) and on a
+    Qwen1.5-MoE-shaped layer, each replayed from a CUDA graph; beside each the time of a launch that only reads the
+    same number of bytes (16-byte loads from many CTAs), i.e. what the part does for a call of that size."""
+    from uma_qmoe_b200 import ops
+    pk, pk_kind = peaks()
+
+    def hbm_roofline(nbytes, ms_, traffic):
+        return {"bound": "hbm", "kernel": "decode_gateup_kernel + decode_down_kernel",
+                "achieved": nbytes / (ms_ / 1e3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": nbytes / (ms_ / 1e3) / 1e9 / pk["hbm_gbs"], "traffic": traffic, "peak_source": pk_kind,
+                "bytes_per_launch": nbytes}
+    steps, warmup = 40, 10
+    xd = x_dev[:1].contiguous()
+    routes1 = [stack.route(l, xd) for l in range(LAYERS)]
+    wsd = ops.decode_workspace(stack.layers[0], shape.top_k, None, dev)
+    outd = torch.empty_like(xd)
+
+    def decode_pass():
+        for l in range(LAYERS):
+            ops.moe_decode(stack.layers[l], xd, routes1[l][1], routes1[l][0], wsd, out=outd)
+    dms = timed(graphed(decode_pass), steps, warmup, 1) / LAYERS
+    cap = CAPTURES["decode_pair"]
+    out = {"decode": {"metric": "decode_hbm_gbs", "workload": "one OLMoE layer call at batch 1: 8 of 64 experts, packed Q4 group-128",
+                      "us_per_layer": dms * 1e3, "roofline": hbm_roofline(DECODE_BYTES, dms, int(cap["read"] + cap["write"])),
+                      "stream_only_us": stream_floor_us(DECODE_BYTES, LAYERS, dev, steps, warmup),
+                      "status": ops.workspace_status(wsd)}}
+    out["decode_qwen"] = qwen_decode_leg(dev, hbm_roofline, steps, warmup)
+    launches = (2 + 1) * (steps + warmup + 2) * LAYERS + out["decode_qwen"].pop("launches")
+    return out, launches
+
+
+def stream_floor_us(nbytes: int, buffers: int, dev, steps: int, warmup: int) -> float:
+    from uma_qmoe_b200 import ops
+    nbytes = nbytes // 16 * 16
+    bufs = [torch.empty(nbytes, dtype=torch.uint8, device=dev).random_(0, 255) for _ in range(buffers)]
+
+    def run():
+        for b in bufs:
+            ops.probe_stream(b, 0)
+    return timed(graphed(run), steps, warmup, 1) / buffers * 1e3
+
+
+def qwen_decode_leg(dev, hbm_roofline, steps: int = 20, warmup: int = 3) -> dict:
+    """Batch-1 decode of a Qwen1.5-MoE-shaped layer: 4 of 60 Q8 group-128 experts (intermediate 1408), the BF16 shared
+    expert (intermediate 5632) and its sigmoid gate; 8 layers in rotation (840 MB > L2), replayed from a CUDA graph."""
+    from uma_qmoe_b200 import ops, synthetic as syn
+    from uma_qmoe_b200.stack import MoEStack, random_shared_expert
+    layers, shape = 8, syn.QWEN
+    stack = MoEStack.build(shape, "q8_group128", layers, SEED, dev, renormalize=False, skew=1.0)
+    shared = [random_shared_expert(shape, SEED + l, dev) for l in range(layers)]
+    x = syn.activations(SEED, 1).to(dev)
+    routes = [stack.route(l, x) for l in range(layers)]
+    ws = ops.decode_workspace(stack.layers[0], shape.top_k, shared[0], dev)
+    out = torch.empty_like(x)
+
+    def run():
+        for l in range(layers):
+            ops.moe_decode(stack.layers[l], x, routes[l][1], routes[l][0], ws, shared[l], out=out)
+    ms = timed(graphed(run), steps, warmup, 1) / layers
+    return {"metric": "decode_hbm_gbs", "workload": "one Qwen1.5-MoE layer call at batch 1: 4 of 60 experts Q8 group-128, "
+            "BF16 shared expert + gate", "us_per_layer": ms * 1e3, "roofline": hbm_roofline(QWEN_DECODE_BYTES, ms, None),
+            "stream_only_us": stream_floor_us(QWEN_DECODE_BYTES, layers, dev, steps, warmup),
+            "status": ops.workspace_status(ws), "launches": (2 + 1) * (steps + warmup + 2) * layers}
+
+
+def prefill_kernel_times(stack, x, shape, dev) -> dict:
+    """Device time (microseconds) of every kernel of one prefill layer on the tokens of `x` (layer 0), each replayed
+    from a CUDA graph of 8 back-to-back launches so that no launch gap is inside the figure."""
+    from uma_qmoe_b200 import ops
+    from uma_qmoe_b200.stack import rms_renorm
+    layer = stack.layers[0]
+    w, idx = stack.route(0, x)
+    routes = ops.route_sort(idx, w, shape.experts)
+    xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)
+    inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
+    yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
+    ws = ops.prefill_workspace(layer, x.shape[0], shape.top_k, None, dev)
+    phases = [("router", lambda: stack.route(0, x)),
+              ("route_sort", lambda: ops.route_sort(idx, w, shape.experts)),
+              ("gather_rows", lambda: ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)),
+              ("gemm_gate_up", lambda: ops.grouped_gemm(layer, 0, xs, routes, permute_out=True, out=inter)),
+              ("gemm_down", lambda: ops.grouped_gemm(layer, 1, inter, routes, route_weight=routes.sorted_weight, out=yw)),
+              ("combine", lambda: ops.combine_routes(yw, idx, routes.route_pos)),
+              ("rms_norm", lambda: rms_renorm(x)),
+              ("whole_operator", lambda: ops.moe_prefill(layer, x, idx, w, ws))]
+    out = {}
+    for name, fn in phases:
+        def eight(fn=fn):
+            for _ in range(8):
+                fn()
+        out[name] = round(timed(graphed(eight), 3, 1, 1) / 8 * 1e3, 2)
+    return out
+
+
+def compare(got: torch.Tensor, want: torch.Tensor) -> dict:
+    a, b = got.double().flatten(), want.double().flatten()
+    return {"max_abs": float((a - b).abs().max()), "cosine": float((a @ b) / (a.norm() * b.norm()).clamp_min(1e-300))}
+
+
 def ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world) -> dict:
     """Outside the timed region: layer 0 over this rank's tokens through the measured exchange and through the
     exact-count exchange, against the one-GPU operator on the same tokens with the full layer 0 (every rank builds
     it from the same seeds).  Worst case over the ranks."""
-    from oracle import moe_oracle as orc
     from uma_qmoe_b200 import ops
     from uma_qmoe_b200.stack import random_layer
     dist = torch.distributed
@@ -422,7 +533,7 @@ def ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world) -> dict:
     got = layer_forward(0, x_dev, w, idx)
     exact = eps[0].forward(x_dev, idx, w)
     torch.cuda.synchronize()
-    m = orc.compare(got.cpu(), want.cpu())
+    m = compare(got, want)
     stats = torch.tensor([m["max_abs"], -m["cosine"], 0.0 if torch.equal(exact, want) else 1.0], device=dev, dtype=torch.float64)
     dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     del full, ws
@@ -484,15 +595,17 @@ def kernel_case(args) -> None:
         return model_case(args, dev)
     if args.only == "phases":
         return prefill_phases_case(args, dev)
+    if args.only == "stream":
+        return stream_case(args, dev)
     qwen = args.only == "decode" and args.model == "qwen"
     shape = syn.QWEN if qwen else syn.OLMOE
     stack = MoEStack.build(shape, "q8_group128" if qwen else "q4_group128", args.layers, SEED, dev,
                            renormalize=not qwen, skew=1.0)
     if args.only == "decode":
-        # BASELINE config 0 (OLMoE layer, Q4) or config 2 (Qwen layer: Q8 routed experts, BF16 shared expert + gate)
+        # an OLMoE layer (Q4) or a Qwen1.5-MoE layer (Q8 routed experts, BF16 shared expert + gate)
         from uma_qmoe_b200.stack import random_shared_expert
         shared = [random_shared_expert(shape, SEED + l, dev) for l in range(args.layers)] if qwen else None
-        nbytes = (4 * 8_921_088 + 69_206_016 + 4_096 + 8_192) if qwen else DECODE_BYTES
+        nbytes = QWEN_DECODE_BYTES if qwen else DECODE_BYTES
         x = syn.activations(SEED, 1).to(dev)
         routes = [stack.route(l, x) for l in range(args.layers)]
         ws = ops.decode_workspace(stack.layers[0], shape.top_k, shared[0] if qwen else None, dev)
@@ -529,40 +642,50 @@ def kernel_case(args) -> None:
                           "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
 
 
+def stream_case(args, dev) -> None:
+    """Floors for the batch-1 decode call of --model: (a) launches that only read the call's bytes (16-byte loads
+    from many CTAs; bulk copies into a shared-memory ring from one CTA per SM), (b) the decode kernels themselves
+    with their arithmetic and / or their weight copies switched off.  Same harness as the decode figure: the layers'
+    buffers in rotation (more bytes than L2), replayed from a CUDA graph, CUDA events."""
+    from uma_qmoe_b200 import ops
+    qwen = args.model == "qwen"
+    nbytes = (QWEN_DECODE_BYTES if qwen else DECODE_BYTES) // 16 * 16
+    layers = 8 if qwen else 16
+    pk, pk_kind = peaks()
+    bufs = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(layers)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = {"case": "stream", "model": args.model, "bytes_per_launch": nbytes, "peak_gbs": pk["hbm_gbs"], "peak_source": pk_kind}
+    for mode, name in ((0, "loads_16_bytes_many_ctas"), (1, "bulk_copy_ring_one_cta_per_sm")):
+        def run(mode=mode):
+            for b in bufs:
+                ops.probe_stream(b, mode, status)
+        ms = timed(graphed(run), args.steps, args.warmup, 1) / layers
+        out[name] = {"us_per_launch": round(ms * 1e3, 2), "gbs": round(nbytes / (ms / 1e3) / 1e9, 1),
+                     "frac_of_peak": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+    out["probe_status"] = int(status.item())
+    # the switch is read once per process, so each setting runs in a process of its own
+    for flag, name in ((3, "decode_kernels_without_weight_copies_and_arithmetic"), (1, "decode_kernels_without_arithmetic"),
+                       (0, "decode_kernels")):
+        cmd = [sys.executable, str(ROOT / "bench.py"), "--only", "decode", "--model", args.model, "--layers", str(layers),
+               "--steps", str(args.steps), "--warmup", str(args.warmup)]
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, UMAQ_DECODE_DEBUG=str(flag)))
+        lines = [t for t in proc.stdout.splitlines() if t.startswith("{")]
+        out[name] = {"us_per_layer": round(json.loads(lines[-1])["us_per_layer"], 2)} if lines else {"error": proc.stderr[-200:]}
+    print(json.dumps(out))
+
+
 def prefill_phases_case(args, dev) -> None:
-    """Device time of every kernel of one prefill layer (OLMoE Q4, layer 0, --tokens tokens), each replayed from a
-    CUDA graph of 8 back-to-back launches so that no launch gap is inside the figure."""
-    from uma_qmoe_b200 import ops, synthetic as syn
-    from uma_qmoe_b200.stack import MoEStack, rms_renorm
+    """Device time of every kernel of one prefill layer (OLMoE Q4, layer 0, --tokens tokens)."""
+    from uma_qmoe_b200 import synthetic as syn
+    from uma_qmoe_b200.stack import MoEStack
     shape = syn.OLMOE
     stack = MoEStack.build(shape, "q4_group128", 1, SEED, dev, renormalize=True, skew=1.0)
-    layer = stack.layers[0]
     x = syn.activations(SEED, args.tokens).to(dev)
-    w, idx = stack.route(0, x)
-    routes = ops.route_sort(idx, w, shape.experts)
-    xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)
-    inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
-    yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
-    ws = ops.prefill_workspace(layer, args.tokens, shape.top_k, None, dev)
-    phases = [("router", lambda: stack.route(0, x)),
-              ("route_sort", lambda: ops.route_sort(idx, w, shape.experts)),
-              ("gather_rows", lambda: ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)),
-              ("gemm_gate_up", lambda: ops.grouped_gemm(layer, 0, xs, routes, permute_out=True, out=inter)),
-              ("gemm_down", lambda: ops.grouped_gemm(layer, 1, inter, routes, route_weight=routes.sorted_weight, out=yw)),
-              ("combine", lambda: ops.combine_routes(yw, idx, routes.route_pos)),
-              ("rms_norm", lambda: rms_renorm(x)),
-              ("whole_operator", lambda: ops.moe_prefill(layer, x, idx, w, ws))]
-    out = {}
-    for name, fn in phases:
-        def eight(fn=fn):
-            for _ in range(8):
-                fn()
-        out[name] = round(timed(graphed(eight), args.steps, args.warmup, 1) / 8 * 1e3, 2)
-    print(json.dumps({"case": "phases", "tokens": args.tokens, "us": out}))
+    print(json.dumps({"case": "phases", "tokens": args.tokens, "us": prefill_kernel_times(stack, x, shape, dev)}))
 
 
 def model_case(args, dev) -> None:
-    """BASELINE config 3: a Qwen1.5-MoE-A2.7B-shaped model with random weights (24 layers unless --layers says
+    """A Qwen1.5-MoE-A2.7B-shaped model with random weights (24 layers unless --layers says
     otherwise), experts of layers 0-15 BF16 and 16-23 Q8 (`--variant 0`) or all Q4 (`--variant 1`), greedy decode of
     128 prompt tokens + 32 generated at batch 1 through the Hugging Face model with this package's blocks."""
     import transformers
@@ -611,7 +734,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
     ap.add_argument("--cpu-tokens", type=int, default=TOKENS, help="tokens of the CPU arm's layer-0 call")
     ap.add_argument("--cpu-budget", type=float, default=240.0, help="seconds the CPU arm may spend on timed calls")
-    ap.add_argument("--only", choices=("all", "decode", "gemm", "model", "phases"), default="all",
+    ap.add_argument("--only", choices=("all", "decode", "gemm", "model", "phases", "stream"), default="all",
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")

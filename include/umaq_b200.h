@@ -86,7 +86,9 @@ int umaq_sm_count(void);
  * status: 0, or a UMAQ_ERR_* code if a bounded wait gave up or an expert index
  * was out of range.  A route with an out-of-range index contributes nothing, as
  * in the reference's kernels (src/uma_qmoe/native/packed_q4_kernel.cu:176), and
- * the output is still complete; after a timeout the output is undefined. */
+ * the output is still complete; after a timeout the output is undefined and the
+ * first 1024 bytes of the workspace must be zeroed again (once all work on it
+ * has drained) before the next call: the arrival counters in it are then stale. */
 size_t umaq_decode_workspace_bytes(int top_k, int intermediate, int shared_intermediate);
 int umaq_moe_decode(const umaq_layer* layer, const umaq_shared_expert* shared /* may be NULL */,
                     const void* hidden_bf16 /* device [H] */,
@@ -194,6 +196,11 @@ int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k
 int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows,
                       const int* num_tiles, const int* tile_table, int max_tiles, const float* route_weight,
                       int permute_out, void* out_bf16, unsigned* status, int variant, void* stream);
+/* Expert-parallel routing table (no counterpart in the reference): local_ids[i] = local expert id of
+ * expert_indices[i] on rank `rank`, or -1 (absent route) when another rank owns the expert.
+ * placement 0: expert e on rank e % ranks as local e / ranks; 1: rank e / experts_per_rank, local e % experts_per_rank. */
+int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long long count, int ranks, int rank,
+                      int experts_per_rank, int placement, int* local_ids, void* stream);
 /* Expert-parallel dispatch into fixed-capacity segments, so that the exchange needs no row counts
  * on the host (no counterpart in the reference, which is single-device).  The routes were sorted by
  * key = owner_rank * experts_per_rank + local_expert (umaq_route_sort over the keys; offsets is its
@@ -203,14 +210,10 @@ int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, l
  * slots keep meta -1, which every kernel of this library treats as an absent route; routes beyond
  * the capacity get route_slot -1 and set *overflow (device int, sticky; the caller then repeats the
  * layer with exact counts). */
-/* Expert-parallel routing table (no counterpart in the reference): local_ids[i] = local expert id of
- * expert_indices[i] on rank `rank`, or -1 (absent route) when another rank owns the expert.
- * placement 0: expert e on rank e % ranks as local e / ranks; 1: rank e / experts_per_rank, local e % experts_per_rank. */
-int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long long count, int ranks, int rank,
-                      int experts_per_rank, int placement, int* local_ids, void* stream);
 int umaq_ep_pack(const void* hidden_bf16, const int* sorted_route, const int* sorted_key, const float* sorted_weight,
                  const int* offsets, int routes, int top_k, int hidden, int ranks, int experts_per_rank, int capacity,
                  void* send_rows_bf16, int* send_meta, int* route_slot, int* overflow, void* stream);
+
 /* ---- expert-parallel exchange over peer memory (no counterpart in the reference) -----------------
  * One process per GPU; every rank holds a buffer of the same layout that all ranks have mapped
  * (torch.distributed._symmetric_memory or any other peer mapping).  base[p] is rank p's buffer as seen
@@ -262,6 +265,13 @@ int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, i
  * (src/uma_qmoe/q4.py:136-165, src/uma_qmoe/target_pack.py:92-112). */
 int umaq_quantize_groups(const void* src_bf16 /* device */, long long elements, int encoding,
                          void* codes /* device */, float* scales /* device */, void* stream);
+
+/* Measurement aid (no counterpart in the reference, not used by the operator): one launch that only reads
+ * `bytes` bytes (a multiple of 16, 16-byte aligned) from device memory and throws them away.  mode 0: 16-byte
+ * loads from many CTAs; mode 1: one persistent CTA per SM, cp.async.bulk copies into a shared-memory ring.
+ * status_u32 (device, may be NULL) receives UMAQ_ERR_DEVICE_TIMEOUT if a bounded wait gave up.  Gives the floor
+ * a batch-1 decode call of the same size can be compared with. */
+int umaq_probe_stream(const void* src, size_t bytes, int mode, void* status_u32, void* stream);
 
 #ifdef __cplusplus
 }

@@ -66,6 +66,55 @@ class _LayerCache:
         self.lock = threading.Lock()
 
 
+class _Workspace:
+    """A kernel workspace owned by one (shape, device, stream) and the host's view of its sticky status word.
+
+    After every call the first 16 bytes of the workspace (prefill status in word 0, decode status in word 2) are
+    copied to pinned host memory on the call's stream and an event is recorded; the next call on this workspace,
+    `cache_summary()` and `release_pack()` look at the copy once the event has completed.  Nothing on the hot
+    path waits for the device."""
+
+    __slots__ = ("kind", "buffer", "host", "event", "tokens")
+
+    def __init__(self, kind: str, buffer: Any, tokens: int) -> None:
+        import torch
+
+        self.kind, self.buffer, self.tokens = kind, buffer, tokens
+        self.host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.event: Any = None
+
+    def publish(self, stream: Any) -> None:
+        import torch
+
+        if torch.cuda.is_current_stream_capturing():
+            return                                   # a captured call reports through the workspace only
+        self.host.copy_(self.buffer[:16].view(torch.int32), non_blocking=True)
+        if self.event is None:
+            self.event = torch.cuda.Event()
+        self.event.record(stream)
+
+    def raise_if_failed(self, wait: bool) -> None:
+        import torch
+
+        if self.event is None or torch.cuda.is_current_stream_capturing():
+            return
+        if wait:
+            self.event.synchronize()
+        elif not self.event.query():
+            return
+        code = int(self.host[0 if self.kind == "prefill" else 2])
+        if code == 0:
+            return
+        # sticky on the device: clear it so that the error is reported once (all work on the buffer has finished)
+        self.host.zero_()
+        self.event = None
+        if code == -1:                               # UMAQ_ERR_BAD_ARGUMENT: the kernels skipped a route
+            self.buffer[:16].zero_()
+            raise RuntimeError("expert_indices contains an invalid expert")
+        self.buffer[:1024].zero_()                   # a timeout leaves stale counters behind
+        raise RuntimeError(f"an earlier uma_qmoe::moe_forward call failed on the device ({_native.ERRORS.get(code, code)})")
+
+
 class MixedTargetNativeBackend:
     """Executes Q4, Q8 and BF16 layers of an ExpertPack or TargetPack."""
 
@@ -80,7 +129,8 @@ class MixedTargetNativeBackend:
         self.platform = platform
         self.extension = extension
         self._cache = _LayerCache()
-        self._workspaces: dict[tuple, Any] = {}
+        self._workspaces: dict[tuple, _Workspace] = {}
+        self._workspace_lock = threading.Lock()
 
     # ---- construction ---------------------------------------------------------------------
     @classmethod
@@ -158,7 +208,15 @@ class MixedTargetNativeBackend:
         with self._cache.lock:
             self._cache.layers[(pack_handle, layer_index, str(device))] = layer
 
+    def check_device_status(self) -> None:
+        """Wait for the calls submitted so far and raise if one of them recorded a device-side error."""
+        with self._workspace_lock:
+            slots = list(self._workspaces.values())
+        for slot in slots:
+            slot.raise_if_failed(wait=True)
+
     def cache_summary(self) -> dict[str, int]:
+        self.check_device_status()
         with self._cache.lock:
             layers = list(self._cache.layers.values())
         return {
@@ -169,27 +227,38 @@ class MixedTargetNativeBackend:
 
     def release_pack(self, pack_handle: int) -> None:
         """Drop every device copy that belongs to a closed pack handle."""
+        try:
+            self.check_device_status()
+        finally:
+            self._drop_layers(pack_handle)
+
+    def _drop_layers(self, pack_handle: int) -> None:
         with self._cache.lock:
             for key in [k for k in self._cache.layers if k[0] == pack_handle]:
                 del self._cache.layers[key]
 
     # ---- execution ------------------------------------------------------------------------
-    def _workspace(self, kind: str, layer: Any, tokens: int, top_k: int, shared: Any, device: Any):
+    def _workspace(self, kind: str, layer: Any, tokens: int, top_k: int, shared: Any, device: Any, stream: Any) -> _Workspace:
+        """The workspace of this shape on this stream.  Calls on different streams (or threads, which have their own
+        current stream only if they set one) never share a workspace, so they may overlap on the device; a stream
+        keeps one prefill workspace per layer shape, grown to the largest token count seen."""
         from . import ops
 
-        key = (kind, str(device), layer.hidden, layer.intermediate, layer.num_experts, tokens, top_k,
-               0 if shared is None else int(shared.gate.shape[0]))
-        ws = self._workspaces.get(key)
-        if ws is None:
-            if kind == "decode":
-                ws = ops.decode_workspace(layer, top_k, shared, device)
-            else:
-                ws = ops.prefill_workspace(layer, tokens, top_k, shared, device)
-                # keep only the largest prefill workspace per shape family
-                for old in [k for k in self._workspaces if k[0] == "prefill" and k[1:5] == key[1:5] and k[6:] == key[6:]]:
-                    del self._workspaces[old]
-            self._workspaces[key] = ws
-        return ws
+        family = (kind, str(device), int(stream.cuda_stream), layer.hidden, layer.intermediate, layer.num_experts, top_k,
+                  0 if shared is None else int(shared.gate.shape[0]))
+        with self._workspace_lock:
+            slot = self._workspaces.get(family)
+            if slot is not None and (kind == "decode" or slot.tokens >= tokens):
+                return slot
+        if slot is not None:
+            slot.raise_if_failed(wait=True)          # the smaller buffer is about to be dropped
+        if kind == "decode":
+            fresh = _Workspace(kind, ops.decode_workspace(layer, top_k, shared, device), 1)
+        else:
+            fresh = _Workspace(kind, ops.prefill_workspace(layer, tokens, top_k, shared, device), tokens)
+        with self._workspace_lock:
+            self._workspaces[family] = fresh
+        return fresh
 
     def _run(self, model: str, hidden_states: Any, expert_indices: Any, routing_weights: Any, layer_index: int,
              pack_handle: int, shared: Optional[Any] = None):
@@ -222,12 +291,15 @@ class MixedTargetNativeBackend:
         out = torch.empty_like(flat)
         if tokens == 0:                       # an empty batch has an empty result; there is nothing to launch
             return out.reshape(hidden_states.shape)
+        slot = self._workspace("decode" if tokens == 1 else "prefill", layer, tokens, top_k, shared,
+                               hidden_states.device, stream)
+        slot.raise_if_failed(wait=False)      # an error an earlier call on this workspace left behind, if already known
+        slot.buffer.record_stream(stream)
         if tokens == 1:
-            ws = self._workspace("decode", layer, 1, top_k, shared, hidden_states.device)
-            ops.moe_decode(layer, flat, indices, weights, ws, shared, out=out)
+            ops.moe_decode(layer, flat, indices, weights, slot.buffer, shared, out=out)
         else:
-            ws = self._workspace("prefill", layer, tokens, top_k, shared, hidden_states.device)
-            ops.moe_prefill(layer, flat, indices, weights, ws, shared, out=out)
+            ops.moe_prefill(layer, flat, indices, weights, slot.buffer, shared, out=out)
+        slot.publish(stream)
         return out.reshape(hidden_states.shape)
 
     def __call__(self, hidden_states, expert_indices, routing_weights, layer_index: int, pack_handle: int):

@@ -318,6 +318,14 @@ def combine_routes(weighted: torch.Tensor, indices: torch.Tensor, route_pos: tor
     return out
 
 
+def probe_stream(buffer: torch.Tensor, mode: int, status: Optional[torch.Tensor] = None) -> None:
+    """One launch that only reads `buffer` (measurement aid): mode 0 = 16-byte loads from many CTAs, 1 = bulk copies
+    into a shared-memory ring from one CTA per SM."""
+    code = _native.lib().umaq_probe_stream(buffer.data_ptr(), buffer.numel() * buffer.element_size(), mode,
+                                           status.data_ptr() if status is not None else None, _stream(buffer.device))
+    _native.check(code, "umaq_probe_stream")
+
+
 def workspace_status(workspace: torch.Tensor) -> int:
     """Sticky device-side status word of a workspace (synchronises)."""
     return int(workspace[8:12].view(torch.int32).item())

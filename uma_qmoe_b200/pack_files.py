@@ -223,6 +223,9 @@ class _PackFile:
     def names(self) -> list[str]:
         return list(self._entries)
 
+    def shapes(self) -> dict[str, tuple[int, ...]]:
+        return {name: tuple(entry["shape"]) for name, entry in self._entries.items()}
+
     def close(self) -> None:
         if self._map is not None:
             self._map.close()
