@@ -352,7 +352,7 @@ def native_arm(args) -> None:
     # The batch-1 decode legs come first: a call is a few microseconds, and right after the long tensor-bound legs
     # the same kernels measured 10 % slower.
     decode_objects, decode_launches = {}, 0
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and args.legs == "all":
         decode_objects, decode_launches = decode_legs(stack, x_dev, shape, dev)
 
     with ClockSampler(local) as clocks:
@@ -371,7 +371,7 @@ def native_arm(args) -> None:
             **({"exchange": exchange_name} if world > 1 else {}),
             "tflops_step": 65536 * 12_582_912 * LAYERS / (ms / 1e3) / 1e12 / world}
 
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and args.legs == "all":
         # ---- roofline of the dominant kernel (the gate/up grouped GEMM of layer 0) and of the down GEMM ----
         w, idx = stack.route(0, x_dev)
         routes = ops.route_sort(idx, w, shape.experts)
@@ -734,6 +734,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
     ap.add_argument("--cpu-tokens", type=int, default=TOKENS, help="tokens of the CPU arm's layer-0 call")
     ap.add_argument("--cpu-budget", type=float, default=240.0, help="seconds the CPU arm may spend on timed calls")
+    ap.add_argument("--legs", choices=("all", "none"), default="all",
+                    help="none: only the timed step (for a profiler's launch list); the line then lacks roofline, decode and cpu_baseline")
     ap.add_argument("--only", choices=("all", "decode", "gemm", "model", "phases", "stream"), default="all",
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
