@@ -597,9 +597,10 @@ def kernel_case(args) -> None:
         return prefill_phases_case(args, dev)
     if args.only == "stream":
         return stream_case(args, dev)
-    qwen = args.only == "decode" and args.model == "qwen"
+    qwen = args.model == "qwen"
     shape = syn.QWEN if qwen else syn.OLMOE
-    stack = MoEStack.build(shape, "q8_group128" if qwen else "q4_group128", args.layers, SEED, dev,
+    encoding = args.encoding or ("q8_group128" if qwen else "q4_group128")
+    stack = MoEStack.build(shape, encoding, args.layers if args.only == "decode" else 1, SEED, dev,
                            renormalize=not qwen, skew=1.0)
     if args.only == "decode":
         # an OLMoE layer (Q4) or a Qwen1.5-MoE layer (Q8 routed experts, BF16 shared expert + gate)
@@ -621,23 +622,24 @@ def kernel_case(args) -> None:
                           "gbs": nbytes / (msg / 1e3) / 1e9, "status": ops.workspace_status(ws)}))
     else:
         x = syn.activations(SEED, args.tokens).to(dev)
+        quant = encoding != "bf16_le"               # quantised GEMMs take their activations in the permuted k order
         w, idx = stack.route(0, x)
         routes = ops.route_sort(idx, w, shape.experts)
-        xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)
+        xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=quant)
         inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
         yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
 
         def run():
-            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter, variant=args.variant)
+            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=quant, out=inter, variant=args.variant)
             ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw,
                              variant=args.variant)
         ms = timed(run, args.steps, args.warmup, 1)
-        ms1 = timed(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter,
+        ms1 = timed(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=quant, out=inter,
                                              variant=args.variant), args.steps, args.warmup, 1)
         ms2 = timed(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight,
                                              out=yw, variant=args.variant), args.steps, args.warmup, 1)
         flops = 2.0 * xs.shape[0] * 3 * shape.hidden * shape.intermediate
-        print(json.dumps({"case": "gemm", "tokens": args.tokens, "variant": args.variant, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
+        print(json.dumps({"case": "gemm", "model": args.model, "encoding": encoding, "tokens": args.tokens, "variant": args.variant, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
                           "tflops": flops / (ms / 1e3) / 1e12, "tflops_gate_up": flops * 2 / 3 / (ms1 / 1e3) / 1e12,
                           "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
 
@@ -742,6 +744,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")
     ap.add_argument("--model", choices=("olmoe", "qwen"), default="olmoe",
                     help="layer shape of the --only decode case: olmoe = config 0 (Q4), qwen = config 2 (Q8 + shared)")
+    ap.add_argument("--encoding", choices=("q4_group128", "q8_group128", "bf16_le"), default=None,
+                    help="expert encoding of the --only decode / gemm cases (default: q4 for olmoe, q8 for qwen)")
     ap.add_argument("--variant", type=int, default=0, choices=(0, 1, 2),
                     help="grouped GEMM kernel of the --only gemm case: 0/1 one CTA per tile (default), 2 CTA pairs")
     args = ap.parse_args()

@@ -72,7 +72,7 @@ def pack_digests(reader, layer: int, experts: list[int]) -> dict[str, str]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "src"))
     from transformers.models.olmoe.modeling_olmoe import OlmoeTopKRouter
