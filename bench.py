@@ -597,6 +597,8 @@ def kernel_case(args) -> None:
         return prefill_phases_case(args, dev)
     if args.only == "stream":
         return stream_case(args, dev)
+    if args.only == "stage":
+        return stage_case(args, dev)
     qwen = args.model == "qwen"
     shape = syn.QWEN if qwen else syn.OLMOE
     encoding = args.encoding or ("q8_group128" if qwen else "q4_group128")
@@ -676,6 +678,61 @@ def stream_case(args, dev) -> None:
     print(json.dumps(out))
 
 
+def stage_case(args, dev) -> None:
+    """Host -> device staging of one OLMoE layer (64 experts, packed Q4: 213.9 MB) from an ExpertPack file: the
+    native reader (C++ mapping and checks, worker thread, pinned 32 MiB chunks, one cudaMemcpyAsync per piece) against
+    the Python reader's path (pinned tensors filled expert by expert, then copied).  The file is written by this
+    package's writer from a layer packed on the device; the staged bytes must equal that layer's."""
+    import tempfile
+    from uma_qmoe_b200 import custom_op, native_backend, synthetic as syn
+    from uma_qmoe_b200.formats import PackedTensor
+    from uma_qmoe_b200.pack_files import ExpertPackFile, NativeExpertPackFile
+    from uma_qmoe_b200.pack_writer import write_expert_pack
+    from uma_qmoe_b200.packs import expert_tensor_name
+    from uma_qmoe_b200.stack import random_layer
+    shape = syn.OLMOE
+    source = random_layer(shape, "q4_group128", SEED, dev)
+    host = {p: (getattr(source, p).cpu().numpy().reshape(shape.experts, -1), getattr(source, p + "_scales").cpu().numpy().reshape(shape.experts, -1))
+            for p in ("gate", "up", "down")}
+
+    def tensors():
+        for e in range(shape.experts):
+            for p in ("gate", "up", "down"):
+                dims = (shape.hidden, shape.intermediate) if p == "down" else (shape.intermediate, shape.hidden)
+                yield expert_tensor_name(0, e, p + "_proj"), PackedTensor("q4_group128", dims, host[p][0][e].tobytes(), host[p][1][e].tobytes())
+    tmp = Path(tempfile.mkdtemp(prefix="umaq_stage_"))
+    path = tmp / "layer0.uqmoepk"
+    identity = dict(model_id="allenai/OLMoE-1B-7B-0125", model_revision="0" * 40, model_manifest_sha256="0" * 64)
+    t0 = time.perf_counter()
+    info = write_expert_pack(path, tensors(), **identity)
+    write_s = time.perf_counter() - t0
+    backend = native_backend.install_mixed_target_backend()
+    out = {"case": "stage", "layer_bytes": source.device_storage_bytes, "file_bytes": info["file_size"], "write_seconds": round(write_s, 3)}
+    for name, cls in (("native_reader", NativeExpertPackFile), ("python_reader", ExpertPackFile)):
+        t0 = time.perf_counter()
+        reader = cls(path, expected_model_id=identity["model_id"])
+        open_s = time.perf_counter() - t0
+        times = []
+        for rep in range(3):
+            handle = custom_op.register_expert_pack(reader)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            with custom_op.acquire_expert_pack(handle) as r:
+                layer = backend._device_layer(handle, 0, dev, r, "olmoe")
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+            same = all(torch.equal(a.reshape(-1).view(torch.uint8), b.reshape(-1).view(torch.uint8))
+                       for a, b in zip(layer.tensors, source.tensors))
+            custom_op.unregister_expert_pack(handle)          # drops the staged copy
+        best = min(times)
+        out[name] = {"open_and_validate_seconds": round(open_s, 3), "stage_seconds": [round(t, 4) for t in times],
+                     "gb_per_s": round(source.device_storage_bytes / best / 1e9, 2), "bytes_equal": bool(same)}
+        reader.close()
+    path.unlink()
+    tmp.rmdir()
+    print(json.dumps(out))
+
+
 def prefill_phases_case(args, dev) -> None:
     """Device time of every kernel of one prefill layer (OLMoE Q4, layer 0, --tokens tokens)."""
     from uma_qmoe_b200 import synthetic as syn
@@ -738,7 +795,7 @@ def main() -> None:
     ap.add_argument("--cpu-budget", type=float, default=240.0, help="seconds the CPU arm may spend on timed calls")
     ap.add_argument("--legs", choices=("all", "none"), default="all",
                     help="none: only the timed step (for a profiler's launch list); the line then lacks roofline, decode and cpu_baseline")
-    ap.add_argument("--only", choices=("all", "decode", "gemm", "model", "phases", "stream"), default="all",
+    ap.add_argument("--only", choices=("all", "decode", "gemm", "model", "phases", "stream", "stage"), default="all",
                     help="small single-kernel cases for profiler captures (not a bench line)")
     ap.add_argument("--tokens", type=int, default=1024, help="tokens of the --only gemm case")
     ap.add_argument("--layers", type=int, default=2, help="layers of the --only cases")

@@ -266,6 +266,49 @@ int umaq_combine_routes(const void* weighted_bf16, const void* expert_indices, i
 int umaq_quantize_groups(const void* src_bf16 /* device */, long long elements, int encoding,
                          void* codes /* device */, float* scales /* device */, void* stream);
 
+/* ---- native pack reader and asynchronous staging --------------------------------------------------
+ * Counterpart of the reference's Python readers (src/uma_qmoe/expert_pack.py:317-556 ExpertPackReader,
+ * src/uma_qmoe/target_pack.py:493-812 TargetPackReader) and of the blocking per-layer staging in
+ * src/uma_qmoe/native_backend.py:374-455.  umaq_pack_open maps the file read-only once and checks every
+ * rule of the container before it returns a handle (prefix, SHA-256 of header, payload and every tensor,
+ * canonical header JSON, model and policy identities, tensor layout, zero gaps, Q4 reserved code, scales);
+ * the first violation fails the call with UMAQ_ERR_BAD_ARGUMENT and umaq_last_error() holds the same
+ * message the Python readers raise.  kind: 0 = ExpertPack (UQMOEPK1), 1 = TargetPack (UQMOTPK1).
+ * The expected_* strings may be NULL (not checked).  Views point into the mapping and stay valid until
+ * umaq_pack_close. */
+typedef struct umaq_pack umaq_pack;
+typedef struct umaq_stage_ticket umaq_stage_ticket;
+typedef struct umaq_pack_tensor {
+  const char* name;
+  const void* data;          /* canonical codes */
+  size_t data_bytes;
+  const void* scales;        /* float32 group scales, scale_bytes == 0 for bf16_le */
+  size_t scale_bytes;
+  int32_t encoding;          /* UMAQ_ENC_* */
+  int32_t rank;
+  long long shape[4];
+  int32_t layer, expert, projection;   /* projection: 0 gate, 1 up, 2 down; -1 where the name is no expert tensor */
+} umaq_pack_tensor;
+int umaq_pack_open(const char* path, int kind, const char* expected_model_id, const char* expected_model_revision,
+                   const char* expected_model_manifest_sha256, const char* expected_policy_id, umaq_pack** out);
+void umaq_pack_close(umaq_pack* pack);
+long long umaq_pack_tensor_count(const umaq_pack* pack);
+const char* umaq_pack_header_json(const umaq_pack* pack, size_t* length);   /* the header bytes as stored (canonical JSON) */
+int umaq_pack_layer_encoding(const umaq_pack* pack, int layer);             /* UMAQ_ENC_* or a negative error */
+int umaq_pack_tensor_view(const umaq_pack* pack, const char* name, umaq_pack_tensor* view);
+int umaq_pack_tensor_at(const umaq_pack* pack, long long index, umaq_pack_tensor* view);   /* file order */
+/* SHA-256 of a host buffer with the reader's implementation (scalar_only != 0: without the CPU's SHA extensions). */
+int umaq_sha256(const void* data, size_t bytes, int scalar_only, unsigned char digest[32]);
+/* Stages layer `layer_index` of the pack into the caller's device tensors `dst` (the umaq_layer layout: per
+ * projection all experts concatenated; dst->encoding / num_experts / hidden / intermediate say what is expected
+ * and must match the pack).  Returns at once: a worker thread copies the tensors from the mapping into two
+ * pinned 32 MiB buffers in turn (several threads per chunk) and issues one cudaMemcpyAsync per piece on a stream
+ * of its own.  umaq_stage_wait blocks the host until everything is enqueued (not until it is copied), makes
+ * `stream` wait for the copies, frees the ticket and reports the worker's host time.  One layer is staged at a
+ * time per pack; close the pack only after every ticket has been waited for. */
+int umaq_stage_layer_async(umaq_pack* pack, int layer_index, const umaq_layer* dst, int device, umaq_stage_ticket** ticket);
+int umaq_stage_wait(umaq_stage_ticket* ticket, void* stream, double* host_seconds /* may be NULL */);
+
 /* Measurement aid (no counterpart in the reference, not used by the operator): one launch that only reads
  * `bytes` bytes (a multiple of 16, 16-byte aligned) from device memory and throws them away.  mode 0: 16-byte
  * loads from many CTAs; mode 1: one persistent CTA per SM, cp.async.bulk copies into a shared-memory ring.

@@ -11,12 +11,24 @@ import pytest
 
 from uma_qmoe_b200 import formats, synthetic as syn
 from uma_qmoe_b200.formats import ContractError
-from uma_qmoe_b200.pack_files import ExpertPackFile, TargetPackFile
+from uma_qmoe_b200.pack_files import ExpertPackFile, NativeExpertPackFile, NativeTargetPackFile, TargetPackFile
 from uma_qmoe_b200.packs import expert_tensor_name
 
 SEED = 20260917
 PREFIX = struct.Struct("<8sIIQQ32s32s")
 SHAPES = (("gate_proj", (4, 256)), ("up_proj", (4, 256)), ("down_proj", (256, 4)))
+
+
+class _Readers:
+    def __init__(self, expert, target):
+        self.Expert, self.Target = expert, target
+
+
+@pytest.fixture(params=["python", "native"])
+def impl(request):
+    """Both reader families: the Python ones and the ones on the library's C++ reader (umaq_pack_open); every case
+    below must hold for both, with the same messages."""
+    return _Readers(ExpertPackFile, TargetPackFile) if request.param == "python" else _Readers(NativeExpertPackFile, NativeTargetPackFile)
 
 
 def _source(expert: int, family: int, shape):
@@ -41,8 +53,8 @@ def _rebuild(path, magic, header, payload, canonical=True):
     return path
 
 
-def test_expert_pack_file_serves_the_writers_bytes(golden_dir):
-    with ExpertPackFile(golden_dir / "tiny.uqmoepk", expected_model_id="allenai/OLMoE-1B-7B-0125") as pack:
+def test_expert_pack_file_serves_the_writers_bytes(golden_dir, impl):
+    with impl.Expert(golden_dir / "tiny.uqmoepk", expected_model_id="allenai/OLMoE-1B-7B-0125") as pack:
         assert pack.mapping_count == 1 and pack.layer_encoding(7) == "q4_group128"
         assert pack.header["quantization"]["group_size"] == 128
         assert len(pack.names()) == 6
@@ -57,8 +69,8 @@ def test_expert_pack_file_serves_the_writers_bytes(golden_dir):
             pack.tensor_views("model.layers.0.mlp.experts.9.gate_proj.weight")
 
 
-def test_target_pack_file_serves_all_three_encodings(golden_dir):
-    with TargetPackFile(golden_dir / "tiny.uqmotpk", expected_policy_id="tiny") as pack:
+def test_target_pack_file_serves_all_three_encodings(golden_dir, impl):
+    with impl.Target(golden_dir / "tiny.uqmotpk", expected_policy_id="tiny") as pack:
         assert pack.mapping_count == 1
         assert [pack.layer_encoding(i) for i in range(3)] == ["q4_group128", "q8_group128", "bf16_le"]
         with pytest.raises(ContractError, match="layer index"):
@@ -76,19 +88,20 @@ def test_target_pack_file_serves_all_three_encodings(golden_dir):
                     data.release(); scales.release()
 
 
-def test_expected_identities_are_enforced(golden_dir):
+def test_expected_identities_are_enforced(golden_dir, impl):
     with pytest.raises(ContractError, match="model id mismatch"):
-        ExpertPackFile(golden_dir / "tiny.uqmoepk", expected_model_id="someone/else")
+        impl.Expert(golden_dir / "tiny.uqmoepk", expected_model_id="someone/else")
     with pytest.raises(ContractError, match="model revision mismatch"):
-        TargetPackFile(golden_dir / "tiny.uqmotpk", expected_model_revision="1" * 40)
+        impl.Target(golden_dir / "tiny.uqmotpk", expected_model_revision="1" * 40)
     with pytest.raises(ContractError, match="policy id mismatch"):
-        TargetPackFile(golden_dir / "tiny.uqmotpk", expected_policy_id="other")
+        impl.Target(golden_dir / "tiny.uqmotpk", expected_policy_id="other")
 
 
-@pytest.mark.parametrize("name,reader", [("tiny.uqmoepk", ExpertPackFile), ("tiny.uqmotpk", TargetPackFile)])
-def test_container_level_corruption_is_rejected(golden_dir, tmp_path, name, reader):
+@pytest.mark.parametrize("name", ["tiny.uqmoepk", "tiny.uqmotpk"])
+def test_container_level_corruption_is_rejected(golden_dir, tmp_path, name, impl):
     raw = bytearray((golden_dir / name).read_bytes())
-    kind = "ExpertPack" if reader is ExpertPackFile else "TargetPack"
+    reader = impl.Expert if name.endswith("epk") else impl.Target
+    kind = "ExpertPack" if name.endswith("epk") else "TargetPack"
 
     def damaged(edit):
         copy = bytearray(raw)
@@ -117,7 +130,7 @@ def test_container_level_corruption_is_rejected(golden_dir, tmp_path, name, read
         reader(tmp_path / "missing.bin")
 
 
-def test_rehashed_tampering_of_the_expert_pack_is_rejected(golden_dir, tmp_path):
+def test_rehashed_tampering_of_the_expert_pack_is_rejected(golden_dir, tmp_path, impl):
     """The container hashes alone are not trusted: documents and payloads that were edited and re-hashed."""
     magic, header, payload = _split(golden_dir / "tiny.uqmoepk")
     out = tmp_path / "edited.uqmoepk"
@@ -130,21 +143,21 @@ def test_rehashed_tampering_of_the_expert_pack_is_rejected(golden_dir, tmp_path)
             payload_change(h, p)
         return _rebuild(out, magic, h, p, canonical)
 
-    ExpertPackFile(edited(lambda h: None)).close()                      # the rebuild itself is faithful
+    impl.Expert(edited(lambda h: None)).close()                      # the rebuild itself is faithful
     with pytest.raises(ContractError, match="tensor count is inconsistent"):
-        ExpertPackFile(edited(lambda h: h.__setitem__("tensor_count", 5)))
+        impl.Expert(edited(lambda h: h.__setitem__("tensor_count", 5)))
     with pytest.raises(ContractError, match="not canonical"):
-        ExpertPackFile(edited(lambda h: None, canonical=False))
+        impl.Expert(edited(lambda h: None, canonical=False))
     with pytest.raises(ContractError, match="quantization contract mismatch"):
-        ExpertPackFile(edited(lambda h: h["quantization"].__setitem__("signed_range", [-8, 7])))
+        impl.Expert(edited(lambda h: h["quantization"].__setitem__("signed_range", [-8, 7])))
     with pytest.raises(ContractError, match="model identity hash mismatch"):
-        ExpertPackFile(edited(lambda h: h["model"].__setitem__("model_revision", "f" * 40)))
+        impl.Expert(edited(lambda h: h["model"].__setitem__("model_revision", "f" * 40)))
     with pytest.raises(ContractError, match="layout is invalid"):
-        ExpertPackFile(edited(lambda h: h["tensors"][1].__setitem__("packed_offset", h["tensors"][1]["packed_offset"] + 64)))
+        impl.Expert(edited(lambda h: h["tensors"][1].__setitem__("packed_offset", h["tensors"][1]["packed_offset"] + 64)))
     with pytest.raises(ContractError, match="effective bpw is invalid"):
-        ExpertPackFile(edited(lambda h: h["tensors"][0].__setitem__("effective_bits_per_weight", 5.0)))
+        impl.Expert(edited(lambda h: h["tensors"][0].__setitem__("effective_bits_per_weight", 5.0)))
     with pytest.raises(ContractError, match="names must be unique and safe"):
-        ExpertPackFile(edited(lambda h: h["tensors"][1].__setitem__("name", h["tensors"][0]["name"])))
+        impl.Expert(edited(lambda h: h["tensors"][1].__setitem__("name", h["tensors"][0]["name"])))
 
     def tensor_hash(h, p, index):
         e = h["tensors"][index]
@@ -166,16 +179,16 @@ def test_rehashed_tampering_of_the_expert_pack_is_rejected(golden_dir, tmp_path)
         p[e["scale_offset"] + e["scale_bytes"]] = 7
 
     with pytest.raises(ContractError, match="contains reserved Q4 -8"):
-        ExpertPackFile(edited(lambda h: None, reserved_code))
+        impl.Expert(edited(lambda h: None, reserved_code))
     with pytest.raises(ContractError, match="scales must be finite and positive"):
-        ExpertPackFile(edited(lambda h: None, bad_scale))
+        impl.Expert(edited(lambda h: None, bad_scale))
     with pytest.raises(ContractError, match="trailing gap must be zero"):
-        ExpertPackFile(edited(lambda h: None, dirty_gap))
+        impl.Expert(edited(lambda h: None, dirty_gap))
     with pytest.raises(ContractError, match="hash mismatch"):
-        ExpertPackFile(edited(lambda h: None, lambda h, p: p.__setitem__(h["tensors"][3]["packed_offset"], 0x11)))
+        impl.Expert(edited(lambda h: None, lambda h, p: p.__setitem__(h["tensors"][3]["packed_offset"], 0x11)))
 
 
-def test_rehashed_tampering_of_the_target_pack_is_rejected(golden_dir, tmp_path):
+def test_rehashed_tampering_of_the_target_pack_is_rejected(golden_dir, tmp_path, impl):
     magic, header, payload = _split(golden_dir / "tiny.uqmotpk")
     out = tmp_path / "edited.uqmotpk"
 
@@ -184,25 +197,105 @@ def test_rehashed_tampering_of_the_target_pack_is_rejected(golden_dir, tmp_path)
         change(h)
         return _rebuild(out, magic, h, payload)
 
-    TargetPackFile(edited(lambda h: None)).close()
+    impl.Target(edited(lambda h: None)).close()
     with pytest.raises(ContractError, match="encoding tensor counts are inconsistent"):
-        TargetPackFile(edited(lambda h: h["encoding_tensor_counts"].__setitem__("bf16_le", 5)))
+        impl.Target(edited(lambda h: h["encoding_tensor_counts"].__setitem__("bf16_le", 5)))
     with pytest.raises(ContractError, match="policy identity hash mismatch"):
-        TargetPackFile(edited(lambda h: h["policy"].__setitem__("policy_id", "renamed")))
+        impl.Target(edited(lambda h: h["policy"].__setitem__("policy_id", "renamed")))
     with pytest.raises(ContractError, match="every layer exactly once"):
-        TargetPackFile(edited(lambda h: h["policy"]["layer_encodings"].pop("15")))
+        impl.Target(edited(lambda h: h["policy"]["layer_encodings"].pop("15")))
     with pytest.raises(ContractError, match="unsupported encoding"):
-        TargetPackFile(edited(lambda h: h["policy"]["layer_encodings"].__setitem__("3", "q2_group64")))
+        impl.Target(edited(lambda h: h["policy"]["layer_encodings"].__setitem__("3", "q2_group64")))
     with pytest.raises(ContractError, match="policy identity is invalid"):
-        TargetPackFile(edited(lambda h: h["tensors"][0].__setitem__("encoding", "q8_group128")))
+        impl.Target(edited(lambda h: h["tensors"][0].__setitem__("encoding", "q8_group128")))
     with pytest.raises(ContractError, match="schema is unsupported"):
-        TargetPackFile(edited(lambda h: h.__setitem__("format", "something_else")))
+        impl.Target(edited(lambda h: h.__setitem__("format", "something_else")))
 
 
-def test_pack_files_register_with_the_operator_registry(golden_dir):
+def test_pack_files_register_with_the_operator_registry(golden_dir, impl):
     from uma_qmoe_b200 import custom_op
-    with TargetPackFile(golden_dir / "tiny.uqmotpk") as pack:
+    with impl.Target(golden_dir / "tiny.uqmotpk") as pack:
         handle = custom_op.register_target_pack(pack)
         with custom_op.acquire_expert_pack(handle) as reader:
             assert reader is pack and reader.layer_encoding(1) == "q8_group128"
         custom_op.unregister_expert_pack(handle)
+
+
+def _hand_made_expert_pack(path, tail_nibble: int = 0, scale: float = 0.5):
+    """A one-tensor ExpertPack written here byte by byte: shape [1, 3], so the second data byte has a padding
+    nibble, and a bits-per-weight value (512 / 3) whose canonical JSON form needs all 17 digits."""
+    data = bytes([0x21, 0x03 | (tail_nibble << 4)])
+    scales = struct.pack("<f", scale)
+    payload = data + bytes(2) + scales + bytes(56)
+    triple = {"model_id": "allenai/OLMoE-1B-7B-0125", "model_revision": "0" * 40, "model_manifest_sha256": "0" * 64}
+    canonical = lambda doc: json.dumps(doc, sort_keys=True, separators=(",", ":")).encode()
+    header = {
+        "schema_version": 1,
+        "model": dict(triple, model_identity_sha256=hashlib.sha256(canonical(triple)).hexdigest()),
+        "quantization": {"bits": 4, "group_size": 128, "nibble_order": "low_first_twos_complement", "rounding": "nearest_even",
+                         "scale_dtype": "float32_le", "signed_range": [-7, 7], "zero_point": None},
+        "tensor_alignment_bytes": 64, "tensor_count": 1,
+        "tensors": [{"name": "model.layers.0.mlp.experts.0.gate_proj.weight", "shape": [1, 3], "element_count": 3,
+                     "group_count": 1, "packed_offset": 0, "packed_bytes": 2, "scale_offset": 4, "scale_bytes": 4,
+                     "storage_end_offset": 64, "effective_bits_per_weight": 64 * 8 / 3,
+                     "tensor_payload_sha256": hashlib.sha256(data + scales).hexdigest()}],
+    }
+    return _rebuild(path, b"UQMOEPK1", header, payload)
+
+
+def test_odd_element_count_tail_nibble_and_scales(tmp_path, impl):
+    """The remaining rejection cases of the reference's ``tests/unit/test_expert_pack.py:132-168``: a non-zero padding
+    nibble behind an odd element count and a NaN scale, each with every hash recomputed."""
+    with impl.Expert(_hand_made_expert_pack(tmp_path / "good.uqmoepk")) as pack:
+        data, scales, entry = pack.tensor_views("model.layers.0.mlp.experts.0.gate_proj.weight")
+        assert bytes(data) == b"\x21\x03" and struct.unpack("<f", bytes(scales)) == (0.5,)
+        assert entry["effective_bits_per_weight"] == 512 / 3
+        data.release(); scales.release()
+    with pytest.raises(ContractError, match="non-zero Q4 tail padding"):
+        impl.Expert(_hand_made_expert_pack(tmp_path / "tail.uqmoepk", tail_nibble=1))
+    with pytest.raises(ContractError, match="scales must be finite and positive"):
+        impl.Expert(_hand_made_expert_pack(tmp_path / "nan.uqmoepk", scale=float("nan")))
+    with pytest.raises(ContractError, match="scales must be finite and positive"):
+        impl.Expert(_hand_made_expert_pack(tmp_path / "zero.uqmoepk", scale=0.0))
+
+
+def test_native_sha256_matches_hashlib_on_both_code_paths():
+    """The C++ reader's SHA-256, with and without the CPU's SHA extensions, on lengths around the block and padding
+    boundaries."""
+    import ctypes as C
+
+    from uma_qmoe_b200 import _native
+    lib = _native.lib()
+    rng = np.random.default_rng(3)
+    for n in (0, 1, 55, 56, 57, 63, 64, 65, 119, 120, 128, 4097, 1 << 20):
+        data = rng.integers(0, 256, n, dtype=np.uint8).tobytes()
+        for scalar_only in (0, 1):
+            digest = (C.c_ubyte * 32)()
+            assert lib.umaq_sha256(data, n, scalar_only, digest) == 0
+            assert bytes(digest) == hashlib.sha256(data).digest(), (n, scalar_only)
+
+
+def test_writers_reproduce_the_reference_writers_files(golden_dir, tmp_path):
+    """This package's writers, given the inputs the golden files were made from, must write the same files byte for
+    byte as the reference's writers did (prefix, canonical header, payload layout and hashes)."""
+    from uma_qmoe_b200.pack_writer import write_expert_pack, write_target_pack
+    zeros40, zeros64 = "0" * 40, "0" * 64
+    small = [(expert_tensor_name(0, e, p), _source(e, i, s)) for e in range(2) for i, (p, s) in enumerate(SHAPES)]
+    info = write_expert_pack(tmp_path / "mine.uqmoepk", small, model_id="allenai/OLMoE-1B-7B-0125", model_revision=zeros40,
+                             model_manifest_sha256=zeros64)
+    assert (tmp_path / "mine.uqmoepk").read_bytes() == (golden_dir / "tiny.uqmoepk").read_bytes()
+    assert info["file_size"] == (golden_dir / "tiny.uqmoepk").stat().st_size
+    layered = [(expert_tensor_name(l, e, p), _source(e, i, s)) for l in range(3) for e in range(2)
+               for i, (p, s) in enumerate(SHAPES)]
+    write_target_pack(tmp_path / "mine.uqmotpk", layered, model_id="allenai/OLMoE-1B-7B-0125", model_revision=zeros40,
+                      model_manifest_sha256=zeros64, policy_id="tiny",
+                      layer_encodings={i: ("q4_group128", "q8_group128", "bf16_le")[i % 3] for i in range(16)},
+                      policy_evidence_sha256=zeros64)
+    assert (tmp_path / "mine.uqmotpk").read_bytes() == (golden_dir / "tiny.uqmotpk").read_bytes()
+    with pytest.raises(ContractError, match="refusing to overwrite"):
+        write_expert_pack(tmp_path / "mine.uqmoepk", small, model_id="x", model_revision=zeros40, model_manifest_sha256=zeros64)
+    with pytest.raises(ContractError, match="every layer exactly once"):
+        write_target_pack(tmp_path / "other.uqmotpk", layered, model_id="allenai/OLMoE-1B-7B-0125", model_revision=zeros40,
+                          model_manifest_sha256=zeros64, policy_id="tiny", layer_encodings={0: "q4_group128"},
+                          policy_evidence_sha256=zeros64)
+    assert not (tmp_path / "other.uqmotpk").exists() and len(list(tmp_path.iterdir())) == 2    # no temporary files left

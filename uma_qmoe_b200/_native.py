@@ -33,6 +33,14 @@ class SharedExpert(C.Structure):
 
 
 # name -> (restype, argtypes); every symbol include/umaq_b200.h declares
+class PackTensor(C.Structure):
+    """``umaq_pack_tensor``: one tensor of a mapped pack file."""
+
+    _fields_ = [("name", C.c_char_p), ("data", C.c_void_p), ("data_bytes", C.c_size_t), ("scales", C.c_void_p),
+                ("scale_bytes", C.c_size_t), ("encoding", C.c_int32), ("rank", C.c_int32), ("shape", C.c_longlong * 4),
+                ("layer", C.c_int32), ("expert", C.c_int32), ("projection", C.c_int32)]
+
+
 SIGNATURES = {
     "umaq_build_info": (C.c_int, [C.c_char_p, C.c_int]),
     "umaq_last_error": (C.c_char_p, []),
@@ -69,6 +77,16 @@ SIGNATURES = {
                                       C.c_void_p, C.c_void_p]),
     "umaq_quantize_groups": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "umaq_probe_stream": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]),
+    "umaq_pack_open": (C.c_int, [C.c_char_p, C.c_int, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_void_p)]),
+    "umaq_pack_close": (None, [C.c_void_p]),
+    "umaq_pack_tensor_count": (C.c_longlong, [C.c_void_p]),
+    "umaq_pack_header_json": (C.c_void_p, [C.c_void_p, C.POINTER(C.c_size_t)]),
+    "umaq_pack_layer_encoding": (C.c_int, [C.c_void_p, C.c_int]),
+    "umaq_pack_tensor_view": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(PackTensor)]),
+    "umaq_pack_tensor_at": (C.c_int, [C.c_void_p, C.c_longlong, C.POINTER(PackTensor)]),
+    "umaq_sha256": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
+    "umaq_stage_layer_async": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Layer), C.c_int, C.POINTER(C.c_void_p)]),
+    "umaq_stage_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_double)]),
 }
 
 

@@ -130,6 +130,7 @@ class MixedTargetNativeBackend:
         self.extension = extension
         self._cache = _LayerCache()
         self._workspaces: dict[tuple, _Workspace] = {}
+        self._pending: dict[tuple[int, int, str], Any] = {}      # layers being staged: (DeviceLayer, wait)
         self._workspace_lock = threading.Lock()
 
     # ---- construction ---------------------------------------------------------------------
@@ -170,6 +171,15 @@ class MixedTargetNativeBackend:
             raise RuntimeError(f"this backend cannot execute layer {layer_index} encoded as {encoding}; "
                                "install the mixed backend")
         quantised = encoding != "bf16_le"
+        if hasattr(reader, "stage_layer_async"):
+            # the native reader stages by itself: a worker thread, pinned chunks, copies on a stream of its own;
+            # a prefetch may already be under way
+            with self._cache.lock:
+                pending = self._pending.pop(key, None)
+            layer, wait = pending if pending is not None else self._start_staging(reader, layer_index, device, model)
+            wait(torch.cuda.current_stream(device))
+            with self._cache.lock:
+                return self._cache.layers.setdefault(key, layer)
         staged = {}
         for proj, (rows, k) in (("gate_proj", (inter, hidden)), ("up_proj", (inter, hidden)),
                                 ("down_proj", (hidden, inter))):
@@ -202,6 +212,42 @@ class MixedTargetNativeBackend:
         with self._cache.lock:
             return self._cache.layers.setdefault(key, layer)
 
+    def _start_staging(self, reader: Any, layer_index: int, device: Any, model: str):
+        import torch
+
+        from .ops import DeviceLayer
+        layers, experts, _k, hidden, inter = _MODELS[model]
+        if not 0 <= layer_index < layers:
+            raise RuntimeError(f"{'OLMoE' if model == 'olmoe' else 'Qwen'} layer_index must be in [0, {layers - 1}]")
+        encoding = self._encoding_of(reader, layer_index)
+        if encoding not in self.allowed_encodings:
+            raise RuntimeError(f"this backend cannot execute layer {layer_index} encoded as {encoding}; "
+                               "install the mixed backend")
+        quantised = encoding != "bf16_le"
+        codes = lambda rows, k: torch.empty(experts * rows * row_bytes(encoding, k), dtype=torch.uint8, device=device)
+        scales = lambda rows, k: torch.empty(experts * rows * k // 128, dtype=torch.float32, device=device) if quantised else None
+        layer = DeviceLayer(encoding, experts, hidden, inter, codes(inter, hidden), codes(inter, hidden), codes(hidden, inter),
+                            scales(inter, hidden), scales(inter, hidden), scales(hidden, inter))
+        # the copies run on the reader's own stream: whatever used this memory before must have finished
+        torch.cuda.current_stream(device).synchronize()
+        return layer, reader.stage_layer_async(layer_index, layer, device)
+
+    def prefetch_layer(self, pack_handle: int, layer_index: int, device: Any, model: str = "olmoe") -> None:
+        """Start staging a layer of a pack opened with the native reader and return at once; the first call that
+        needs the layer waits for what is left.  (Nothing to do for the Python readers, which stage on demand.)"""
+        import torch
+        device = torch.device(device)
+        key = (pack_handle, layer_index, str(device))
+        with acquire_expert_pack(pack_handle) as reader:
+            if not hasattr(reader, "stage_layer_async"):
+                return
+            with self._cache.lock:
+                if key in self._cache.layers or key in self._pending:
+                    return
+            started = self._start_staging(reader, layer_index, device, model)
+            with self._cache.lock:
+                self._pending[key] = started
+
     def preload_layer(self, pack_handle: int, layer_index: int, device: Any, layer: Any) -> None:
         """Adopt a layer that already sits on the device in the staged layout (synthetic weights
         built with the device-side packer), instead of staging it from the pack's host bytes."""
@@ -233,6 +279,11 @@ class MixedTargetNativeBackend:
             self._drop_layers(pack_handle)
 
     def _drop_layers(self, pack_handle: int) -> None:
+        import torch
+        with self._cache.lock:
+            unfinished = [self._pending.pop(k) for k in [k for k in self._pending if k[0] == pack_handle]]
+        for layer, wait in unfinished:              # the worker threads must be done before the mapping goes away
+            wait(torch.cuda.current_stream(layer.gate.device))
         with self._cache.lock:
             for key in [k for k in self._cache.layers if k[0] == pack_handle]:
                 del self._cache.layers[key]

@@ -344,3 +344,132 @@ class TargetPackFile(_PackFile):
         if not 0 <= layer_index < layers:
             raise ContractError(f"TargetPack layer index must be in [0, {layers - 1}]")
         return self.header["policy"]["layer_encodings"][str(layer_index)]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The same two readers on the library's native pack reader (umaq_pack_open): one mapping made and checked in
+# C++, SHA-256 with the CPU's SHA extensions, tensors served as views into that mapping, and a layer staged
+# to the device by a worker thread through pinned chunks while the caller goes on.
+# ---------------------------------------------------------------------------------------------------------
+
+class _NativePackFile:
+    KIND_ID = 0
+    KIND = "ExpertPack"
+
+    def __init__(self, path: str | Path, **expected: Optional[str]) -> None:
+        import ctypes as C
+
+        from . import _native
+        self.path = Path(path)
+        self._lib = _native.lib()
+        self._handle = C.c_void_p()
+        text = lambda key: None if expected.get(key) is None else str(expected[key]).encode("utf-8")
+        code = self._lib.umaq_pack_open(str(self.path).encode("utf-8"), self.KIND_ID, text("expected_model_id"),
+                                        text("expected_model_revision"), text("expected_model_manifest_sha256"),
+                                        text("expected_policy_id"), C.byref(self._handle))
+        if code != 0:
+            self._handle = C.c_void_p()
+            raise ContractError(self._lib.umaq_last_error().decode("utf-8", "replace"))
+        self.mapping_count = 1
+        length = C.c_size_t()
+        raw = self._lib.umaq_pack_header_json(self._handle, C.byref(length))
+        self.header = json.loads(C.string_at(raw, length.value))
+        self._names = [entry["name"] for entry in self.header["tensors"]]
+        self._entries = {entry["name"]: entry for entry in self.header["tensors"]}
+
+    def _view(self, name: str):
+        import ctypes as C
+
+        from . import _native
+        if not self._handle:
+            raise ContractError(f"{self.KIND} is closed")
+        view = _native.PackTensor()
+        if self._lib.umaq_pack_tensor_view(self._handle, name.encode("utf-8"), C.byref(view)) != 0:
+            raise ContractError(self._lib.umaq_last_error().decode("utf-8", "replace"))
+        return view
+
+    def tensor_views(self, name: str) -> tuple[memoryview, memoryview, Mapping[str, Any]]:
+        """(data, scales, header entry): read-only views into the native mapping, valid until ``close``."""
+        import ctypes as C
+        view = self._view(name)
+        data = memoryview((C.c_ubyte * view.data_bytes).from_address(view.data)).cast("B").toreadonly()
+        scales = (memoryview((C.c_ubyte * view.scale_bytes).from_address(view.scales)).cast("B").toreadonly()
+                  if view.scale_bytes else memoryview(b""))
+        return data, scales, self._entries[name]
+
+    def names(self) -> list[str]:
+        return list(self._names)
+
+    def shapes(self) -> dict[str, tuple[int, ...]]:
+        return {name: tuple(entry["shape"]) for name, entry in self._entries.items()}
+
+    def layer_encoding(self, layer_index: int) -> str:
+        code = self._lib.umaq_pack_layer_encoding(self._handle, int(layer_index))
+        if code < 0:
+            raise ContractError(self._lib.umaq_last_error().decode("utf-8", "replace"))
+        return ("q4_group128", "q8_group128", "bf16_le")[code]
+
+    def stage_layer_async(self, layer_index: int, destination: Any, device: Any):
+        """Start copying layer ``layer_index`` into the device tensors of ``destination`` (a ``DeviceLayer`` of the
+        right encoding and shape).  Returns a callable: ``wait(stream) -> host seconds`` blocks until every copy has
+        been issued and makes ``stream`` wait for them."""
+        import ctypes as C
+
+        import torch
+        ticket = C.c_void_p()
+        index = torch.device(device).index or 0
+        code = self._lib.umaq_stage_layer_async(self._handle, int(layer_index), C.byref(destination.struct()), index,
+                                                C.byref(ticket))
+        if code != 0:
+            raise RuntimeError(self._lib.umaq_last_error().decode("utf-8", "replace"))
+
+        def wait(stream: Any = None) -> float:
+            seconds = C.c_double()
+            handle = (stream or torch.cuda.current_stream(device)).cuda_stream
+            if self._lib.umaq_stage_wait(ticket, C.c_void_p(handle), C.byref(seconds)) != 0:
+                raise RuntimeError(self._lib.umaq_last_error().decode("utf-8", "replace"))
+            return seconds.value
+        return wait
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            self._lib.umaq_pack_close(self._handle)
+            import ctypes as C
+            self._handle = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_: Any) -> None:
+        self.close()
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class NativeExpertPackFile(_NativePackFile):
+    """``UQMOEPK1`` through the native reader; same protocol and errors as :class:`ExpertPackFile`."""
+
+    KIND_ID, KIND = 0, "ExpertPack"
+
+    def __init__(self, path: str | Path, *, expected_model_id: Optional[str] = None,
+                 expected_model_revision: Optional[str] = None,
+                 expected_model_manifest_sha256: Optional[str] = None) -> None:
+        super().__init__(path, expected_model_id=expected_model_id, expected_model_revision=expected_model_revision,
+                         expected_model_manifest_sha256=expected_model_manifest_sha256)
+
+
+class NativeTargetPackFile(_NativePackFile):
+    """``UQMOTPK1`` through the native reader; same protocol and errors as :class:`TargetPackFile`."""
+
+    KIND_ID, KIND = 1, "TargetPack"
+
+    def __init__(self, path: str | Path, *, expected_model_id: Optional[str] = None,
+                 expected_model_revision: Optional[str] = None,
+                 expected_model_manifest_sha256: Optional[str] = None, expected_policy_id: Optional[str] = None) -> None:
+        super().__init__(path, expected_model_id=expected_model_id, expected_model_revision=expected_model_revision,
+                         expected_model_manifest_sha256=expected_model_manifest_sha256,
+                         expected_policy_id=expected_policy_id)
