@@ -190,6 +190,26 @@ def test_large_batch_prefill_matches_the_pair_kernel_and_the_oracle():
     assert_parity(y[sample], want)
 
 
+def test_bf16_large_batch_takes_the_pair_kernel_by_default_and_matches_the_one_cta_kernel():
+    """BF16 layers on 16,384 routes or more run on the CTA-pair kernel unless the caller picks one; the whole
+    operator must agree with the stages run explicitly on the one-CTA kernel and with the oracle on a sample."""
+    src = expert_source(SEED, 6, "olmoe", "bf16_le")
+    tokens, experts = 2048, 16
+    gen = torch.Generator().manual_seed(SEED + 78)
+    idx = torch.stack([torch.randperm(experts, generator=gen)[:8] for _ in range(tokens)])
+    w = torch.rand((tokens, 8), generator=gen, dtype=torch.float32) / 8
+    layer = stage_layer({e: src(e) for e in range(experts)}, experts, 2048, 1024, "bf16_le", DEV)
+    x = syn.activations(SEED + 35, tokens)
+    y = _run_prefill(layer, x, idx, w)                                        # 16,384 routes: variant 0 -> pairs
+    _, y1 = _stagewise(layer, x.to(DEV), idx.to(DEV), w.to(DEV), variant=1)
+    _, y2 = _stagewise(layer, x.to(DEV), idx.to(DEV), w.to(DEV), variant=2)
+    assert torch.equal(y, y2.cpu())
+    assert_parity(y, y1.cpu(), max_abs=4e-3)
+    sample = torch.arange(0, tokens, 256)
+    want = orc.moe_forward(x[sample], idx[sample], w[sample], src, num_experts=experts, top_k=8, qwen=False)
+    assert_parity(y[sample], want)
+
+
 def test_operator_edge_shapes_through_the_registered_backend():
     """The public operator on an empty batch, on one token (decode kernels) and on two tokens (prefill kernels):
     same pack, results consistent with each other."""

@@ -405,11 +405,16 @@ int launch_one(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap&
 
 }  // namespace
 
-// The CTA-pair kernel (grouped_pair.cu) runs only on request: measured on B200 it is slower than this
-// file's kernel for every encoding and size tried (its barrier hops between CTAs need a deeper pipeline
-// than shared memory holds).
+// Which kernel a caller gets that does not ask for one (variant 0), from measurements on B200.  Quantised
+// encodings: this file's kernel at every size (the CTA-pair kernel's barrier hops between two CTAs need a deeper
+// pipeline than shared memory holds next to the conversion ring: 0.66 against 0.48 ms for the OLMoE Q4 gate/up
+// GEMM at 8192 tokens).  BF16 weights need no conversion ring, and there the pair kernel, which drains one
+// accumulator while the next tile is multiplied, wins on large batches: Qwen shape, 8192 tokens, both GEMMs 0.510
+// against 0.530 ms; OLMoE shape 0.687 against 0.725 ms; at 128 tokens it loses 1.5 %.
+constexpr long long kPairMinRows = 16384;
 int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
-  return a.variant == 2 ? launch_grouped_gemm_pair(a, stream) : launch_grouped_gemm_single(a, stream);
+  const bool pair = a.variant == 2 || (a.variant == 0 && a.enc == ENC_BF16 && a.total_rows >= kPairMinRows);
+  return pair ? launch_grouped_gemm_pair(a, stream) : launch_grouped_gemm_single(a, stream);
 }
 
 int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {

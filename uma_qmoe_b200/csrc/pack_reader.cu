@@ -532,7 +532,7 @@ namespace {
 constexpr size_t kPrefixBytes = 96;
 constexpr size_t kPayloadAlignment = 4096;
 constexpr size_t kChunkBytes = 32u << 20;         // one pinned buffer
-constexpr int kCopyThreads = 4;
+constexpr int kCopyThreads = 8;
 const char* kQwenId = "Qwen/Qwen1.5-MoE-A2.7B";
 const char* kEncodingNames[3] = {"q4_group128", "q8_group128", "bf16_le"};
 
@@ -839,16 +839,28 @@ void open_checked(umaq_pack& pack, const char* path, const Expected& expected) {
 // ---------------------------------------------------------------------------------------------------
 // Staging: mapping -> pinned chunk (several threads) -> cudaMemcpyAsync on the pack's copy stream
 // ---------------------------------------------------------------------------------------------------
-void parallel_copy(uint8_t* dst, const uint8_t* src, size_t bytes) {
-  if (bytes < (4u << 20)) { std::memcpy(dst, src, bytes); return; }
-  std::thread helpers[kCopyThreads - 1];
-  const size_t piece = (bytes / kCopyThreads + 4095) / 4096 * 4096;
-  for (int i = 1; i < kCopyThreads; ++i) {
-    const size_t at = std::min(bytes, (size_t)i * piece), n = std::min(bytes - at, piece);
-    helpers[i - 1] = std::thread([=] { if (n) std::memcpy(dst + at, src + at, n); });
-  }
-  std::memcpy(dst, src, std::min(bytes, piece));
-  for (auto& t : helpers) t.join();
+struct Piece { const uint8_t* src; uint8_t* device_dst; size_t at; size_t bytes; };   // `at`: offset in the pinned buffer
+
+// Fills one pinned buffer from the mapping: the pieces are cut into runs of at most 1 MiB and the runs dealt to
+// the copy threads in turn (a layer's tensors are 64 KiB to a few MiB each, so no single piece is worth splitting
+// further and no thread is left with all the large ones).
+void fill_pinned(uint8_t* pinned, const std::vector<Piece>& pieces) {
+  struct Run { const uint8_t* src; uint8_t* dst; size_t bytes; };
+  std::vector<Run> runs;
+  size_t total = 0;
+  for (const Piece& p : pieces)
+    for (size_t done = 0; done < p.bytes; done += (1u << 20)) {
+      runs.push_back({p.src + done, pinned + p.at + done, std::min(p.bytes - done, (size_t)1 << 20)});
+      total += runs.back().bytes;
+    }
+  const int threads = total < (2u << 20) ? 1 : kCopyThreads;
+  auto work = [&runs, threads](int t) {
+    for (size_t i = t; i < runs.size(); i += threads) std::memcpy(runs[i].dst, runs[i].src, runs[i].bytes);
+  };
+  std::vector<std::thread> helpers;
+  for (int t = 1; t < threads; ++t) helpers.emplace_back(work, t);
+  work(0);
+  for (auto& h : helpers) h.join();
 }
 
 struct Span { const uint8_t* src; uint8_t* dst; size_t bytes; };
@@ -868,14 +880,16 @@ std::string stage_spans(umaq_pack& pack, const std::vector<Span>& spans, int dev
     if (!err.empty()) return err;
     pack.staging_device = device;
   }
-  // The spans are packed back to back into chunks of the pinned buffers; a chunk is one or more
-  // cudaMemcpyAsync calls (one per span piece, destinations differ), then an event.
+  // The spans are packed back to back into chunks of the pinned buffers.  A chunk is filled by the copy threads,
+  // then sent with one cudaMemcpyAsync per piece (the pieces' destinations differ) and closed with an event; while it
+  // travels the other buffer is filled.
   int buffer = 0;
   size_t fill = 0;
-  std::vector<std::tuple<uint8_t*, size_t, size_t>> pieces;      // (device dst, offset in the buffer, bytes)
+  std::vector<Piece> pieces;
   auto flush = [&]() -> std::string {
-    for (auto& [dst, at, n] : pieces) {
-      std::string e = cuda(cudaMemcpyAsync(dst, pack.pinned[buffer] + at, n, cudaMemcpyHostToDevice, pack.copy_stream), "cudaMemcpyAsync");
+    fill_pinned(pack.pinned[buffer], pieces);
+    for (const Piece& p : pieces) {
+      std::string e = cuda(cudaMemcpyAsync(p.device_dst, pack.pinned[buffer] + p.at, p.bytes, cudaMemcpyHostToDevice, pack.copy_stream), "cudaMemcpyAsync");
       if (!e.empty()) return e;
     }
     pieces.clear();
@@ -892,8 +906,7 @@ std::string stage_spans(umaq_pack& pack, const std::vector<Span>& spans, int dev
     size_t done = 0;
     while (done < s.bytes && err.empty()) {
       const size_t n = std::min(s.bytes - done, kChunkBytes - fill);
-      parallel_copy(pack.pinned[buffer] + fill, s.src + done, n);
-      pieces.emplace_back(s.dst + done, fill, n);
+      pieces.push_back({s.src + done, s.dst + done, fill, n});
       fill += (n + 255) / 256 * 256;
       done += n;
       if (fill + 256 > kChunkBytes) err = flush();
