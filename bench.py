@@ -776,6 +776,18 @@ def model_case(args, dev) -> None:
                    "graphed_tokens_equal_eager": more[0]["tokens"] == runs[0]["tokens"]}
     except Exception as exc:
         graphed = {"graphed": f"capture failed: {type(exc).__name__}: {exc}"[:300]}
+    # the MoE blocks alone (router, routed experts, shared expert and gate of every layer) on one token, replayed from a
+    # CUDA graph: their share of the time per generated token
+    h = torch.randn(1, 1, cfg.hidden_size, device=dev, dtype=torch.bfloat16)
+
+    @torch.no_grad()
+    def blocks_only():
+        for layer in model.model.layers:
+            layer.mlp(h)
+    moe_ms = timed(graphed(blocks_only), 20, 5, 1)
+    graphed["moe_blocks_ms_per_token"] = moe_ms
+    if "graphed_tpot_ms_p50" in graphed:
+        graphed["moe_share_of_graphed_tpot"] = moe_ms / graphed["graphed_tpot_ms_p50"]
     print(json.dumps({"case": "model", "layers": layers, "policy": "all q4_group128" if args.variant == 1 else
                       "layers 0-15 bf16_le, 16-23 q8_group128", "prompt_tokens": 128, "new_tokens": 32,
                       "ttft_ms": statistics.median(r["ttft_ms"] for r in runs), "tpot_ms_p50": statistics.median(tpot),

@@ -306,21 +306,33 @@ static int prefill_impl(const umaq_layer* layer, const umaq_shared_expert* share
   int rc = launch_route_sort(sa, stream);
   if (rc) return rc;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(at(pl.xs));
-  // routes with expert id -1 are absent: only the first offsets[E] sorted rows exist
-  rc = launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sa.sorted_route, top_k, routes, H, quant, xs,
-                          sa.offsets + E, stream);
-  if (rc) return rc;
-
   GroupedGemmArgs g{};
   g.mode = 0; g.enc = layer->encoding; g.num_experts = E; g.n_rows = I; g.k = H;
-  g.act = xs; g.total_rows = routes;
+  g.total_rows = routes;
   g.w0 = layer->gate; g.s0 = layer->gate_scales; g.w1 = layer->up; g.s1 = layer->up_scales;
   g.num_tiles = sa.num_tiles; g.tile_expert = sa.tile_expert; g.tile_row0 = sa.tile_row0; g.tile_rows = sa.tile_rows;
   g.max_tiles = pl.max_tiles;
   g.out = reinterpret_cast<__nv_bfloat16*>(at(pl.inter)); g.out_stride = I; g.permute_out = quant; g.status = status;
+  if (grouped_gemm_can_gather(g)) {
+    // The gate/up GEMM fetches its activation rows by index: no [routes, H] copy of the activations exists.  The
+    // quantised kernels want k in the order their conversion produces, so x is permuted once (tokens rows, not routes).
+    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(hidden_bf16);
+    if (quant) {
+      rc = launch_gather_rows(src, nullptr, 1, tokens, H, 1, xs, nullptr, stream);
+      if (rc) return rc;
+      src = xs;
+    }
+    g.act = src; g.gather_route = sa.sorted_route; g.gather_top_k = top_k;
+  } else {
+    // routes with expert id -1 are absent: only the first offsets[E] sorted rows exist
+    rc = launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden_bf16), sa.sorted_route, top_k, routes, H, quant, xs,
+                            sa.offsets + E, stream);
+    if (rc) return rc;
+    g.act = xs;
+  }
   rc = launch_grouped_gemm(g, stream);
   if (rc) return rc;
-  g.mode = 1; g.n_rows = H; g.k = I; g.act = g.out;
+  g.mode = 1; g.n_rows = H; g.k = I; g.act = g.out; g.gather_route = nullptr;
   g.w0 = layer->down; g.s0 = layer->down_scales; g.w1 = nullptr; g.s1 = nullptr;
   g.out = reinterpret_cast<__nv_bfloat16*>(at(pl.yw)); g.out_stride = H; g.route_weight = sa.sorted_weight; g.permute_out = 0;
   rc = launch_grouped_gemm(g, stream);

@@ -39,6 +39,9 @@ constexpr int kBStages = 2;           // converted B tiles (256 rows x 64 k)
 constexpr int kConvertWarps = 8;
 constexpr int kGemmThreads = (3 + kConvertWarps) * 32;   // + activation TMA, MMA issuer, weight TMA
 constexpr int kWeightWarp = 2 + kConvertWarps;
+constexpr int kGatherWarps = 4;       // launched only when the kernel fetches its activation rows by index
+constexpr int kGatherThreads = kGatherWarps * 32;
+constexpr int kGatherAhead = 2;       // a gather thread hands a stage over two steps after issuing it (< kInStages)
 constexpr int kHalves = 2;            // M = 128 accumulators per tile
 constexpr int kTmemCols = BN * kHalves;   // 512: the whole tensor memory of the SM
 constexpr int kMaxGroups = 16;        // quantised K <= 2048
@@ -60,6 +63,7 @@ struct GemmShared {
   uint64_t acc_empty;       // the epilogue has read the accumulators
   uint32_t tmem_base;
   int abort_flag;
+  int gather_token[2 * BM];   // gather mode: token of every row of the current tile
 };
 
 struct TileInfo {
@@ -71,7 +75,7 @@ struct TileInfo {
 // boundaries: while the eight conversion warps drain the accumulators of tile i, the activation and
 // packed-weight stages and the scales of tile i + 1 are already landing.
 template <int ENC, int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads + kGatherThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
                     const __grid_constant__ CUtensorMap map_b1, const GroupedParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -95,9 +99,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int total = *p.num_tiles * n_col;
   const int first = blockIdx.x, step = gridDim.x;
   volatile int* abort_flag = &sh.abort_flag;
+  // Gather mode (gate/up GEMM only): the activation tile of a stage is written by kGatherThreads threads with
+  // 16-byte cp.async copies, row by row from wherever the row's token lives, in the same swizzled layout the TMA
+  // produces; the stage's barrier then counts those threads (plus the TMA warp for a BF16 weight tile).
+  const bool gather = MODE == 0 && p.gather_route != nullptr;
 
   if (tid == 0) {
-    for (int s = 0; s < kInStages; ++s) { mbar_init(&sh.in_full[s], 1); mbar_init(&sh.in_empty[s], 1); }
+    const uint32_t in_count = gather ? kGatherThreads + (ENC == ENC_BF16 ? 1 : 0) : 1;
+    for (int s = 0; s < kInStages; ++s) { mbar_init(&sh.in_full[s], in_count); mbar_init(&sh.in_empty[s], 1); }
     for (int s = 0; s < kMaxPStages; ++s) { mbar_init(&sh.p_full[s], 1); mbar_init(&sh.p_empty[s], kConvertWarps); }
     for (int s = 0; s < kBStages; ++s) { mbar_init(&sh.b_full[s], kConvertWarps); mbar_init(&sh.b_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&sh.sc_full[s], 1); mbar_init(&sh.sc_empty[s], kConvertWarps); }
@@ -131,7 +140,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     // ===================== TMA producer: activation tiles (and BF16 weight tiles) ==================
-    if (lane == 0) {
+    if (lane == 0 && !(gather && ENC != ENC_BF16)) {
       uint32_t kidx = 0;
       int inflight_from = 0;
       for (int it = first; it < total && !*abort_flag; it += step) {
@@ -142,10 +151,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kc = 0; kc < nk; ++kc, ++kidx) {
           const uint32_t s = kidx % kInStages, use = kidx / kInStages;
           if (use > 0 && !mbar_wait(&sh.in_empty[s], (use - 1) & 1)) { ok = false; break; }
-          const uint32_t bytes = (two ? kATile : kAHalf) + (ENC == ENC_BF16 ? kBTile : 0);
+          const uint32_t bytes = (gather ? 0 : (two ? kATile : kAHalf)) + (ENC == ENC_BF16 ? kBTile : 0);
           mbar_expect_tx(&sh.in_full[s], bytes);
-          tma_load_2d(sA + s * kATile, &map_a, kc * BK, t.row0, &sh.in_full[s]);
-          if (two) tma_load_2d(sA + s * kATile + kAHalf, &map_a, kc * BK, t.row0 + BM, &sh.in_full[s]);
+          if (!gather) {
+            tma_load_2d(sA + s * kATile, &map_a, kc * BK, t.row0, &sh.in_full[s]);
+            if (two) tma_load_2d(sA + s * kATile + kAHalf, &map_a, kc * BK, t.row0 + BM, &sh.in_full[s]);
+          }
           if (ENC == ENC_BF16) {
             uint8_t* dst = sB + s * kBTile;
             if (MODE == 0) {
@@ -200,6 +211,61 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (uint32_t k2 = from; k2 < kidx; ++k2) mbar_wait(&sh.p_full[k2 % kPStages], (k2 / kPStages) & 1);
       }
     }
+  } else if (warp > kWeightWarp) {
+    // ===================== gather producers: 128 threads write every activation tile =========================
+    // A row of a stage is 64 k = 128 bytes = eight 16-byte chunks; chunk c of row r lands at r * 128 +
+    // ((c ^ (r & 7)) << 4), the 128-byte swizzle the MMA descriptors expect.  Thread j copies chunk j & 7 of
+    // rows (j >> 3) + 16 i: eight neighbouring lanes read one row's 128 contiguous bytes, so every copy
+    // instruction of a warp covers four whole lines.  Rows past the tile's end are zero-filled.  cp.async writes
+    // go through the generic proxy: a thread waits for its own copies of a stage (the younger stages stay in
+    // flight), fences them towards the async proxy and arrives.
+    const int pt = tid - (kWeightWarp + 1) * 32;          // 0 .. 127
+    const int c = pt & 7, rbase = pt >> 3;                // rows rbase, rbase + 16, ...: all have r & 7 == rbase & 7
+    const uint32_t dst_off = (uint32_t)rbase * 128 + (uint32_t)((c ^ (rbase & 7)) << 4);
+    uint32_t kidx = 0, published = 0;
+    bool ok = true;
+    auto publish = [&]() {
+      fence_proxy_async();
+      mbar_arrive(&sh.in_full[published % kInStages]);
+      ++published;
+    };
+    for (int it = first; it < total; it += step) {
+      // Everybody has read the previous tile's table; and the threads agree whether to go on (a thread that gave up
+      // on a wait, or saw the abort flag, must not leave the others waiting at this barrier).
+      if (named_bar_or(1, kGatherThreads, !ok || *abort_flag != 0)) break;
+      const TileInfo t = tile_of(it);
+      const bool two = t.nrows > BM;
+      // the tile's token of every row, shared by the gather threads (-1: no such row)
+      sh.gather_token[pt] = pt < t.nrows ? p.gather_route[t.row0 + pt] / p.gather_top_k : -1;
+      sh.gather_token[pt + BM] = pt + BM < t.nrows ? p.gather_route[t.row0 + BM + pt] / p.gather_top_k : -1;
+      named_bar_sync(1, kGatherThreads);
+      int tok[2 * BM / 16];
+#pragma unroll
+      for (int i = 0; i < 2 * BM / 16; ++i) tok[i] = sh.gather_token[rbase + 16 * i];
+      const uint8_t* base = reinterpret_cast<const uint8_t*>(p.gather_src) + c * 16;
+      for (int kc = 0; kc < nk; ++kc, ++kidx) {
+        // first hand over the stage issued two steps ago (its copies have had two steps to land), so that the
+        // MMA issuer never waits for this thread's wait on a free slot below
+        if (kidx >= (uint32_t)kGatherAhead) { cp_async_wait<kGatherAhead - 1>(); publish(); }
+        const uint32_t s = kidx % kInStages, use = kidx / kInStages;
+        if (use > 0 && !mbar_wait(&sh.in_empty[s], (use - 1) & 1)) { ok = false; break; }
+        uint8_t* dst = sA + s * kATile + dst_off;
+        const uint8_t* col = base + kc * 128;
+#pragma unroll
+        for (int i = 0; i < BM / 16; ++i)
+          cp_async16(dst + i * 2048, col + (size_t)(tok[i] < 0 ? 0 : tok[i]) * K * 2, tok[i] >= 0);
+        if (two) {
+#pragma unroll
+          for (int i = BM / 16; i < 2 * BM / 16; ++i)
+            cp_async16(dst + i * 2048, col + (size_t)(tok[i] < 0 ? 0 : tok[i]) * K * 2, tok[i] >= 0);
+        }
+        cp_async_commit();
+      }
+    }
+    if (!ok && lane == 0) fail();
+    cp_async_wait<0>();                                  // also on the abort path: nothing of this thread stays in flight
+    if (ok && !*abort_flag)
+      while (published < kidx) publish();
   } else if (warp == 1) {
     // ===================== MMA issuer ============================================================
     if (lane == 0) {
@@ -397,7 +463,7 @@ int launch_one(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap&
     configured = dev;
   }
   (void)n_tiles;
-  kernel<<<dim3(sm_count()), kGemmThreads, smem, stream>>>(ma, mb0, mb1, p);
+  kernel<<<dim3(sm_count()), kGemmThreads + (MODE == 0 && p.gather_route ? kGatherThreads : 0), smem, stream>>>(ma, mb0, mb1, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("grouped: launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
   return ERR_NONE;
@@ -412,9 +478,16 @@ int launch_one(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap&
 // accumulator while the next tile is multiplied, wins on large batches: Qwen shape, 8192 tokens, both GEMMs 0.510
 // against 0.530 ms; OLMoE shape 0.687 against 0.725 ms; at 128 tokens it loses 1.5 %.
 constexpr long long kPairMinRows = 16384;
+static bool takes_pair_kernel(const GroupedGemmArgs& a) {
+  return a.variant == 2 || (a.variant == 0 && a.enc == ENC_BF16 && a.total_rows >= kPairMinRows);
+}
+bool grouped_gemm_can_gather(const GroupedGemmArgs& a) { return a.mode == 0 && !takes_pair_kernel(a); }
 int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream) {
-  const bool pair = a.variant == 2 || (a.variant == 0 && a.enc == ENC_BF16 && a.total_rows >= kPairMinRows);
-  return pair ? launch_grouped_gemm_pair(a, stream) : launch_grouped_gemm_single(a, stream);
+  if (takes_pair_kernel(a)) {
+    if (a.gather_route) { set_error("grouped: the CTA-pair kernel takes gathered activation rows"); return ERR_BAD_ARGUMENT; }
+    return launch_grouped_gemm_pair(a, stream);
+  }
+  return launch_grouped_gemm_single(a, stream);
 }
 
 int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
@@ -424,8 +497,10 @@ int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
     set_error("grouped: unsupported shape (k %d, rows per expert %d)", K, a.n_rows);
     return ERR_BAD_ARGUMENT;
   }
+  if (a.gather_route && (a.mode != 0 || a.gather_top_k < 1)) { set_error("grouped: rows are fetched by index only for the gate/up GEMM"); return ERR_BAD_ARGUMENT; }
+  // with rows fetched by index `act` is [tokens, k] and the kernel never uses the activation map: any valid map will do
   CUtensorMap ma, mb0, mb1;
-  if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.act, (uint64_t)K, (uint64_t)a.total_rows, BK, BM,
+  if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.act, (uint64_t)K, (uint64_t)(a.gather_route ? BM : a.total_rows), BK, BM,
                 CU_TENSOR_MAP_SWIZZLE_128B))
     return ERR_LAUNCH;
   const uint64_t wrows = (uint64_t)a.num_experts * a.n_rows;
@@ -450,6 +525,7 @@ int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
   p.max_tiles = a.max_tiles;
   p.out = a.out; p.out_stride = a.out_stride; p.route_weight = a.route_weight; p.permute_out = a.permute_out;
   p.status = a.status;
+  p.gather_route = a.gather_route; p.gather_top_k = a.gather_top_k; p.gather_src = static_cast<const __nv_bfloat16*>(a.act);
   const int n_tiles = a.n_rows / (a.mode == 0 ? BN / 2 : BN);
 #define UMAQ_DISPATCH(E)                                                                       \
   return a.mode == 0 ? launch_one<E, 0>(p, ma, mb0, mb1, n_tiles, stream) : launch_one<E, 1>(p, ma, mb0, mb1, n_tiles, stream)

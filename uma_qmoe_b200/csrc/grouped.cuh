@@ -25,6 +25,11 @@ struct GroupedParams {
   const float* route_weight;  // mode 1: routing weight per sorted route
   int permute_out;            // mode 0: write the [k0,k4,k1,k5,k2,k6,k3,k7] order a quantised GEMM 2 expects
   unsigned* status;           // sticky error word
+  // mode 0, optional: fetch the activation rows by index instead of reading pre-gathered rows.  Sorted route r
+  // is row gather_route[r] / gather_top_k of gather_src ([tokens, k] BF16, k already in the order the encoding wants)
+  const int* gather_route;
+  int gather_top_k;
+  const __nv_bfloat16* gather_src;
 };
 
 struct GroupedGemmArgs {
@@ -44,7 +49,14 @@ struct GroupedGemmArgs {
   int permute_out;
   unsigned* status;
   int variant;                // 0: by size; 1: one CTA per tile (grouped.cu); 2: persistent CTA pairs (grouped_pair.cu)
+  // mode 0 on the one-CTA kernel, optional: act = [tokens, k] and the kernel fetches row sorted_route[r] / top_k
+  // for sorted route r itself (no gathered copy of the activations)
+  const int* gather_route;
+  int gather_top_k;
 };
+
+// true if launch_grouped_gemm would run the kernel that can fetch its activation rows by index
+bool grouped_gemm_can_gather(const GroupedGemmArgs& a);
 
 int launch_grouped_gemm(const GroupedGemmArgs& a, cudaStream_t stream);        // picks the variant
 int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream);

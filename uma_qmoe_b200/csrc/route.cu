@@ -288,11 +288,6 @@ constexpr int kRmTokens = 64, kRmChunk = 128, kRmStages = 6;
 constexpr int kRmTile = 64 * kRmChunk * 2;                 // 16 KiB: 64 rows x 256 bytes
 constexpr int kRmSmem = kRmStages * 2 * kRmTile;
 
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-  const uint32_t d = smem_u32(dst);
-  const int bytes = valid ? 16 : 0;                        // 0 source bytes: the 16 destination bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)

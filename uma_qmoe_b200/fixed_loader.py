@@ -34,7 +34,7 @@ import torch
 from . import custom_op, native_backend
 from .blocks import QuantizedMoEBlock, QuantizedQwenMoEBlock
 from .formats import ContractError
-from .pack_files import ExpertPackFile, TargetPackFile
+from .pack_files import ExpertPackFile, NativeExpertPackFile, NativeTargetPackFile, TargetPackFile
 
 _EXPERT_TENSOR = re.compile(r"^model\.layers\.(\d+)\.mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
 
@@ -86,7 +86,7 @@ def is_expert_tensor_name(name: str) -> bool:
     return _EXPERT_TENSOR.fullmatch(name) is not None
 
 
-def _open_pack(spec: FixedModel, path: Path, manifest: str, policy_id: Optional[str]):
+def _open_pack(spec: FixedModel, path: Path, manifest: str, policy_id: Optional[str], native: bool):
     try:
         with path.open("rb") as stream:
             magic = stream.read(8)
@@ -97,10 +97,10 @@ def _open_pack(spec: FixedModel, path: Path, manifest: str, policy_id: Optional[
     if magic == TargetPackFile.MAGIC:
         if not policy_id:
             raise ContractError(f"{spec.label} TargetPack loading requires a policy id")
-        return TargetPackFile(path, expected_policy_id=policy_id, **identity)
+        return (NativeTargetPackFile if native else TargetPackFile)(path, expected_policy_id=policy_id, **identity)
     if policy_id is not None:
         raise ContractError(f"{spec.label} ExpertPack cannot satisfy a TargetPack policy id")
-    return ExpertPackFile(path, **identity)
+    return (NativeExpertPackFile if native else ExpertPackFile)(path, **identity)
 
 
 def _require_every_expert(spec: FixedModel, reader: Any, layers: int) -> None:
@@ -182,7 +182,8 @@ def _load_dense(spec: FixedModel, model: Any, root: Path, device: str, layers: i
 
 
 def _load_fixed(spec: FixedModel, model_directory: str | Path, expert_pack_path: str | Path, *, model_manifest_sha256: str,
-                device: str, performance_mode: bool, target_policy_id: Optional[str], expected_layers: Optional[int]) -> FixedHost:
+                device: str, performance_mode: bool, target_policy_id: Optional[str], expected_layers: Optional[int],
+                native_reader: bool) -> FixedHost:
     from transformers import AutoConfig, AutoModelForCausalLM
 
     root, pack_path = Path(model_directory), Path(expert_pack_path)
@@ -194,7 +195,7 @@ def _load_fixed(spec: FixedModel, model_directory: str | Path, expert_pack_path:
                 getattr(config, "num_experts", None), getattr(config, "num_experts_per_tok", None))
     if observed != (spec.model_type, layers, spec.experts, spec.top_k):
         raise ContractError(f"unexpected fixed {spec.label} architecture {observed!r}")
-    reader = _open_pack(spec, pack_path, model_manifest_sha256, target_policy_id)
+    reader = _open_pack(spec, pack_path, model_manifest_sha256, target_policy_id, native_reader)
     try:
         _require_every_expert(spec, reader, layers)
         native_backend.install_mixed_target_backend() if performance_mode else custom_op.register_moe_forward()
@@ -245,20 +246,22 @@ def _load_fixed(spec: FixedModel, model_directory: str | Path, expert_pack_path:
 
 def load_fixed_qwen(model_directory: str | Path, expert_pack_path: str | Path, *, model_manifest_sha256: str,
                     device: str = "cuda:0", performance_mode: bool = False, target_policy_id: Optional[str] = None,
-                    expected_layers: Optional[int] = None) -> FixedHost:
-    """Dense Qwen1.5-MoE BF16 tensors plus one pack mapping; the routed experts run through ``torch.ops.uma_qmoe``."""
+                    expected_layers: Optional[int] = None, native_reader: bool = True) -> FixedHost:
+    """Dense Qwen1.5-MoE BF16 tensors plus one pack mapping; the routed experts run through ``torch.ops.uma_qmoe``.
+    ``native_reader``: open the pack with the library's C++ reader (layers are then staged asynchronously) instead of
+    the Python one; both apply the same checks."""
     return _load_fixed(QWEN1_5_MOE, model_directory, expert_pack_path, model_manifest_sha256=model_manifest_sha256,
                        device=device, performance_mode=performance_mode, target_policy_id=target_policy_id,
-                       expected_layers=expected_layers)
+                       expected_layers=expected_layers, native_reader=native_reader)
 
 
 def load_fixed_olmoe(model_directory: str | Path, expert_pack_path: str | Path, *, model_manifest_sha256: str,
                      device: str = "cuda:0", performance_mode: bool = False, target_policy_id: Optional[str] = None,
-                     expected_layers: Optional[int] = None) -> FixedHost:
+                     expected_layers: Optional[int] = None, native_reader: bool = True) -> FixedHost:
     """Dense OLMoE BF16 tensors plus one pack mapping."""
     return _load_fixed(OLMOE, model_directory, expert_pack_path, model_manifest_sha256=model_manifest_sha256,
                        device=device, performance_mode=performance_mode, target_policy_id=target_policy_id,
-                       expected_layers=expected_layers)
+                       expected_layers=expected_layers, native_reader=native_reader)
 
 
 __all__ = ["FixedHost", "FixedOlmoeHost", "FixedQwenHost", "OLMOE", "QWEN1_5_MOE", "is_expert_tensor_name",
