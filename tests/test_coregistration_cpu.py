@@ -18,7 +18,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _reference_src() -> Path | None:
-    for candidate in (os.environ.get("UMA_QMOE_REFERENCE"), "/root/reference", str(ROOT / "oracle" / "_ref")):
+    for candidate in (os.environ.get("UMA_QMOE_REFERENCE"), str(ROOT.parent / "reference"), str(ROOT / "oracle" / "_ref")):
         if not candidate:
             continue
         for src in (Path(candidate) / "src", Path(candidate)):
