@@ -1004,10 +1004,6 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
     const DecodeKind& K0 = P.kind[0];
     const uint32_t wbytes = (uint32_t)npairs * 2 * K0.row_bytes, sbytes = fast ? 0u : (uint32_t)npairs * 2 * K0.groups * 4;
     if (tid == 0) mbar_expect_tx(full, K0.nvs * (((p.debug & 2) ? 0u : wbytes) + sbytes));
-    if (p.down_delay_ns > 0 && warp < K0.nvs) {      // let the gate/up kernel's own loads go first
-      const uint64_t t0 = global_ns();
-      while (global_ns() - t0 < (uint64_t)p.down_delay_ns) __nanosleep(100);
-    }
     if (warp < K0.nvs && lane < 2) {
       const size_t row = (size_t)s_expert[warp] * H + 2 * rp0;
       if (lane == 0 && !(p.debug & 2)) bulk_g2s(smem + warp * K0.mstride, p.down + row * K0.row_bytes, wbytes, full);
@@ -1030,10 +1026,6 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
 
   if (!consumer) {
     // ---- producer ----------------------------------------------------------------------------------------------
-    if (p.down_delay_ns > 0 && !P.resident) {                 // lets the gate/up kernel's own loads go first
-      const uint64_t t0 = global_ns();
-      while (global_ns() - t0 < (uint64_t)p.down_delay_ns) __nanosleep(200);
-    }
     const DecodeKind& K0 = P.kind[0];
     const int pj = warp - ncons;
     if (P.resident) {
@@ -1378,14 +1370,6 @@ bool plan_both(DecodeParams& p, int sms) {
   return plan_gateup(p, sms, kPairSmemBudget - align_up(p.d.smem_bytes, 1024));
 }
 
-int down_delay_from_env() {
-  static const int value = [] {
-    const char* s = std::getenv("UMAQ_DECODE_DOWN_DELAY_NS");
-    return s ? std::max(0, std::atoi(s)) : 0;
-  }();
-  return value;
-}
-
 int debug_from_env() {
   static const int value = [] {
     const char* s = std::getenv("UMAQ_DECODE_DEBUG");
@@ -1432,7 +1416,6 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
               "encoding %d)", p.hidden, p.inter, p.top_k, p.shared_inter, p.enc);
     return ERR_UNSUPPORTED;
   }
-  p.down_delay_ns = down_delay_from_env();
   p.debug = debug_from_env();
   static thread_local int configured_device = -1;
   int dev = 0;

@@ -92,7 +92,6 @@ struct DecodeParams {
   // launch plans, filled by launch_moe_decode
   DecodeKernelPlan g;         // gate/up + SwiGLU kernel
   DecodeKernelPlan d;         // down + combine kernel
-  int down_delay_ns;          // the down kernel's producer waits this long before its first copy
   int debug;                  // measurement switches: 1 = consumers skip the arithmetic, 2 = producers skip the weight
                               // copies, 4 = CTA 0 writes %globaltimer stamps into the header (bytes 128 and up)
 };
