@@ -52,11 +52,16 @@ CAPTURES = {
 }
 
 
-def gemm_traffic(name: str, tokens: int) -> int:
-    """DRAM bytes of one grouped-GEMM launch on `tokens` tokens, from the capture of that kernel."""
+def gemm_traffic(name: str, tokens: int, by_index: bool = False) -> int:
+    """DRAM bytes of one grouped-GEMM launch on `tokens` tokens, from the capture of that kernel.  `by_index`: the
+    launch reads its activation rows from the [tokens, H] input (each row once from DRAM, re-reads from L2) instead
+    of the [routes, H] gathered copy the capture was made on."""
     c = CAPTURES[name]
     grow = tokens / c["tokens"]
-    return int(c["weights"] + (c["read"] - c["weights"]) * grow + c["write"] * grow)
+    activations = (c["read"] - c["weights"]) * grow
+    if by_index:
+        activations = min(activations, tokens * 2048 * 2)
+    return int(c["weights"] + activations + c["write"] * grow)
 
 
 def peaks() -> tuple[dict, str]:
@@ -351,9 +356,10 @@ def native_arm(args) -> None:
 
     # The batch-1 decode legs come first: a call is a few microseconds, and right after the long tensor-bound legs
     # the same kernels measured 10 % slower.
-    decode_objects, decode_launches = {}, 0
+    decode_objects, decode_launches, kernel_objects = {}, 0, {}
     if rank == 0 and world == 1 and args.legs == "all":
         decode_objects, decode_launches = decode_legs(stack, x_dev, shape, dev)
+        kernel_objects = kernel_legs(stack, x_dev, shape, dev)
 
     with ClockSampler(local) as clocks:
         ms = timed(step_resident, args.steps, args.warmup, world)
@@ -372,38 +378,7 @@ def native_arm(args) -> None:
             "tflops_step": 65536 * 12_582_912 * LAYERS / (ms / 1e3) / 1e12 / world}
 
     if rank == 0 and world == 1 and args.legs == "all":
-        # ---- roofline of the dominant kernel (the gate/up grouped GEMM of layer 0) and of the down GEMM ----
-        w, idx = stack.route(0, x_dev)
-        routes = ops.route_sort(idx, w, shape.experts)
-        xs = ops.gather_rows(x_dev, routes.sorted_route, shape.top_k, permute=True)
-        inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
-        yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
-        def cold(fn):
-            times = []
-            for i in range(3 + 10):
-                flush.zero_()                                        # weights leave L2 between launches
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(); fn(); b.record()
-                torch.cuda.synchronize()
-                if i >= 3:
-                    times.append(a.elapsed_time(b))
-            return statistics.mean(times)
-        gemm_ms = cold(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter))
-        down_ms = cold(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw))
-        flops = 2.0 * xs.shape[0] * shape.hidden * 2 * shape.intermediate
-
-        def tensor_roofline(kernel, fl, ms_, capture):
-            return {"bound": "tensor", "kernel": kernel, "achieved": fl / (ms_ / 1e3) / 1e12, "peak": pk["bf16_tflops"],
-                    "unit": "TFLOP/s", "frac": fl / (ms_ / 1e3) / 1e12 / pk["bf16_tflops"],
-                    "traffic": gemm_traffic(capture, TOKENS), "traffic_source": f"ncu capture at {CAPTURES[capture]['tokens']} tokens, "
-                    "scaled by routes (weights fixed)", "peak_source": f"{pk_kind} (burst)", "ms_per_launch": ms_,
-                    "flops_per_launch": fl}
-        line["roofline"] = tensor_roofline("grouped_gemm_kernel<Q4, gate/up+SwiGLU>", flops, gemm_ms, "gemm_gate_up")
-        line["roofline_down"] = tensor_roofline("grouped_gemm_kernel<Q4, down x route weight>", flops / 2, down_ms, "gemm_down")
-        line["kernels_us"] = prefill_kernel_times(stack, x_dev, shape, dev)
-        del xs, inter, yw, flush
+        line.update(kernel_objects)
         line.update(decode_objects)
         line["gpu_launches"] += 26 + decode_launches              # the roofline legs and the decode legs
         line["cpu_baseline"] = cpu_baseline_subprocess()
@@ -417,6 +392,54 @@ def native_arm(args) -> None:
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
+
+
+def kernel_legs(stack, x_dev, shape, dev) -> dict:
+    """The two grouped GEMMs of layer 0 timed alone (CUDA events around single launches, a 256 MB write between them so
+    that the weights come from HBM) against the burst tensor peak, and every kernel of a layer in graphs of eight
+    launches.  Run before the long timed region: the peak they are compared with is a burst figure, and after seconds
+    at the power cap the same launches take 8 % longer."""
+    from uma_qmoe_b200 import ops
+    pk, pk_kind = peaks()
+    out = {}
+    # ---- roofline of the dominant kernel (the gate/up grouped GEMM of layer 0) and of the down GEMM ----
+    w, idx = stack.route(0, x_dev)
+    routes = ops.route_sort(idx, w, shape.experts)
+    xs = ops.gather_rows(x_dev, routes.sorted_route, shape.top_k, permute=True)
+    inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
+    yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def cold(fn):
+        times = []
+        for i in range(3 + 10):
+            flush.zero_()                                        # weights leave L2 between launches
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        return statistics.mean(times)
+    x_perm = ops.gather_rows(x_dev, None, 1, permute=True)        # k order of the quantised kernels, [tokens, H]
+    # the gate/up GEMM as the step runs it: activation rows fetched by index, no gathered copy
+    gemm_ms = cold(lambda: ops.grouped_gemm_by_index(stack.layers[0], x_perm, routes, shape.top_k, permute_out=True, out=inter))
+    gathered_ms = cold(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=True, out=inter))
+    down_ms = cold(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw))
+    flops = 2.0 * xs.shape[0] * shape.hidden * 2 * shape.intermediate
+
+    def tensor_roofline(kernel, fl, ms_, capture):
+        return {"bound": "tensor", "kernel": kernel, "achieved": fl / (ms_ / 1e3) / 1e12, "peak": pk["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": fl / (ms_ / 1e3) / 1e12 / pk["bf16_tflops"],
+                "traffic": gemm_traffic(capture, TOKENS, by_index=capture == "gemm_gate_up"),
+                "traffic_source": f"ncu capture at {CAPTURES[capture]['tokens']} tokens, scaled by routes (weights fixed"
+                + ("; activations read once per token, not per route)" if capture == "gemm_gate_up" else ")"), "peak_source": f"{pk_kind} (burst)", "ms_per_launch": ms_,
+                "flops_per_launch": fl}
+    out["roofline"] = tensor_roofline("grouped_gemm_kernel<Q4, gate/up+SwiGLU>, rows fetched by index", flops, gemm_ms, "gemm_gate_up")
+    out["roofline"]["ms_per_launch_on_gathered_rows"] = gathered_ms
+    out["roofline_down"] = tensor_roofline("grouped_gemm_kernel<Q4, down x route weight>", flops / 2, down_ms, "gemm_down")
+    out["kernels_us"] = prefill_kernel_times(stack, x_dev, shape, dev)
+    del xs, inter, yw, flush, x_perm
+    return out
 
 
 def decode_legs(stack, x_dev, shape, dev) -> tuple[dict, int]:
@@ -494,13 +517,16 @@ def prefill_kernel_times(stack, x, shape, dev) -> dict:
     w, idx = stack.route(0, x)
     routes = ops.route_sort(idx, w, shape.experts)
     xs = ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)
+    x_perm = ops.gather_rows(x, None, 1, permute=True)
     inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
     yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
     ws = ops.prefill_workspace(layer, x.shape[0], shape.top_k, None, dev)
     phases = [("router", lambda: stack.route(0, x)),
               ("route_sort", lambda: ops.route_sort(idx, w, shape.experts)),
-              ("gather_rows", lambda: ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)),
-              ("gemm_gate_up", lambda: ops.grouped_gemm(layer, 0, xs, routes, permute_out=True, out=inter)),
+              ("permute_k", lambda: ops.gather_rows(x, None, 1, permute=True)),
+              ("gemm_gate_up", lambda: ops.grouped_gemm_by_index(layer, x_perm, routes, shape.top_k, permute_out=True, out=inter)),
+              ("gather_rows_not_on_the_path", lambda: ops.gather_rows(x, routes.sorted_route, shape.top_k, permute=True)),
+              ("gemm_gate_up_on_gathered_rows", lambda: ops.grouped_gemm(layer, 0, xs, routes, permute_out=True, out=inter)),
               ("gemm_down", lambda: ops.grouped_gemm(layer, 1, inter, routes, route_weight=routes.sorted_weight, out=yw)),
               ("combine", lambda: ops.combine_routes(yw, idx, routes.route_pos)),
               ("rms_norm", lambda: rms_renorm(x)),
@@ -765,17 +791,17 @@ def model_case(args, dev) -> None:
     greedy_decode(model, prompt, 4)                                  # warm-up: workspaces, autotuned attention
     runs = [greedy_decode(model, prompt, 32) for _ in range(3)]
     tpot = sorted(t for r in runs for t in r["tpot_ms"])
-    graphed = {}
+    graph_stats = {}
     try:                                            # the same loop with the decode step replayed from a CUDA graph
         first = greedy_decode_graphed(model, prompt, 32)
         more = [greedy_decode_graphed(model, prompt, 32, decoder=first["decoder"]) for _ in range(3)]
         gt = sorted(t for r in more for t in r["tpot_ms"])
-        graphed = {"graphed_tpot_ms_p50": statistics.median(gt), "graphed_tpot_ms_p95": gt[int(0.95 * (len(gt) - 1))],
+        graph_stats = {"graphed_tpot_ms_p50": statistics.median(gt), "graphed_tpot_ms_p95": gt[int(0.95 * (len(gt) - 1))],
                    "graphed_decode_tokens_per_s": 1e3 / statistics.median(gt),
                    "graphed_ttft_ms": statistics.median(r["ttft_ms"] for r in more),
                    "graphed_tokens_equal_eager": more[0]["tokens"] == runs[0]["tokens"]}
     except Exception as exc:
-        graphed = {"graphed": f"capture failed: {type(exc).__name__}: {exc}"[:300]}
+        graph_stats = {"graphed": f"capture failed: {type(exc).__name__}: {exc}"[:300]}
     # the MoE blocks alone (router, routed experts, shared expert and gate of every layer) on one token, replayed from a
     # CUDA graph: their share of the time per generated token
     h = torch.randn(1, 1, cfg.hidden_size, device=dev, dtype=torch.bfloat16)
@@ -785,15 +811,15 @@ def model_case(args, dev) -> None:
         for layer in model.model.layers:
             layer.mlp(h)
     moe_ms = timed(graphed(blocks_only), 20, 5, 1)
-    graphed["moe_blocks_ms_per_token"] = moe_ms
-    if "graphed_tpot_ms_p50" in graphed:
-        graphed["moe_share_of_graphed_tpot"] = moe_ms / graphed["graphed_tpot_ms_p50"]
+    graph_stats["moe_blocks_ms_per_token"] = moe_ms
+    if "graphed_tpot_ms_p50" in graph_stats:
+        graph_stats["moe_share_of_graphed_tpot"] = moe_ms / graph_stats["graphed_tpot_ms_p50"]
     print(json.dumps({"case": "model", "layers": layers, "policy": "all q4_group128" if args.variant == 1 else
                       "layers 0-15 bf16_le, 16-23 q8_group128", "prompt_tokens": 128, "new_tokens": 32,
                       "ttft_ms": statistics.median(r["ttft_ms"] for r in runs), "tpot_ms_p50": statistics.median(tpot),
                       "tpot_ms_p95": tpot[int(0.95 * (len(tpot) - 1))], "decode_tokens_per_s": 1e3 / statistics.median(tpot),
                       "expert_storage_bytes": host.evidence["expert_storage_bytes"],
-                      "tokens_equal_across_runs": all(r["tokens"] == runs[0]["tokens"] for r in runs), **graphed}))
+                      "tokens_equal_across_runs": all(r["tokens"] == runs[0]["tokens"] for r in runs), **graph_stats}))
     host.close()
 
 

@@ -197,6 +197,12 @@ int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k
 int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows,
                       const int* num_tiles, const int* tile_table, int max_tiles, const float* route_weight,
                       int permute_out, void* out_bf16, unsigned* status, int variant, void* stream);
+/* The gate/up GEMM (mode 0) as umaq_moe_prefill runs it on the one-CTA kernel: no gathered copy of the
+ * activations; sorted route r reads row sorted_route[r] / top_k of hidden_bf16 ([tokens, H]; for a quantised
+ * layer already in the permuted k order, i.e. umaq_gather_rows with sorted_route NULL and permute != 0). */
+int umaq_grouped_gemm_by_index(const umaq_layer* layer, const void* hidden_bf16, const int* sorted_route, int top_k,
+                               long long routes, const int* num_tiles, const int* tile_table, int max_tiles,
+                               int permute_out, void* out_bf16, unsigned* status, void* stream);
 /* Expert-parallel routing table (no counterpart in the reference): local_ids[i] = local expert id of
  * expert_indices[i] on rank `rank`, or -1 (absent route) when another rank owns the expert.
  * placement 0: expert e on rank e % ranks as local e / ranks; 1: rank e / experts_per_rank, local e % experts_per_rank. */

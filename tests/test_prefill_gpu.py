@@ -190,6 +190,31 @@ def test_large_batch_prefill_matches_the_pair_kernel_and_the_oracle():
     assert_parity(y[sample], want)
 
 
+@pytest.mark.parametrize("encoding", ["q4_group128", "q8_group128", "bf16_le"])
+def test_gate_up_gemm_by_index_equals_the_gemm_on_gathered_rows(encoding):
+    """The gate/up GEMM that fetches its activation rows itself (cp.async producers writing the swizzled tile) must
+    give the bits of the same GEMM on a gathered copy: full, ragged and half tiles, and an expert without routes."""
+    from uma_qmoe_b200 import ops
+    src = expert_source(SEED, 7, "olmoe", encoding)
+    tokens = 777
+    rng = np.random.default_rng(12)
+    pool = np.array([0, 1, 3, 4, 7, 8, 11])
+    idx = torch.from_numpy(np.stack([rng.choice(pool, 2, replace=False, p=[.5, .2, .1, .1, .05, .03, .02]) for _ in range(tokens)]))
+    w = torch.rand((tokens, 2), generator=torch.Generator().manual_seed(3)) / 2
+    layer = stage_layer({int(e): src(int(e)) for e in pool}, 16, 2048, 1024, encoding, DEV)
+    x = syn.activations(SEED + 36, tokens).to(DEV)
+    quant = encoding != "bf16_le"
+    r = ops.route_sort(idx.to(DEV), w.to(DEV), layer.num_experts)
+    xs = ops.gather_rows(x, r.sorted_route, 2, permute=quant)
+    want = ops.grouped_gemm(layer, 0, xs, r, permute_out=quant, variant=1)
+    source = ops.gather_rows(x, None, 1, permute=True) if quant else x
+    got = ops.grouped_gemm_by_index(layer, source, r, 2, permute_out=quant)
+    again = ops.grouped_gemm_by_index(layer, source, r, 2, permute_out=quant)
+    torch.cuda.synchronize()
+    assert int(r.status.item()) == 0
+    assert torch.equal(got, want) and torch.equal(got, again)
+
+
 def test_bf16_large_batch_takes_the_pair_kernel_by_default_and_matches_the_one_cta_kernel():
     """BF16 layers on 16,384 routes or more run on the CTA-pair kernel unless the caller picks one; the whole
     operator must agree with the stages run explicitly on the one-CTA kernel and with the oracle on a sample."""

@@ -63,6 +63,8 @@ SIGNATURES = {
                                    C.c_void_p]),
     "umaq_grouped_gemm": (C.c_int, [C.POINTER(Layer), C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p,
                                     C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "umaq_grouped_gemm_by_index": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p,
+                                             C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "umaq_ep_local_ids": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                     C.c_void_p]),
     "umaq_ep_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,

@@ -173,6 +173,26 @@ int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, l
   return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
 }
 
+int umaq_grouped_gemm_by_index(const umaq_layer* layer, const void* hidden_bf16, const int* sorted_route, int top_k,
+                               long long routes, const int* num_tiles, const int* tile_table, int max_tiles,
+                               int permute_out, void* out_bf16, unsigned* status, void* stream) {
+  if (!layer || !hidden_bf16 || !sorted_route || !num_tiles || !tile_table || !out_bf16 || !status || top_k < 1 || routes <= 0) {
+    set_error("umaq_grouped_gemm_by_index: bad argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  GroupedGemmArgs g{};
+  g.mode = 0; g.enc = layer->encoding; g.num_experts = layer->num_experts;
+  g.n_rows = layer->intermediate; g.k = layer->hidden;
+  g.act = hidden_bf16; g.total_rows = routes;
+  g.w0 = layer->gate; g.s0 = layer->gate_scales; g.w1 = layer->up; g.s1 = layer->up_scales;
+  g.num_tiles = num_tiles; g.tile_expert = tile_table; g.tile_row0 = tile_table + max_tiles;
+  g.tile_rows = tile_table + 2 * max_tiles; g.max_tiles = max_tiles;
+  g.out = static_cast<__nv_bfloat16*>(out_bf16); g.out_stride = g.n_rows;
+  g.permute_out = permute_out; g.status = status; g.variant = 1;
+  g.gather_route = sorted_route; g.gather_top_k = top_k;
+  return launch_grouped_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
 int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long long count, int ranks, int rank,
                        int experts_per_rank, int placement, int* local_ids, void* stream) {
   if (!expert_indices || !local_ids) { set_error("umaq_ep_local_ids: null argument"); return ERR_BAD_ARGUMENT; }

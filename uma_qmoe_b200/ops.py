@@ -227,6 +227,22 @@ def grouped_gemm(layer: DeviceLayer, mode: int, act: torch.Tensor, routes: Sorte
     return out
 
 
+def grouped_gemm_by_index(layer: DeviceLayer, hidden: torch.Tensor, routes: SortedRoutes, top_k: int,
+                          permute_out: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The gate/up GEMM fetching its activation rows by index from ``hidden`` ([tokens, H]; permuted k order for a
+    quantised layer), as ``moe_prefill`` runs it: no ``[routes, H]`` copy of the activations."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    n_routes = routes.sorted_route.numel()
+    if out is None:
+        out = torch.empty((n_routes, layer.intermediate), dtype=torch.bfloat16, device=hidden.device)
+    code = _native.lib().umaq_grouped_gemm_by_index(
+        C.byref(layer.struct()), hidden.data_ptr(), routes.sorted_route.data_ptr(), top_k, n_routes,
+        routes.num_tiles.data_ptr(), routes.tile_table.data_ptr(), routes.max_tiles, int(permute_out), out.data_ptr(),
+        routes.status.data_ptr(), _stream(hidden.device))
+    _native.check(code, "umaq_grouped_gemm_by_index")
+    return out
+
+
 def ep_local_ids(indices: torch.Tensor, ranks: int, rank: int, experts_per_rank: int, interleaved: bool) -> torch.Tensor:
     """int32 local expert ids of the routes this rank owns, -1 elsewhere (see ``umaq_ep_local_ids``)."""
     if not indices.is_cuda or indices.dtype not in (torch.int32, torch.int64):
