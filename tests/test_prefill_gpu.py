@@ -67,7 +67,8 @@ def test_prefill_many_tokens_few_experts_matches_oracle():
     assert_parity(_run_prefill(layer, x, idx, w), want)
 
 
-@pytest.mark.parametrize("tokens", [500, 40])      # tensor-core kernel (ragged last CTA) / tiled kernel
+@pytest.mark.parametrize("tokens", [500, 40, 5, 299])      # tensor-core kernel (ragged last CTA) / cluster kernel: ten
+                                                            # clusters, two with a one-token tail, 75 with a ragged tail
 @pytest.mark.parametrize("model,renorm", [("olmoe", True), ("olmoe", False), ("qwen", False)])
 def test_router_matches_oracle(model, renorm, tokens):
     from uma_qmoe_b200 import ops
@@ -88,7 +89,8 @@ def test_router_matches_oracle(model, renorm, tokens):
     all_clear = same_logits & (srt[:, : k + 1].diff(dim=1) != 0).all(dim=1)
     # the kernel rounds an exactly summed dot product; the CPU GEMM of the oracle is off by one BF16 ulp on
     # about 1 logit in 5000, i.e. on 1-2 % of the rows
-    assert same_logits.float().mean() >= 0.95 and boundary_clear.float().mean() > 0.85 and all_clear.any()
+    if tokens >= 40:                                   # (with a handful of rows these shares are not statistics)
+        assert same_logits.float().mean() >= 0.95 and boundary_clear.float().mean() > 0.85 and all_clear.any()
     assert torch.equal(idx[boundary_clear].sort(dim=1).values, idx_ref[boundary_clear].sort(dim=1).values)
     assert torch.allclose(w[boundary_clear].sort(dim=1).values, w_ref[boundary_clear].sort(dim=1).values,
                           rtol=2e-5, atol=1e-8)
@@ -99,7 +101,7 @@ def test_router_matches_oracle(model, renorm, tokens):
     chosen = own.gather(1, idx)
     kth = own.sort(dim=1, descending=True).values[:, shape.top_k - 1]
     assert bool((chosen >= kth[:, None] - 1e-9).all())
-    assert int((~same_logits).sum()) <= 0.05 * x.shape[0]
+    assert int((~same_logits).sum()) <= max(1, 0.05 * x.shape[0])
 
 
 @pytest.mark.parametrize("tokens,top_k,experts,dtype", [(8192, 8, 64, torch.int64), (5000, 4, 60, torch.int32),

@@ -5,6 +5,8 @@
 // accumulation order of the reference's CPU path (src/uma_qmoe/custom_op.py:312-338).
 #include "grouped.cuh"
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace umaq {
@@ -274,6 +276,108 @@ __global__ void __launch_bounds__(256) router_tiled_kernel(const RouterArgs a) {
     if (t < a.tokens)
       softmax_topk_warp(logit[r], E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)t * a.top_k,
                         a.out_indices + (size_t)t * a.top_k);
+  }
+}
+
+// Router for a handful of tokens (decode steps, short prompts; E <= 64): latency is everything here -- at one token
+// the tiled kernel above is a single CTA walking 16 k-chunks with two barriers each and takes 65 us, more than the
+// expert kernels of the same layer.  Here a cluster of eight CTAs takes four tokens: CTA r of the cluster owns
+// experts 8 r .. 8 r + 7, a warp takes half of one expert's row for all four tokens (every load of the router
+// matrix is in flight at once: one round trip to L2 per CTA), the two halves meet in shared memory, and the logits
+// go to CTA 0 of the cluster through distributed shared memory, which runs the softmax / top-k after a cluster
+// barrier.  Products of BF16 values are exact in float32; eight of them are summed in float32 and the runs in
+// float64, which makes the BF16 rounding of the logit that of the exact dot product (the other router kernels'
+// bound, with shorter runs).
+constexpr int kRsTokens = 4, kRsWarps = 16, kRsCluster = 8, kRsExperts = 8;      // experts per CTA
+// Most tokens this kernel takes (UMAQ_ROUTER_SMALL_MAX overrides).  Measured on B200, 64 experts: 6 us up to 32
+// tokens, 8 us at 128, 16 us at 256, 26 us at 512 against a constant 20 us of the tensor-core kernel.
+constexpr int kRouterSmallMax = 320;
+
+__device__ __forceinline__ float dot8_bf16(const uint4& x, const uint4& w) {
+  const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ws[4] = {w.x, w.y, w.z, w.w};
+  float run = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    run = fmaf(__uint_as_float(xs[i] << 16), __uint_as_float(ws[i] << 16), run);
+    run = fmaf(__uint_as_float(xs[i] & 0xffff0000u), __uint_as_float(ws[i] & 0xffff0000u), run);
+  }
+  return run;
+}
+
+__global__ void __cluster_dims__(kRsCluster, 1, 1) __launch_bounds__(kRsWarps * 32)
+router_small_kernel(const RouterArgs a) {
+  extern __shared__ __align__(16) uint8_t rs_smem[];
+  __shared__ float logit[kRsTokens][kRtExperts + 1];                      // used in CTA 0 of the cluster
+  __shared__ double part[kRsWarps][kRsTokens];
+  const int H = a.hidden, E = a.experts, chunks = H >> 3, half_chunks = chunks >> 1;   // 16-byte chunks
+  uint4* xs = reinterpret_cast<uint4*>(rs_smem);                          // [kRsTokens][chunks]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t cr;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cr));
+  // a CTA may write into another CTA's shared memory only once that CTA runs: arrive now, wait before the stores
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  const int token0 = (blockIdx.x / kRsCluster) * kRsTokens, nt = min(kRsTokens, a.tokens - token0);
+  const uint4* xg = reinterpret_cast<const uint4*>(a.x + (size_t)token0 * H);     // consecutive token rows
+  for (int v = tid; v < nt * chunks; v += kRsWarps * 32) xs[v] = xg[v];
+  __syncthreads();
+  const int e = (int)cr * kRsExperts + (warp & 7), half = warp >> 3;
+  double acc[kRsTokens];
+#pragma unroll
+  for (int t = 0; t < kRsTokens; ++t) acc[t] = 0.0;
+  if (e < E) {
+    const uint4* wr = reinterpret_cast<const uint4*>(a.weight + (size_t)e * H);
+    const int end = (half + 1) * half_chunks;
+    for (int base = half * half_chunks; base < end; base += 256) {        // up to 8 chunks per lane and pass
+      uint4 wv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = base + j * 32 + lane;
+        wv[j] = c < end ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = base + j * 32 + lane;
+        if (c < end) {
+#pragma unroll
+          for (int t = 0; t < kRsTokens; ++t)
+            if (t < nt) acc[t] += (double)dot8_bf16(xs[t * chunks + c], wv[j]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kRsTokens; ++t) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+    if (lane == 0) part[warp][t] = acc[t];
+  }
+  __syncthreads();
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (tid < kRsExperts * kRsTokens) {                                      // both halves of (expert, token) -> logit
+    const int ee = tid & 7, t = tid >> 3, ge = (int)cr * kRsExperts + ee;
+    if (ge < E && t < nt) {
+      const float l = bf16_round((float)(part[ee][t] + part[ee + 8][t]));  // F.linear output in BF16
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&logit[t][ge])), "r"(0));
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(l) : "memory");
+      if (a.out_logits) a.out_logits[(size_t)(token0 + t) * E + ge] = __float2bfloat16_rn(l);
+    }
+  }
+  // every CTA's logits are in CTA 0's shared memory after this barrier; CTA 0 outlives the others' stores
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (cr != 0) return;
+  if (a.top_k <= 8) {
+    if (warp == 0) {                                                       // eight lanes per token, four tokens
+      const int r = lane >> 3;
+      const bool live = r < nt;
+      const int t = token0 + (live ? r : 0);
+      softmax_topk_oct(logit[live ? r : 0], live, E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)t * a.top_k,
+                       a.out_indices + (size_t)t * a.top_k);
+    }
+  } else if (warp < nt) {
+    const int t = token0 + warp;
+    softmax_topk_warp(logit[warp], E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)t * a.top_k,
+                      a.out_indices + (size_t)t * a.top_k);
   }
 }
 
@@ -758,7 +862,8 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
     set_error("router: unsupported shape (tokens %d, hidden %d, experts %d, top_k %d)", a.tokens, a.hidden, a.experts, a.top_k);
     return ERR_BAD_ARGUMENT;
   }
-  if (a.experts <= kRtExperts && a.hidden % kRmChunk == 0 && a.tokens >= 128) {
+  static const int small_max = [] { const char* v = std::getenv("UMAQ_ROUTER_SMALL_MAX"); return v ? std::atoi(v) : kRouterSmallMax; }();
+  if (a.experts <= kRtExperts && a.hidden % kRmChunk == 0 && a.tokens > small_max) {
     static thread_local int configured = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -768,6 +873,19 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
       configured = dev;
     }
     router_mma_kernel<<<(a.tokens + kRmTokens - 1) / kRmTokens, 256, kRmSmem, stream>>>(a);
+    return check_launch("router");
+  }
+  const size_t small_smem = (size_t)kRsTokens * a.hidden * 2;
+  if (a.experts <= kRtExperts && a.tokens <= small_max && small_smem <= 200 * 1024) {
+    static thread_local int small_configured = -1, small_bytes = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (small_smem > 48 * 1024 && (small_configured != dev || small_bytes < (int)small_smem)) {
+      cudaError_t e = cudaFuncSetAttribute(router_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_smem);
+      if (e != cudaSuccess) { set_error("router: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
+      small_configured = dev; small_bytes = (int)small_smem;
+    }
+    router_small_kernel<<<kRsCluster * ((a.tokens + kRsTokens - 1) / kRsTokens), kRsWarps * 32, small_smem, stream>>>(a);
     return check_launch("router");
   }
   if (a.experts <= kRtExperts && a.hidden % kRtChunk == 0 && a.top_k <= 32) {
