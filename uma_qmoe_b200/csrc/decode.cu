@@ -77,6 +77,7 @@ constexpr int kMaxSlots = 8;
 // whole share needs, up to kDownSmemMax; the gate/up kernel gets the rest.
 constexpr int kPairSmemBudget = 224 * 1024;
 constexpr int kDownSmemMax = 112 * 1024;
+constexpr int kDownSmemCeiling = 160 * 1024;      // what the kernel is allowed to ask for (UMAQ_DECODE_DOWN_SMEM)
 constexpr long long kDecodeWaitCycles = 40ll * 1000 * 1000;     // ~20 ms of SM clock: far beyond any healthy wait
 constexpr int kSyncStatus = 2, kSyncGateUpDone = 4, kSyncTarget = 6;
 
@@ -810,8 +811,9 @@ __device__ __forceinline__ void down_pairs(const DecodeKernelPlan& P, const Deco
   const bool odd = g & 1, diag = t == (g >> 1);
   const float nbias = -K.bias;
   if (P.resident && !wait_or_fail(full, 0, fail)) return;
-  for (int ul = 0; ul < npairs; ul += 2) {
-    const bool two = ul + 1 < npairs;
+  const int step = P.resident ? 2 : P.pair_step;
+  for (int ul = 0; ul < npairs; ul += step) {
+    const bool two = step == 2 && ul + 1 < npairs;
     int sa = ul, sb = two ? ul + 1 : ul;
     bool ready = true;
     int slot_a = 0, slot_b = 0;
@@ -1287,9 +1289,16 @@ bool plan_gateup(DecodeParams& p, int sms, int budget) {
   return P.smem_bytes <= budget;
 }
 
+int env_int(const char* name, int fallback) {
+  const char* s = std::getenv(name);
+  return s ? std::atoi(s) : fallback;
+}
+
 bool plan_down(DecodeParams& p, int sms) {
   DecodeKernelPlan& P = p.d;
   P = DecodeKernelPlan{};
+  static const int down_cap = std::min(kDownSmemCeiling, std::max(64 * 1024, env_int("UMAQ_DECODE_DOWN_SMEM", kDownSmemMax)));
+  static const int step_override = env_int("UMAQ_DECODE_DOWN_STEP", 0);
   const int H = p.hidden, I = p.inter;
   const int S = p.sh_gate ? p.shared_inter : 0;
   int cursor = 0, ws = 0;
@@ -1330,7 +1339,8 @@ bool plan_down(DecodeParams& p, int sms) {
   const int fixed = cursor;
   // scales as bulk copies need 16-byte sizes and offsets: an even number of groups per row
   P.bulk_scales = K0.groups % 2 == 0;
-  const int room = kDownSmemMax - fixed - 256;
+  const int room = down_cap - fixed - 256;
+  P.pair_step = 2;
   // resident: the CTA's rows of every slot in one block per slot (64 bytes apart modulo 128), then the scales
   const int slot_block = P.max_units * 2 * K0.row_bytes + 64;
   const int sc_slot = P.max_units * 2 * K0.groups * 4;
@@ -1356,13 +1366,16 @@ bool plan_down(DecodeParams& p, int sms) {
     const int want = P.max_units * (S ? 2 : 1);
     P.stages = std::min(want, room / (P.stage_bytes + 16));
     if (P.stages < 1 || (P.stages < 2 && want >= 2)) return false;
+    // (measured on the Qwen layer with its three-stage ring: one row pair per round 44.2 us, two 41.2 us -- sharing
+    // the fragments between two row pairs is worth more than the extra stage in flight)
+    if (step_override == 1 || step_override == 2) P.pair_step = step_override;
   }
   const int stage_total = P.stages * P.stage_bytes;
   for (int k = 0; k < 2; ++k) { P.kind[k].frag_off += stage_total; P.kind[k].gsum_off += stage_total; }
   P.red_off += stage_total; P.red2_off += stage_total; P.ysum_off += stage_total;
   P.bar_off = stage_total + fixed;
   P.smem_bytes = P.bar_off + 2 * P.stages * 8 + 16;
-  return P.smem_bytes <= kDownSmemMax;
+  return P.smem_bytes <= down_cap;
 }
 
 bool plan_both(DecodeParams& p, int sms) {
@@ -1423,7 +1436,7 @@ int launch_moe_decode(DecodeParams p, cudaStream_t stream) {
   if (configured_device != dev) {
     cudaError_t e = cudaFuncSetAttribute(decode_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBudget);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDownSmemMax);
+      e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDownSmemCeiling);
     // both kernels live on an SM at the same time: ask for the largest shared-memory carve-out
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(decode_gateup_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
