@@ -43,25 +43,26 @@ METRIC, UNIT = "prefill_tokens_per_s", "tokens/s"
 
 # One ncu capture per kernel (dram__bytes_read.sum, dram__bytes_write.sum per launch).  The decode pair was captured
 # on the benchmark's own layer; the grouped GEMMs on 2048 tokens of it (a full-size capture would hold more than a
-# gigabyte through ~40 replay passes), so their traffic is scaled to the benchmark's token count below: the weights
-# of all 64 experts are read once whatever the token count, everything else grows with the routes.
+# gigabyte through ~40 replay passes), so their traffic is scaled to the benchmark's token count below.
 CAPTURES = {
-    "decode_pair": {"read": 17.86e6 + 9.01e6, "write": 0.0},
-    "gemm_gate_up": {"tokens": 2048, "read": 196.6e6, "write": 22.3e6, "weights": 64 * 2 * (1024 * 1024 + 1024 * 16 * 4)},
+    "decode_pair": {"read": 17.89e6 + 9.00e6, "write": 0.0},
+    # gate/up GEMM fetching its activation rows by index: the read is the layer's gate/up codes and scales (142.6 MB, a
+    # few per cent of them L2 hits) plus the 2048 activation rows (8.4 MB); the write is the intermediate
+    "gemm_gate_up": {"tokens": 2048, "read": 139.4e6, "write": 19.2e6},
+    # down GEMM: weights 71.3 MB + the intermediate rows it reads; the write is the weighted per-route output
     "gemm_down": {"tokens": 2048, "read": 98.4e6, "write": 28.5e6, "weights": 64 * (2048 * 512 + 2048 * 8 * 4)},
 }
 
 
-def gemm_traffic(name: str, tokens: int, by_index: bool = False) -> int:
-    """DRAM bytes of one grouped-GEMM launch on `tokens` tokens, from the capture of that kernel.  `by_index`: the
-    launch reads its activation rows from the [tokens, H] input (each row once from DRAM, re-reads from L2) instead
-    of the [routes, H] gathered copy the capture was made on."""
+def gemm_traffic(name: str, tokens: int) -> int:
+    """DRAM bytes of one grouped-GEMM launch on `tokens` tokens, from the capture of that kernel: the weights of all
+    64 experts are read once whatever the token count; what is written grows with the routes; the gate/up GEMM reads
+    each further token's activation row once (4 KiB), the down GEMM its intermediate rows in proportion to the routes."""
     c = CAPTURES[name]
     grow = tokens / c["tokens"]
-    activations = (c["read"] - c["weights"]) * grow
-    if by_index:
-        activations = min(activations, tokens * 2048 * 2)
-    return int(c["weights"] + activations + c["write"] * grow)
+    if name == "gemm_gate_up":
+        return int(c["read"] + (tokens - c["tokens"]) * 2048 * 2 + c["write"] * grow)
+    return int(c["weights"] + (c["read"] - c["weights"]) * grow + c["write"] * grow)
 
 
 def peaks() -> tuple[dict, str]:
@@ -430,9 +431,8 @@ def kernel_legs(stack, x_dev, shape, dev) -> dict:
     def tensor_roofline(kernel, fl, ms_, capture):
         return {"bound": "tensor", "kernel": kernel, "achieved": fl / (ms_ / 1e3) / 1e12, "peak": pk["bf16_tflops"],
                 "unit": "TFLOP/s", "frac": fl / (ms_ / 1e3) / 1e12 / pk["bf16_tflops"],
-                "traffic": gemm_traffic(capture, TOKENS, by_index=capture == "gemm_gate_up"),
-                "traffic_source": f"ncu capture at {CAPTURES[capture]['tokens']} tokens, scaled by routes (weights fixed"
-                + ("; activations read once per token, not per route)" if capture == "gemm_gate_up" else ")"), "peak_source": f"{pk_kind} (burst)", "ms_per_launch": ms_,
+                "traffic": gemm_traffic(capture, TOKENS),
+                "traffic_source": f"ncu capture at {CAPTURES[capture]['tokens']} tokens, scaled to {TOKENS} (weights fixed)", "peak_source": f"{pk_kind} (burst)", "ms_per_launch": ms_,
                 "flops_per_launch": fl}
     out["roofline"] = tensor_roofline("grouped_gemm_kernel<Q4, gate/up+SwiGLU>, rows fetched by index", flops, gemm_ms, "gemm_gate_up")
     out["roofline"]["ms_per_launch_on_gathered_rows"] = gathered_ms
@@ -657,17 +657,25 @@ def kernel_case(args) -> None:
         inter = torch.empty((xs.shape[0], shape.intermediate), dtype=torch.bfloat16, device=dev)
         yw = torch.empty((xs.shape[0], shape.hidden), dtype=torch.bfloat16, device=dev)
 
+        source = ops.gather_rows(x, None, 1, permute=True) if quant else x     # [tokens, H] for the by-index kernel
+
+        def gate_up():
+            if args.by_index:
+                ops.grouped_gemm_by_index(stack.layers[0], source, routes, shape.top_k, permute_out=quant, out=inter)
+            else:
+                ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=quant, out=inter, variant=args.variant)
+
         def run():
-            ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=quant, out=inter, variant=args.variant)
+            gate_up()
             ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight, out=yw,
                              variant=args.variant)
         ms = timed(run, args.steps, args.warmup, 1)
-        ms1 = timed(lambda: ops.grouped_gemm(stack.layers[0], 0, xs, routes, permute_out=quant, out=inter,
-                                             variant=args.variant), args.steps, args.warmup, 1)
+        ms1 = timed(gate_up, args.steps, args.warmup, 1)
         ms2 = timed(lambda: ops.grouped_gemm(stack.layers[0], 1, inter, routes, route_weight=routes.sorted_weight,
                                              out=yw, variant=args.variant), args.steps, args.warmup, 1)
         flops = 2.0 * xs.shape[0] * 3 * shape.hidden * shape.intermediate
-        print(json.dumps({"case": "gemm", "model": args.model, "encoding": encoding, "tokens": args.tokens, "variant": args.variant, "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
+        print(json.dumps({"case": "gemm", "model": args.model, "encoding": encoding, "tokens": args.tokens, "variant": args.variant,
+                          "gate_up_rows_by_index": bool(args.by_index), "ms_both_gemms": ms, "ms_gate_up": ms1, "ms_down": ms2,
                           "tflops": flops / (ms / 1e3) / 1e12, "tflops_gate_up": flops * 2 / 3 / (ms1 / 1e3) / 1e12,
                           "tflops_down": flops / 3 / (ms2 / 1e3) / 1e12, "status": int(routes.status.item())}))
 
@@ -841,6 +849,8 @@ def main() -> None:
                     help="layer shape of the --only decode case: olmoe = config 0 (Q4), qwen = config 2 (Q8 + shared)")
     ap.add_argument("--encoding", choices=("q4_group128", "q8_group128", "bf16_le"), default=None,
                     help="expert encoding of the --only decode / gemm cases (default: q4 for olmoe, q8 for qwen)")
+    ap.add_argument("--by-index", action="store_true",
+                    help="--only gemm: the gate/up GEMM fetches its activation rows by index (as the operator runs it)")
     ap.add_argument("--variant", type=int, default=0, choices=(0, 1, 2),
                     help="grouped GEMM kernel of the --only gemm case: 0/1 one CTA per tile (default), 2 CTA pairs")
     args = ap.parse_args()

@@ -314,6 +314,9 @@ router_small_kernel(const RouterArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint32_t cr;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cr));
+  // A kernel launched behind this one with programmatic stream serialisation (the decode kernels are) may become
+  // resident now and run its prologue; it still waits for this grid to finish before it reads the routes.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // a CTA may write into another CTA's shared memory only once that CTA runs: arrive now, wait before the stores
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   const int token0 = (blockIdx.x / kRsCluster) * kRsTokens, nt = min(kRsTokens, a.tokens - token0);
