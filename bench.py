@@ -10,11 +10,13 @@ seeded synthetic (no checkpoint); the 3.4 GB of packed weights exceed L2, so eve
 from HBM.  With N ranks the experts and the tokens are split N ways (strong scaling).
 
 One JSON line on rank 0.  `value` = tokens/s with inputs resident on the device; `e2e` = the same
-through torch.ops.uma_qmoe.moe_forward with the step's activations coming from pinned host memory
-and the result read back; `roofline` = the gate/up grouped GEMM alone (tensor-bound) and `decode`
-= the batch-1 decode kernels rotating over the 16 layers, replayed from a CUDA graph (HBM-bound); `cpu_baseline` = the
-reference's own CPU correctness path (the package installed under oracle/_ref by oracle/make_ref.py; the port in
-oracle/ only if that is absent, `kind` says which) timed on one full-size call of layer 0 on this host.
+through torch.ops.uma_qmoe.moe_forward with every step's activations coming from pinned host memory
+and every step's result read back into pinned host memory (the copies ride on a copy stream under the
+next step's compute, as in a serving loop); `roofline` / `roofline_down` = the two grouped GEMMs alone
+(tensor-bound), `decode` / `decode_qwen` = the batch-1 decode kernels rotating over the layers, replayed
+from a CUDA graph (HBM-bound); `cpu_baseline` = the reference's own CPU correctness path (the package
+installed under oracle/_ref by oracle/make_ref.py; the port in oracle/ only if that is absent, `kind`
+says which) timed on one full-size call of layer 0 on this host.
 `--impl reference` times that CPU path as the measured arm.
 """
 
@@ -350,10 +352,58 @@ def native_arm(args) -> None:
     def step_resident():
         run_stack(x_dev)
 
-    def step_e2e():
-        y = run_stack(x_host.to(dev, non_blocking=True))
-        out_host.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def timed_e2e(steps: int, warmup: int) -> float:
+        """Milliseconds per step with every step's input coming from pinned host memory and every step's result
+        read back into pinned host memory, as a serving loop runs it: the copies of step i + 1 (in) and of step i
+        (out) travel on a copy stream while step i + 1 computes, two device buffers in turn; the host looks at a
+        step's result one step later.  Device-timed: from before the first input copy to after the last result copy."""
+        main = torch.cuda.current_stream()
+        copy = torch.cuda.Stream()
+        inputs = [torch.empty_like(x_dev) for _ in range(2)]
+        results = [out_host, torch.empty_like(out_host).pin_memory()]
+        new_event = lambda: [torch.cuda.Event() for _ in range(2)]
+        loaded, computed, stored = new_event(), new_event(), new_event()
+
+        def load(i):                                   # on the copy stream, once step i - 2 no longer reads the buffer
+            with torch.cuda.stream(copy):
+                if i >= 2:
+                    copy.wait_event(computed[i % 2])
+                inputs[i % 2].copy_(x_host, non_blocking=True)
+                loaded[i % 2].record(copy)
+
+        def loop(n, first=None, last=None):
+            if first is not None:
+                first.record(copy)
+            load(0)
+            for i in range(n):
+                main.wait_event(loaded[i % 2])
+                y = run_stack(inputs[i % 2])
+                computed[i % 2].record(main)
+                if i + 1 < n:
+                    load(i + 1)
+                with torch.cuda.stream(copy):
+                    copy.wait_event(computed[i % 2])
+                    results[i % 2].copy_(y, non_blocking=True)
+                    stored[i % 2].record(copy)
+                y.record_stream(copy)
+                if i >= 1:
+                    stored[(i - 1) % 2].synchronize()  # the host has the previous step's result
+            if last is not None:
+                last.record(copy)
+            stored[(n - 1) % 2].synchronize()
+        loop(max(1, warmup))
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        loop(steps, start, stop)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(stop) / steps], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        return float(ms.item())
 
     # The batch-1 decode legs come first: a call is a few microseconds, and right after the long tensor-bound legs
     # the same kernels measured 10 % slower.
@@ -364,7 +414,7 @@ def native_arm(args) -> None:
 
     with ClockSampler(local) as clocks:
         ms = timed(step_resident, args.steps, args.warmup, world)
-        ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2), world)
+        ms_e2e = timed_e2e(args.steps, max(1, args.warmup // 2))
 
     launches = launches_per_step * args.steps
     pk, pk_kind = peaks()
@@ -373,6 +423,7 @@ def native_arm(args) -> None:
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
             "e2e": {"value": TOKENS / (ms_e2e / 1e3), "unit": UNIT, "ms_per_step": ms_e2e,
+                    "copies": "input from and result to pinned host memory every step, on a copy stream under the next step's compute",
                     "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2 * world},
             "gpu_launches": launches, "clocks": clocks.summary(),
             **({"exchange": exchange_name} if world > 1 else {}),
