@@ -131,6 +131,7 @@ class MixedTargetNativeBackend:
         self._cache = _LayerCache()
         self._workspaces: dict[tuple, _Workspace] = {}
         self._pending: dict[tuple[int, int, str], Any] = {}      # layers being staged: (DeviceLayer, wait)
+        self._linear_cache: dict[tuple[int, str, str], Any] = {}  # single tensors staged for q4_linear / q8_linear
         self._workspace_lock = threading.Lock()
 
     # ---- construction ---------------------------------------------------------------------
@@ -287,6 +288,8 @@ class MixedTargetNativeBackend:
         with self._cache.lock:
             for key in [k for k in self._cache.layers if k[0] == pack_handle]:
                 del self._cache.layers[key]
+            for key in [k for k in self._linear_cache if k[0] == pack_handle]:
+                del self._linear_cache[key]
 
     # ---- execution ------------------------------------------------------------------------
     def _workspace(self, kind: str, layer: Any, tokens: int, top_k: int, shared: Any, device: Any, stream: Any) -> _Workspace:
@@ -352,6 +355,57 @@ class MixedTargetNativeBackend:
             ops.moe_prefill(layer, flat, indices, weights, slot.buffer, shared, out=out)
         slot.publish(stream)
         return out.reshape(hidden_states.shape)
+
+    # ---- one projection as a linear layer -----------------------------------------------------
+    def _linear(self, input_tensor: Any, pack_handle: int, tensor_name: str, encoding: str):
+        """``bf16(input . W^T)`` for one packed tensor of a registered pack (the reference backend's ``q4_linear`` /
+        ``q8_linear``, ``src/uma_qmoe/native_backend.py:319-372``; there a GEMV kernel per call, here the grouped GEMM's
+        down mode on a one-expert layer: rows of any count, out features a multiple of 256, in features of 128)."""
+        import torch
+
+        from . import ops
+        from .ops import DeviceLayer
+        if input_tensor.dtype != torch.bfloat16 or input_tensor.ndim != 2 or not input_tensor.is_cuda:
+            raise RuntimeError("the native backend requires a 2-D BF16 CUDA input")
+        device = input_tensor.device
+        key = (pack_handle, tensor_name, str(device))
+        with self._cache.lock:
+            hit = self._linear_cache.get(key)
+        if hit is None:
+            with acquire_expert_pack(pack_handle) as reader:
+                data, scales, meta = reader.tensor_views(tensor_name)
+                try:
+                    if meta.get("encoding", "q4_group128") != encoding:
+                        raise RuntimeError(f"tensor {tensor_name!r} is not {encoding}")
+                    rows, k = (int(d) for d in meta["shape"])
+                    with warnings.catch_warnings():
+                        warnings.filterwarnings("ignore", message="The given buffer is not writable")
+                        codes = torch.frombuffer(data, dtype=torch.uint8).to(device)
+                        sc = torch.frombuffer(scales, dtype=torch.float32).to(device)
+                finally:
+                    data.release()
+                    scales.release()
+            if rows % 256 or k % 128:
+                raise RuntimeError(f"tensor {tensor_name!r} has a shape the linear path does not take: {(rows, k)}")
+            # a one-expert layer whose "down" projection is this tensor: hidden = out features, intermediate = in
+            hit = DeviceLayer(encoding, 1, rows, k, codes, codes, codes, sc, sc, sc)
+            with self._cache.lock:
+                hit = self._linear_cache.setdefault(key, hit)
+        if input_tensor.shape[1] != hit.intermediate:
+            raise RuntimeError(f"input has {input_tensor.shape[1]} features, the tensor takes {hit.intermediate}")
+        n = input_tensor.shape[0]
+        if n == 0:
+            return input_tensor.new_empty((0, hit.hidden))
+        ones = torch.ones((n, 1), dtype=torch.float32, device=device)
+        routes = ops.route_sort(torch.zeros((n, 1), dtype=torch.int32, device=device), ones, 1)
+        act = ops.gather_rows(input_tensor.contiguous(), None, 1, permute=True)      # the k order of the quantised GEMM
+        return ops.grouped_gemm(hit, 1, act, routes, variant=1)
+
+    def q4_linear(self, input_tensor: Any, pack_handle: int, tensor_name: str):
+        return self._linear(input_tensor, pack_handle, tensor_name, "q4_group128")
+
+    def q8_linear(self, input_tensor: Any, pack_handle: int, tensor_name: str):
+        return self._linear(input_tensor, pack_handle, tensor_name, "q8_group128")
 
     def __call__(self, hidden_states, expert_indices, routing_weights, layer_index: int, pack_handle: int):
         return self._run("olmoe", hidden_states, expert_indices, routing_weights, layer_index, pack_handle)
