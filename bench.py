@@ -490,7 +490,30 @@ def kernel_legs(stack, x_dev, shape, dev) -> dict:
     out["roofline_down"] = tensor_roofline("grouped_gemm_kernel<Q4, down x route weight>", flops / 2, down_ms, "gemm_down")
     out["kernels_us"] = prefill_kernel_times(stack, x_dev, shape, dev)
     del xs, inter, yw, flush, x_perm
+    out["prefill_512_tokens"] = small_prefill_leg(stack, shape, dev)
     return out
+
+
+def small_prefill_leg(stack, shape, dev) -> dict:
+    """One layer on 512 tokens with the skewed router (expert loads vary, some experts get no token): router + the
+    whole operator, replayed from a CUDA graph of eight calls."""
+    from uma_qmoe_b200 import ops, synthetic as syn
+    tokens = 512
+    x = syn.activations(SEED + 1, tokens).to(dev)
+    wr = syn.router_weight(SEED, 0, shape, skew=1.5).to(dev)
+    w, idx = ops.route_topk(x, wr, shape.top_k, True)
+    counts = torch.bincount(idx.flatten(), minlength=shape.experts)
+    ws = ops.prefill_workspace(stack.layers[0], tokens, shape.top_k, None, dev)
+
+    def eight():
+        for _ in range(8):
+            ww, ii = ops.route_topk(x, wr, shape.top_k, True)
+            ops.moe_prefill(stack.layers[0], x, ii, ww, ws)
+    ms = timed(graphed(eight), 5, 2, 1) / 8
+    flops = 2.0 * tokens * shape.top_k * 3 * shape.hidden * shape.intermediate
+    return {"workload": "one OLMoE layer, 512 tokens, router skew 1.5", "us_per_call": round(ms * 1e3, 2),
+            "tokens_per_s": round(tokens / (ms / 1e3)), "tflops": round(flops / (ms / 1e3) / 1e12, 1),
+            "experts_without_tokens": int((counts == 0).sum()), "largest_expert_load": int(counts.max())}
 
 
 def decode_legs(stack, x_dev, shape, dev) -> tuple[dict, int]:
