@@ -432,7 +432,9 @@ def native_arm(args) -> None:
     if rank == 0 and world == 1 and args.legs == "all":
         line.update(kernel_objects)
         line.update(decode_objects)
-        line["gpu_launches"] += 26 + decode_launches              # the roofline legs and the decode legs
+        # the single-kernel legs (3 x 13 cold launches, ten kernels x 7 graph passes x 8 launches, the 512-token leg:
+        # 10 passes x 8 calls x 7 kernels) and the decode legs
+        line["gpu_launches"] += 39 + 10 * 7 * 8 + 10 * 8 * 7 + decode_launches
         line["cpu_baseline"] = cpu_baseline_subprocess()
     if world > 1:
         line["ep_check"] = ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world)
