@@ -597,7 +597,8 @@ __global__ void __maxnreg__(64) decode_gateup_kernel(const DecodeParams p) {
   // last kGProducers warps produce and the others compute
   const bool whole_rows = P.kind[0].nch == 1 && (P.kind[1].units == 0 || P.kind[1].nch == 1);
   const bool all_at_once = whole_rows && ue - ub <= P.stages;
-  const int ncons = all_at_once ? kGW : kGW - kGProducers;
+  const int nprod = P.producers;
+  const int ncons = all_at_once ? kGW : kGW - nprod;
   const bool consumer = warp < ncons;
   // resident Q4 fast path: every unit of this CTA is a routed one, a stage has one item per warp
   const bool fast = all_at_once && P.kind[0].enc == ENC_Q4 && P.kind[0].ips == kGW && ue <= U0 && ue - ub <= 8;
@@ -700,7 +701,7 @@ __global__ void __maxnreg__(64) decode_gateup_kernel(const DecodeParams p) {
       }
       const uint32_t scale_bytes = 8u * K.groups * 4;              // per projection
       for (int ch = 0; ch < K.nch; ++ch, ++n) {
-        if (n % kGProducers != pj) continue;
+        if (n % nprod != pj) continue;
         const int slot = n % P.stages, round = n / P.stages;
         if (round > 0 && !wait_or_fail(empty + slot, (round - 1) & 1, fail)) break;
         uint8_t* st = smem + (size_t)slot * P.stage_bytes;
@@ -962,7 +963,8 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
   const uint32_t full_count = P.bulk_scales ? 1 : 1 + 32;
   // with the whole share issued up front by all warps every warp computes; otherwise the last kDProducers produce
   const bool all_at_once = P.resident && P.bulk_scales;
-  const int ncons = all_at_once ? kNW : kNW - kDProducers;
+  const int nprod = P.producers;
+  const int ncons = all_at_once ? kNW : kNW - nprod;
   const bool consumer = warp < ncons;
   // resident fast path: quantised rows, one item per warp
   const bool fast = all_at_once && P.kind[0].groups && P.kind[0].ips == kNW && !P.kind[1].nvs && P.max_units <= 8;
@@ -1052,7 +1054,7 @@ __global__ void __maxnreg__(96) decode_down_kernel(const DecodeParams p) {
         const DecodeKind& K = P.kind[k];
         const uint32_t sbytes = 2u * K.groups * 4;
         for (int rp = rp0; rp < rp1; ++rp, ++n) {
-          if (n % kDProducers != pj) continue;
+          if (n % nprod != pj) continue;
           const int slot = n % P.stages, round = n / P.stages;
           if (round > 0 && !wait_or_fail(empty + slot, (round - 1) & 1, fail)) break;
           uint8_t* st = smem + (size_t)slot * P.stage_bytes;
@@ -1229,6 +1231,11 @@ void describe_kind(DecodeKind& K, int enc, int k) {
   K.bias = enc == ENC_Q4 ? 136.f : (enc == ENC_Q8 ? 2304.f : 0.f);
 }
 
+int env_int(const char* name, int fallback) {
+  const char* s = std::getenv(name);
+  return s ? std::atoi(s) : fallback;
+}
+
 bool plan_gateup(DecodeParams& p, int sms, int budget) {
   DecodeKernelPlan& P = p.g;
   P = DecodeKernelPlan{};
@@ -1250,6 +1257,8 @@ bool plan_gateup(DecodeParams& p, int sms, int budget) {
     K.mstride = 8 * K.ch + 64;             // gate block, 64 bytes, up block
     P.cost[k] = K.row_bytes;
   }
+  static const int g_producers = std::max(1, std::min(kGProducers, env_int("UMAQ_DECODE_GATEUP_PRODUCERS", kGProducers)));
+  P.producers = g_producers;
   P.total_cost = (long long)P.kind[0].units * P.cost[0] + (long long)P.kind[1].units * P.cost[1];
   P.grid = std::min(sms, P.kind[0].units + P.kind[1].units);
   P.bulk_scales = 1;
@@ -1289,11 +1298,6 @@ bool plan_gateup(DecodeParams& p, int sms, int budget) {
   return P.smem_bytes <= budget;
 }
 
-int env_int(const char* name, int fallback) {
-  const char* s = std::getenv(name);
-  return s ? std::atoi(s) : fallback;
-}
-
 bool plan_down(DecodeParams& p, int sms) {
   DecodeKernelPlan& P = p.d;
   P = DecodeKernelPlan{};
@@ -1331,7 +1335,10 @@ bool plan_down(DecodeParams& p, int sms) {
   }
   DecodeKind& K0 = P.kind[0];
   const int pairs = H / 2;
-  P.grid = std::min(sms, pairs);
+  // With a shared expert the kernel runs a ring with few consumer warps per CTA; two CTAs per SM (the second one
+  // becomes resident when the gate/up CTA of that SM has left) double the warps that do the arithmetic.
+  static const int ring_ctas_per_sm = std::max(1, std::min(4, env_int("UMAQ_DECODE_DOWN_CTAS_PER_SM", 2)));
+  P.grid = std::min(sms * (S ? ring_ctas_per_sm : 1), pairs);
   P.max_units = (pairs + P.grid - 1) / P.grid;
   P.red_off = cursor; cursor += align_up(P.max_units * kNW * 16 * 4, 128);
   P.red2_off = cursor; if (S) cursor += align_up(P.max_units * kNW * 16 * 4, 128);
@@ -1341,6 +1348,8 @@ bool plan_down(DecodeParams& p, int sms) {
   P.bulk_scales = K0.groups % 2 == 0;
   const int room = down_cap - fixed - 256;
   P.pair_step = 2;
+  static const int d_producers = std::max(1, std::min(3, env_int("UMAQ_DECODE_DOWN_PRODUCERS", kDProducers)));
+  P.producers = d_producers;
   // resident: the CTA's rows of every slot in one block per slot (64 bytes apart modulo 128), then the scales
   const int slot_block = P.max_units * 2 * K0.row_bytes + 64;
   const int sc_slot = P.max_units * 2 * K0.groups * 4;

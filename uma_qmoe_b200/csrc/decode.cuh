@@ -57,6 +57,7 @@ struct DecodeKernelPlan {
   int sc_slot_stride;       // down: bytes from one slot's scales to the next
   int smem_bytes;
   int max_units;            // most units (gate/up) or row pairs (down) any CTA gets
+  int producers;            // warps that feed the ring when a CTA's share does not fit it at once
   int pair_step;            // down: row pairs a consumer round takes together (2 shares the fragments; 1 when the ring
                             // is too short to hold two rounds)
 };
