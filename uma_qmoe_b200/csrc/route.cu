@@ -408,17 +408,29 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
   const int H = a.hidden, E = a.experts, nchunks = H / kRmChunk;
   const int g = warp >> 1, h = warp & 1;                   // tokens 16g.., experts 32h..
 
+  // per thread: four 16-byte pieces of the token tile and of the router matrix per chunk; everything that does not
+  // depend on the chunk is computed once (the loop is one CTA's dependent chain, every instruction in it counts)
+  const uint8_t* x_src[4];
+  const uint8_t* w_src[4];
+  uint32_t piece_dst[4];
+  bool x_ok[4], w_ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int v = tid + i * 256, r = v >> 4, c = v & 15;
+    const int t = token0 + r;
+    x_ok[i] = t < a.tokens;
+    w_ok[i] = r < E;
+    x_src[i] = reinterpret_cast<const uint8_t*>(a.x + (size_t)(x_ok[i] ? t : 0) * H + c * 8);
+    w_src[i] = reinterpret_cast<const uint8_t*>(a.weight + (size_t)(w_ok[i] ? r : 0) * H + c * 8);
+    piece_dst[i] = (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4));
+  }
   auto load_chunk = [&](int kc, int stage) {
     uint8_t* xs = rm_smem + stage * 2 * kRmTile;
     uint8_t* ws = xs + kRmTile;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int v = tid + i * 256, r = v >> 4, c = v & 15;
-      const int t = token0 + r;
-      const bool ok = t < a.tokens;
-      cp_async16(xs + r * 256 + ((c ^ (r & 7)) << 4), a.x + (size_t)(ok ? t : 0) * H + kc * kRmChunk + c * 8, ok);
-      const bool wok = r < E;
-      cp_async16(ws + r * 256 + ((c ^ (r & 7)) << 4), a.weight + (size_t)(wok ? r : 0) * H + kc * kRmChunk + c * 8, wok);
+      cp_async16(xs + piece_dst[i], x_src[i] + kc * (kRmChunk * 2), x_ok[i]);
+      cp_async16(ws + piece_dst[i], w_src[i] + kc * (kRmChunk * 2), w_ok[i]);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -435,12 +447,18 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
   // ldmatrix row / chunk of this lane: A = 16 tokens x 16 k, B = 2 n-tiles (16 experts) x 16 k
   const int a_row = g * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_sel = lane >> 4;
   const int b_row = h * 32 + (lane & 7) + ((lane >> 4) & 1) * 8, b_sel = (lane >> 3) & 1;
+  uint32_t a_off[kRmChunk / 16], b_off[kRmChunk / 16];   // swizzled offsets of this lane's ldmatrix rows, per k step
+#pragma unroll
+  for (int k16 = 0; k16 < kRmChunk / 16; ++k16) {
+    a_off[k16] = (uint32_t)(a_row * 256 + (((k16 * 2 + a_sel) ^ (a_row & 7)) << 4));
+    b_off[k16] = (uint32_t)(kRmTile + b_row * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4));
+  }
   for (int kc = 0; kc < nchunks; ++kc) {
     asm volatile("cp.async.wait_group %0;" ::"n"(kRmStages - 2) : "memory");
     __syncthreads();                                       // chunk kc has landed; chunk kc - 1's buffer is free
     if (kc + kRmStages - 1 < nchunks) load_chunk(kc + kRmStages - 1, (kc + kRmStages - 1) % kRmStages);
     else asm volatile("cp.async.commit_group;" ::: "memory");
-    const uint32_t xs = smem_u32(rm_smem + (kc % kRmStages) * 2 * kRmTile), ws = xs + kRmTile;
+    const uint32_t xs = smem_u32(rm_smem + (kc % kRmStages) * 2 * kRmTile);
     float part[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -449,9 +467,9 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
 #pragma unroll
     for (int k16 = 0; k16 < kRmChunk / 16; ++k16) {
       uint32_t a0, a1, a2, a3, b[8];
-      ldmatrix_x4(xs + a_row * 256 + (((k16 * 2 + a_sel) ^ (a_row & 7)) << 4), a0, a1, a2, a3);
-      ldmatrix_x4(ws + b_row * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4), b[0], b[1], b[2], b[3]);
-      ldmatrix_x4(ws + (b_row + 16) * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4), b[4], b[5], b[6], b[7]);
+      ldmatrix_x4(xs + a_off[k16], a0, a1, a2, a3);
+      ldmatrix_x4(xs + b_off[k16], b[0], b[1], b[2], b[3]);
+      ldmatrix_x4(xs + b_off[k16] + 16 * 256, b[4], b[5], b[6], b[7]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) mma_bf16_16816(part[j], a0, a1, a2, a3, b[2 * j], b[2 * j + 1]);
     }
