@@ -352,6 +352,12 @@ def native_arm(args) -> None:
     def step_resident():
         run_stack(x_dev)
 
+    def step_in_line():
+        """One step with its copies in line: input copy, compute, result copy, host waits."""
+        y = run_stack(x_host.to(dev, non_blocking=True))
+        out_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
     def timed_e2e(steps: int, warmup: int) -> float:
         """Milliseconds per step with every step's input coming from pinned host memory and every step's result
         read back into pinned host memory, as a serving loop runs it: the copies of step i + 1 (in) and of step i
@@ -415,6 +421,7 @@ def native_arm(args) -> None:
     with ClockSampler(local) as clocks:
         ms = timed(step_resident, args.steps, args.warmup, world)
         ms_e2e = timed_e2e(args.steps, max(1, args.warmup // 2))
+        ms_in_line = timed(step_in_line, max(2, args.steps // 2), 1, world)
 
     launches = launches_per_step * args.steps
     pk, pk_kind = peaks()
@@ -423,6 +430,7 @@ def native_arm(args) -> None:
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
             "e2e": {"value": TOKENS / (ms_e2e / 1e3), "unit": UNIT, "ms_per_step": ms_e2e,
+                    "ms_per_step_with_copies_in_line": ms_in_line,
                     "copies": "input from and result to pinned host memory every step, on a copy stream under the next step's compute",
                     "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2 * world},
             "gpu_launches": launches, "clocks": clocks.summary(),
