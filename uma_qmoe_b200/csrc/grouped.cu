@@ -90,6 +90,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int kNumB = ENC == ENC_BF16 ? kInStages : kBStages;
   float* sScales = reinterpret_cast<float*>(sB + kNumB * kBTile);
   GemmShared& sh = *reinterpret_cast<GemmShared*>(reinterpret_cast<uint8_t*>(sScales) + 2 * BN * kMaxGroups * 4);
+  // The down GEMM of a quantised layer stages its results in shared memory (BF16 weight stages are TMA-fed across
+  // tiles and never idle; the gate/up GEMM writes half as much and measured faster with direct stores).
+  constexpr bool kStaged = ENC != ENC_BF16 && MODE == 1;
+  static_assert(kBStages >= 2 && kBTile >= kConvertWarps * 4096, "epilogue staging lives in two converted stages");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int K = p.k;
@@ -354,6 +358,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int quarter = warp & 3, ch = (warp - 2) >> 2;
       const int nchunks = two ? 8 : 4;                   // per warp: {half 0, half 1} x 4 chunks
       const uint32_t tq = tmem + ((uint32_t)(quarter * 32) << 16);
+      // Staged results leave through shared memory so that a warp's store instruction covers whole 128-byte
+      // lines (one row per lane costs 32 partly written lines per instruction).  The staging bytes are
+      // the rows this warp itself writes in the two converted-weight stages, idle between the tile's last MMA and
+      // this warp's next conversion: no other warp and no TMA touches them.
+      uint8_t* const stage0 = sB + (warp - 2) * 4096;
+      auto stage_piece_of = [&](int i) { return stage0 + i * kBTile; };
       auto release = [&]() {
         tc_fence_before();                               // every tcgen05.ld of this tile is complete (wait::ld)
         __syncwarp();
@@ -376,7 +386,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               release();
             }
             const int row = (c >> 2) * BM + quarter * 32 + lane;   // route row inside the tile
-            if (row < t.nrows) {
+            if (row < t.nrows && !(p.debug & 2)) {
               const uint32_t (&gg)[16] = g[c & 1];
               const uint32_t (&uu)[16] = u[c & 1];
               __nv_bfloat16* dst = p.out + ((long long)t.row0 + row) * p.out_stride + f0 + ch * 64 + (c & 3) * 16;
@@ -397,8 +407,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                   o[4 * q8 + 2] = prmt(b, d, 0x5410); o[4 * q8 + 3] = prmt(b, d, 0x7632);
                 }
               }
-              reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-              reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+              if (!(p.debug & 1)) {
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+              }
             }
           }
         }
@@ -413,23 +425,52 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (c + 1 < nchunks) tmem_ld32(tq + ((c + 1) >> 2) * BN + ch * 128 + ((c + 1) & 3) * 32, acc[(c + 1) & 1]);
             else release();
             const int row = (c >> 2) * BM + quarter * 32 + lane;
-            if (row < t.nrows) {
+            if ((kStaged || row < t.nrows) && !(p.debug & 2)) {
               const long long grow = (long long)t.row0 + row;
-              const float wr = p.route_weight ? p.route_weight[grow] : 1.f;
+              const float wr = row < t.nrows && p.route_weight ? p.route_weight[grow] : 1.f;
               const uint32_t (&a)[32] = acc[c & 1];
-              __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + ch * 128 + (c & 3) * 32;
               uint32_t o[16];
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
                 const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(a[j]) * wr, __uint_as_float(a[j + 1]) * wr);
                 o[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
               }
+              if (kStaged) {
+                // two chunks = 32 rows x 128 B per piece, pieces in turn: 16-byte slot q of row r at r*128 + ((q ^ r&7) << 4)
+                uint8_t* piece = stage_piece_of((c >> 1) & 1) + lane * 128;
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                for (int i = 0; i < 4; ++i)
+                  *reinterpret_cast<uint4*>(piece + ((((c & 1) * 4 + i) ^ (lane & 7)) << 4)) =
+                      make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              } else if (!(p.debug & 1)) {
+                __nv_bfloat16* dst = p.out + grow * p.out_stride + f0 + ch * 128 + (c & 3) * 32;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              }
+            }
+            if (kStaged && (c & 1)) {
+              // a piece is full: eight lanes write one row's 128 contiguous bytes, four rows per instruction.  The
+              // __syncwarp before the other piece's flush also orders these reads before this piece's next writes.
+              __syncwarp();
+              if (!(p.debug & 3)) {
+                const int q = lane & 7;
+                const uint8_t* piece = stage_piece_of((c >> 1) & 1);
+                __nv_bfloat16* dst = p.out + f0 + ch * 128 + ((c & 3) >> 1) * 64 + q * 8;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const int lr = 4 * j + (lane >> 3);
+                  const int orow = (c >> 2) * BM + quarter * 32 + lr;
+                  if (orow < t.nrows) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(piece + lr * 128 + ((q ^ (lr & 7)) << 4));
+                    *reinterpret_cast<uint4*>(dst + ((long long)t.row0 + orow) * p.out_stride) = v;
+                  }
+                }
+              }
             }
           }
         }
+        if (kStaged) __syncwarp();                           // before this warp's next conversion overwrites its rows
       }
     }
   }
@@ -524,6 +565,7 @@ int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
   p.num_tiles = a.num_tiles; p.tile_expert = a.tile_expert; p.tile_row0 = a.tile_row0; p.tile_rows = a.tile_rows;
   p.max_tiles = a.max_tiles;
   p.out = a.out; p.out_stride = a.out_stride; p.route_weight = a.route_weight; p.permute_out = a.permute_out;
+  { static const int dbg = [] { const char* v = std::getenv("UMAQ_GEMM_DEBUG"); return v ? std::atoi(v) : 0; }(); p.debug = dbg; }
   p.status = a.status;
   p.gather_route = a.gather_route; p.gather_top_k = a.gather_top_k; p.gather_src = static_cast<const __nv_bfloat16*>(a.act);
   const int n_tiles = a.n_rows / (a.mode == 0 ? BN / 2 : BN);

@@ -30,6 +30,7 @@ struct GroupedParams {
   const int* gather_route;
   int gather_top_k;
   const __nv_bfloat16* gather_src;
+  int debug;
 };
 
 struct GroupedGemmArgs {
