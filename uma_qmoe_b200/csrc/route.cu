@@ -765,7 +765,7 @@ __global__ void __launch_bounds__(256, 4)
 combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restrict__ indices, int idx64,
                const int* __restrict__ route_pos, int top_k, int hidden, int experts,
                const __nv_bfloat16* __restrict__ shared_out, const __nv_bfloat16* __restrict__ x,
-               const __nv_bfloat16* __restrict__ gate_vec, __nv_bfloat16* __restrict__ out, const SegmentedOut seg) {
+               const __nv_bfloat16* __restrict__ gate_vec, __nv_bfloat16* __restrict__ out, const __grid_constant__ SegmentedOut seg) {
   __shared__ int order_pos[8];
   __shared__ int present;
   __shared__ float red[8];
@@ -853,6 +853,72 @@ combine_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restric
     o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
     o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
     *reinterpret_cast<uint4*>(dst + c) = o;
+  }
+}
+
+// The same ordered sum without a shared expert, one warp per token: no shared memory and no block barrier, the
+// order of the routes found with shuffles.  A token with one or two present routes (an expert-parallel rank's
+// share) costs a warp a few hundred cycles instead of a block three barriers.
+constexpr int kCombineWarps = 8;
+__global__ void __launch_bounds__(kCombineWarps * 32)
+combine_warp_kernel(const __nv_bfloat16* __restrict__ weighted, const void* __restrict__ indices, int idx64,
+                    const int* __restrict__ route_pos, int tokens, int top_k, int hidden, int experts,
+                    __nv_bfloat16* __restrict__ out, const __grid_constant__ SegmentedOut seg) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
+  if (t >= tokens) return;                                   // the whole warp
+  int e = -1, q = -1;
+  if (lane < top_k) {
+    e = load_expert(indices, idx64, t * top_k + lane);
+    q = route_pos[t * top_k + lane];
+  }
+  const bool valid = lane < top_k && e >= 0 && e < experts && q >= 0;
+  int rank = 0;                                               // among the present routes, by (expert, slot)
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int ej = __shfl_sync(0xffffffffu, e, j);
+    const bool vj = __shfl_sync(0xffffffffu, (int)valid, j);
+    rank += vj && (ej < e || (ej == e && j < lane));
+  }
+  const int n = __popc(__ballot_sync(0xffffffffu, valid));
+  __nv_bfloat16* dst = out + (size_t)t * hidden;
+  if (seg.rows > 0) {                                         // segmented output, possibly in a peer GPU's memory
+    if (seg.skip_empty && n == 0) return;
+    dst = seg.ptr[t / seg.rows] + (size_t)(seg.row0 + t % seg.rows) * hidden;
+  }
+  unsigned rows[8];                                           // row starts in 16-byte words
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    const unsigned m = __ballot_sync(0xffffffffu, valid && rank == s);
+    const int qs = __shfl_sync(0xffffffffu, q, m ? __ffs(m) - 1 : 0);
+    rows[s] = s < n ? (unsigned)(((size_t)qs * hidden) >> 3) : 0u;
+  }
+  const uint4* wbase = reinterpret_cast<const uint4*>(weighted);
+  for (int c = lane; c < (hidden >> 3); c += 32) {            // 16 bytes per lane and row
+    uint4 v[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s < n) v[s] = wbase[rows[s] + c];
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < n) {
+        const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          r[2 * i] = bf16_round(r[2 * i] + __uint_as_float(w[i] << 16));
+          r[2 * i + 1] = bf16_round(r[2 * i + 1] + __uint_as_float(w[i] & 0xffff0000u));
+        }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(r[0], r[1]), p1 = __floats2bfloat162_rn(r[2], r[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(r[4], r[5]), p3 = __floats2bfloat162_rn(r[6], r[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    reinterpret_cast<uint4*>(dst)[c] = o;
   }
 }
 
@@ -949,6 +1015,12 @@ int launch_combine(const __nv_bfloat16* weighted, const void* indices, int idx64
   if (tokens <= 0 || top_k < 1 || top_k > 8 || hidden % 8) { set_error("combine: unsupported shape"); return ERR_BAD_ARGUMENT; }
   SegmentedOut seg{};
   if (segments) seg = *segments;
+  static const int warp_path = [] { const char* v = std::getenv("UMAQ_COMBINE_WARP"); return v ? std::atoi(v) : 1; }();
+  if (!shared_out && warp_path) {
+    combine_warp_kernel<<<(tokens + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, 0, stream>>>(
+        weighted, indices, idx64, route_pos, tokens, top_k, hidden, experts, out, seg);
+    return check_launch("combine");
+  }
   combine_kernel<<<tokens, 256, 0, stream>>>(weighted, indices, idx64, route_pos, top_k, hidden, experts, shared_out, x, gate_vec, out, seg);
   return check_launch("combine");
 }
