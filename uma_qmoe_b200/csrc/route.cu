@@ -290,8 +290,13 @@ __global__ void __launch_bounds__(256) router_tiled_kernel(const RouterArgs a) {
 // bound, with shorter runs).
 constexpr int kRsTokens = 4, kRsWarps = 16, kRsCluster = 8, kRsExperts = 8;      // experts per CTA
 // Most tokens this kernel takes (UMAQ_ROUTER_SMALL_MAX overrides).  Measured on B200, 64 experts: 6 us up to 32
-// tokens, 8 us at 128, 16 us at 256, 26 us at 512 against a constant 20 us of the tensor-core kernel.
-constexpr int kRouterSmallMax = 320;
+// tokens, 8 us at 128, 16 us at 256, 26 us at 512 against a constant 12.7 us of the tensor-core kernel with
+// 32 tokens per CTA.
+constexpr int kRouterSmallMax = 192;
+// From this many tokens on the tensor-core router takes 64 tokens per CTA instead of 32 (UMAQ_ROUTER_WIDE_MIN
+// overrides).  Measured: 32 per CTA 12.7 us up to 4096 tokens and 24 us once its CTAs need a second wave
+// (148 SMs x 32 tokens), 64 per CTA 19.4 to 20 us at any size up to 9472 tokens.
+constexpr int kRouterWideMin = 4737;
 
 __device__ __forceinline__ float dot8_bf16(const uint4& x, const uint4& w) {
   const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ws[4] = {w.x, w.y, w.z, w.w};
@@ -384,16 +389,18 @@ router_small_kernel(const RouterArgs a) {
   }
 }
 
-// Tensor-core router for batches (E <= 64, tokens >= 128): a CTA takes 64 tokens and all experts.
+// Tensor-core router for batches (E <= 64): a CTA takes MT = 32 or 64 tokens and all experts.
 // x and Wr stream through a 6-stage cp.async ring of 128-wide k chunks (16-byte chunks XOR-swizzled by
-// row against bank conflicts); warp (g, h) = (token group of 16, expert half of 32) runs
+// row against bank conflicts); warp (g, h) = (token group of 16, expert half or quarter) runs
 // mma.sync.m16n8k16 BF16 with ldmatrix fragments.  The BF16 products are exact in the FP32 accumulator;
 // a chunk's 128 products are summed by the tensor core in float32, the chunk sums in float64, so the
 // BF16 rounding of the logit equals that of an exactly rounded dot product in all but about one logit
 // in 10^4 (the same bound as the tiled kernel).  The logits then go through the same softmax / top-k.
-constexpr int kRmTokens = 64, kRmChunk = 128, kRmStages = 6;
-constexpr int kRmTile = 64 * kRmChunk * 2;                 // 16 KiB: 64 rows x 256 bytes
-constexpr int kRmSmem = kRmStages * 2 * kRmTile;
+// MT = tokens per CTA: 64 for the largest batches (every CTA re-reads the router matrix from L2), 32 below: the loop
+// is one CTA's dependent chain whose length goes with MT, so more and shorter CTAs finish sooner.
+constexpr int kRmChunk = 128, kRmStages = 6;
+constexpr int kRmTile = 64 * kRmChunk * 2;                 // 16 KiB: 64 rows x 256 bytes (the router matrix's chunk)
+constexpr int rm_smem_bytes(int mt) { return kRmStages * (mt * kRmChunk * 2 + kRmTile); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -401,12 +408,20 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_
                : "r"(addr));
 }
 
+template <int MT>
 __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
   extern __shared__ __align__(128) uint8_t rm_smem[];
+  constexpr int kGroups = MT / 16;                         // token groups of 16
+  constexpr int kPerGroup = 8 / kGroups;                   // warps sharing a token group
+  constexpr int kWarpExperts = 64 / kPerGroup;             // experts of a warp: 32 (MT 64) or 16 (MT 32)
+  constexpr int NJ = kWarpExperts / 8;                     // n-tiles of a warp
+  constexpr int kXTile = MT * kRmChunk * 2, kStage = kXTile + kRmTile;
+  constexpr int kXPieces = MT * 16 / 256;                  // 16-byte pieces of the token tile per thread and chunk
+  static_assert(MT == 64 || MT == 32, "token tile");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int token0 = blockIdx.x * kRmTokens;
+  const int token0 = blockIdx.x * MT;
   const int H = a.hidden, E = a.experts, nchunks = H / kRmChunk;
-  const int g = warp >> 1, h = warp & 1;                   // tokens 16g.., experts 32h..
+  const int g = warp / kPerGroup, h = warp % kPerGroup;    // tokens 16g.., experts kWarpExperts*h..
 
   // per thread: four 16-byte pieces of the token tile and of the router matrix per chunk; everything that does not
   // depend on the chunk is computed once (the loop is one CTA's dependent chain, every instruction in it counts)
@@ -420,24 +435,25 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
     const int t = token0 + r;
     x_ok[i] = t < a.tokens;
     w_ok[i] = r < E;
+    x_ok[i] = x_ok[i] && i < kXPieces;
     x_src[i] = reinterpret_cast<const uint8_t*>(a.x + (size_t)(x_ok[i] ? t : 0) * H + c * 8);
     w_src[i] = reinterpret_cast<const uint8_t*>(a.weight + (size_t)(w_ok[i] ? r : 0) * H + c * 8);
     piece_dst[i] = (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4));
   }
   auto load_chunk = [&](int kc, int stage) {
-    uint8_t* xs = rm_smem + stage * 2 * kRmTile;
-    uint8_t* ws = xs + kRmTile;
+    uint8_t* xs = rm_smem + stage * kStage;
+    uint8_t* ws = xs + kXTile;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      cp_async16(xs + piece_dst[i], x_src[i] + kc * (kRmChunk * 2), x_ok[i]);
+      if (i < kXPieces) cp_async16(xs + piece_dst[i], x_src[i] + kc * (kRmChunk * 2), x_ok[i]);
       cp_async16(ws + piece_dst[i], w_src[i] + kc * (kRmChunk * 2), w_ok[i]);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  double acc[4][4];
+  double acc[NJ][4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+  for (int j = 0; j < NJ; ++j)
 #pragma unroll
     for (int q = 0; q < 4; ++q) acc[j][q] = 0.0;
 
@@ -446,22 +462,22 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
   }
   // ldmatrix row / chunk of this lane: A = 16 tokens x 16 k, B = 2 n-tiles (16 experts) x 16 k
   const int a_row = g * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_sel = lane >> 4;
-  const int b_row = h * 32 + (lane & 7) + ((lane >> 4) & 1) * 8, b_sel = (lane >> 3) & 1;
+  const int b_row = h * kWarpExperts + (lane & 7) + ((lane >> 4) & 1) * 8, b_sel = (lane >> 3) & 1;
   uint32_t a_off[kRmChunk / 16], b_off[kRmChunk / 16];   // swizzled offsets of this lane's ldmatrix rows, per k step
 #pragma unroll
   for (int k16 = 0; k16 < kRmChunk / 16; ++k16) {
     a_off[k16] = (uint32_t)(a_row * 256 + (((k16 * 2 + a_sel) ^ (a_row & 7)) << 4));
-    b_off[k16] = (uint32_t)(kRmTile + b_row * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4));
+    b_off[k16] = (uint32_t)(kXTile + b_row * 256 + (((k16 * 2 + b_sel) ^ (b_row & 7)) << 4));
   }
   for (int kc = 0; kc < nchunks; ++kc) {
     asm volatile("cp.async.wait_group %0;" ::"n"(kRmStages - 2) : "memory");
     __syncthreads();                                       // chunk kc has landed; chunk kc - 1's buffer is free
     if (kc + kRmStages - 1 < nchunks) load_chunk(kc + kRmStages - 1, (kc + kRmStages - 1) % kRmStages);
     else asm volatile("cp.async.commit_group;" ::: "memory");
-    const uint32_t xs = smem_u32(rm_smem + (kc % kRmStages) * 2 * kRmTile);
-    float part[4][4];
+    const uint32_t xs = smem_u32(rm_smem + (kc % kRmStages) * kStage);
+    float part[NJ][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int q = 0; q < 4; ++q) part[j][q] = 0.f;
 #pragma unroll
@@ -469,12 +485,12 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
       uint32_t a0, a1, a2, a3, b[8];
       ldmatrix_x4(xs + a_off[k16], a0, a1, a2, a3);
       ldmatrix_x4(xs + b_off[k16], b[0], b[1], b[2], b[3]);
-      ldmatrix_x4(xs + b_off[k16] + 16 * 256, b[4], b[5], b[6], b[7]);
+      if (NJ == 4) ldmatrix_x4(xs + b_off[k16] + 16 * 256, b[4], b[5], b[6], b[7]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) mma_bf16_16816(part[j], a0, a1, a2, a3, b[2 * j], b[2 * j + 1]);
+      for (int j = 0; j < NJ; ++j) mma_bf16_16816(part[j], a0, a1, a2, a3, b[2 * j], b[2 * j + 1]);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[j][q] += (double)part[j][q];
   }
@@ -482,10 +498,10 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
   __syncthreads();                                         // every warp is done with the ring: reuse it for logits
   float (*logit)[kRtExperts + 1] = reinterpret_cast<float (*)[kRtExperts + 1]>(rm_smem);
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+  for (int j = 0; j < NJ; ++j)
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const int r = g * 16 + (lane >> 2) + (q >> 1) * 8, e = h * 32 + j * 8 + (lane & 3) * 2 + (q & 1);
+      const int r = g * 16 + (lane >> 2) + (q >> 1) * 8, e = h * kWarpExperts + j * 8 + (lane & 3) * 2 + (q & 1);
       const float l = bf16_round((float)acc[j][q]);        // F.linear output in BF16
       logit[r][e] = l;
       const int t = token0 + r;
@@ -493,7 +509,7 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
     }
   __syncthreads();
   if (a.top_k <= 8) {
-    for (int r = warp * 4 + (lane >> 3); r < kRmTokens; r += 32) {     // the loop count is the same for every lane
+    for (int r = warp * 4 + (lane >> 3); r < MT; r += 32) {            // the loop count is the same for every lane
       const int t = token0 + r;
       const bool live = t < a.tokens;
       softmax_topk_oct(logit[r], live, E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)(live ? t : 0) * a.top_k,
@@ -501,7 +517,7 @@ __global__ void __launch_bounds__(256) router_mma_kernel(const RouterArgs a) {
     }
     return;
   }
-  for (int r = warp; r < kRmTokens; r += 8) {
+  for (int r = warp; r < MT; r += 8) {
     const int t = token0 + r;
     if (t < a.tokens)
       softmax_topk_warp(logit[r], E, a.top_k, a.renormalize, lane, a.out_weights + (size_t)t * a.top_k,
@@ -955,11 +971,17 @@ int launch_router_topk(const RouterArgs& a, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured != dev) {
-      cudaError_t e = cudaFuncSetAttribute(router_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRmSmem);
+      cudaError_t e = cudaFuncSetAttribute(router_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, rm_smem_bytes(64));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(router_mma_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, rm_smem_bytes(32));
       if (e != cudaSuccess) { set_error("router: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
       configured = dev;
     }
-    router_mma_kernel<<<(a.tokens + kRmTokens - 1) / kRmTokens, 256, kRmSmem, stream>>>(a);
+    static const int wide_min = [] { const char* v = std::getenv("UMAQ_ROUTER_WIDE_MIN"); return v ? std::atoi(v) : kRouterWideMin; }();
+    if (a.tokens >= wide_min)
+      router_mma_kernel<64><<<(a.tokens + 63) / 64, 256, rm_smem_bytes(64), stream>>>(a);
+    else
+      router_mma_kernel<32><<<(a.tokens + 31) / 32, 256, rm_smem_bytes(32), stream>>>(a);
     return check_launch("router");
   }
   const size_t small_smem = (size_t)kRsTokens * a.hidden * 2;
