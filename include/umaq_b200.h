@@ -236,10 +236,15 @@ typedef struct umaq_ep_peers {
  * buffer); the activation row goes to the same row of p's row table (rows_offset) only when p owns at
  * least one of the token's experts (placement as in umaq_ep_local_ids).  present[i*ranks + p] = p if the
  * row was sent, else -1: the table the final combine uses to skip ranks that hold none of a token's
- * experts.  Replaces an all-gather of rows, ids and weights. */
+ * experts.  Replaces an all-gather of rows, ids and weights.  flags: UMAQ_EP_LOCAL_IDS writes into p's id table
+ * what umaq_ep_local_ids would compute there (the id local to p, -1 for routes of other ranks), so that p needs no
+ * pass of its own; UMAQ_EP_K_PERMUTED writes the rows in the k order the quantised GEMMs read
+ * ([k0,k4,k1,k5,k2,k6,k3,k7] per run of 8; see umaq_moe_prefill_to_peers' rows_k_permuted). */
+#define UMAQ_EP_LOCAL_IDS 1
+#define UMAQ_EP_K_PERMUTED 2
 int umaq_ep_push(const void* hidden_bf16 /* device [tokens, hidden] */, const void* expert_indices, int indices_are_int64,
                  const float* routing_weights, int tokens, int top_k, int hidden, int experts_per_rank, int placement,
-                 const umaq_ep_peers* peers, size_t rows_offset, size_t ids_offset, size_t weights_offset,
+                 int flags, const umaq_ep_peers* peers, size_t rows_offset, size_t ids_offset, size_t weights_offset,
                  int* present /* device [tokens, ranks] */, void* stream);
 /* Barrier across the ranks' streams: writes the next epoch number into every peer's flag word for this
  * rank (at flags_offset, one uint32 per rank, zero at start) and waits until every peer's word for this
@@ -252,11 +257,12 @@ int umaq_ep_barrier(const umaq_ep_peers* peers, size_t flags_offset, unsigned* e
  * this rank, -1 for routes other ranks own), with the combine writing token (p, i)'s ordered partial sum
  * straight into row rank*segment_rows + i of rank p's parts table (parts_offset) instead of a local
  * tensor followed by an all-to-all.  Tokens without a route on this rank are not written; the reader
- * skips them through the `present` table of umaq_ep_push. */
+ * skips them through the `present` table of umaq_ep_push.  rows_k_permuted != 0: the rows were pushed with
+ * UMAQ_EP_K_PERMUTED and the operator's own permutation pass is skipped (quantised layers only). */
 int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, const void* expert_indices,
                               int indices_are_int64, const float* routing_weights, long long tokens, int top_k,
-                              const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, void* workspace,
-                              size_t workspace_bytes, void* stream);
+                              const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, int rows_k_permuted,
+                              void* workspace, size_t workspace_bytes, void* stream);
 /* out[t] = BF16 running sum of weighted[route_pos[t*top_k+s]] over the token's routes in
  * ascending expert order: the accumulation order of the reference's CPU path
  * (src/uma_qmoe/custom_op.py:312-338), in place of

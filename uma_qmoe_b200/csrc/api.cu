@@ -201,14 +201,15 @@ int umaq_ep_local_ids(const void* expert_indices, int indices_are_int64, long lo
 }
 
 int umaq_ep_push(const void* hidden_bf16, const void* expert_indices, int indices_are_int64, const float* routing_weights,
-                 int tokens, int top_k, int hidden, int experts_per_rank, int placement, const umaq_ep_peers* peers,
-                 size_t rows_offset, size_t ids_offset, size_t weights_offset, int* present, void* stream) {
+                 int tokens, int top_k, int hidden, int experts_per_rank, int placement, int flags,
+                 const umaq_ep_peers* peers, size_t rows_offset, size_t ids_offset, size_t weights_offset, int* present,
+                 void* stream) {
   if (!hidden_bf16 || !expert_indices || !routing_weights || !peers || !present) {
     set_error("umaq_ep_push: null argument");
     return ERR_BAD_ARGUMENT;
   }
   return launch_ep_push(static_cast<const __nv_bfloat16*>(hidden_bf16), expert_indices, indices_are_int64, routing_weights,
-                        tokens, top_k, hidden, experts_per_rank, placement, *peers, rows_offset, ids_offset, weights_offset,
+                        tokens, top_k, hidden, experts_per_rank, placement, flags, *peers, rows_offset, ids_offset, weights_offset,
                         present, static_cast<cudaStream_t>(stream));
 }
 
@@ -289,7 +290,7 @@ size_t umaq_prefill_workspace_bytes(long long tokens, int top_k, int num_experts
 static int prefill_impl(const umaq_layer* layer, const umaq_shared_expert* shared, const void* hidden_bf16,
                         const void* expert_indices, int indices_are_int64, const float* routing_weights, long long tokens,
                         int top_k, void* out_bf16, void* workspace, size_t workspace_bytes, void* stream_,
-                        const SegmentedOut* segments) {
+                        const SegmentedOut* segments, bool rows_k_permuted = false) {
   if (!layer || !hidden_bf16 || !expert_indices || !routing_weights || (!out_bf16 && !segments) || !workspace || tokens <= 0) {
     set_error("umaq_moe_prefill: null argument");
     return ERR_BAD_ARGUMENT;
@@ -337,7 +338,7 @@ static int prefill_impl(const umaq_layer* layer, const umaq_shared_expert* share
     // The gate/up GEMM fetches its activation rows by index: no [routes, H] copy of the activations exists.  The
     // quantised kernels want k in the order their conversion produces, so x is permuted once (tokens rows, not routes).
     const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(hidden_bf16);
-    if (quant) {
+    if (quant && !rows_k_permuted) {
       rc = launch_gather_rows(src, nullptr, 1, tokens, H, 1, xs, nullptr, stream);
       if (rc) return rc;
       src = xs;
@@ -394,8 +395,8 @@ int umaq_moe_prefill(const umaq_layer* layer, const umaq_shared_expert* shared, 
 
 int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, const void* expert_indices,
                               int indices_are_int64, const float* routing_weights, long long tokens, int top_k,
-                              const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, void* workspace,
-                              size_t workspace_bytes, void* stream_) {
+                              const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, int rows_k_permuted,
+                              void* workspace, size_t workspace_bytes, void* stream_) {
   if (!peers || peers->ranks < 1 || peers->ranks > kMaxPeers || peers->rank < 0 || peers->rank >= peers->ranks ||
       segment_rows < 1 || tokens != (long long)segment_rows * peers->ranks || !layer) {
     set_error("umaq_moe_prefill_to_peers: bad peer table or segment size");
@@ -409,8 +410,18 @@ int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, 
   seg.rows = segment_rows;
   seg.row0 = peers->rank * segment_rows;
   seg.skip_empty = 1;
+  if (rows_k_permuted) {
+    // only the by-index gate/up GEMM of a quantised layer reads its rows in that order
+    GroupedGemmArgs g{};
+    g.mode = 0; g.enc = layer->encoding; g.num_experts = layer->num_experts; g.n_rows = layer->intermediate; g.k = layer->hidden;
+    g.total_rows = tokens * top_k;
+    if (layer->encoding == ENC_BF16 || !grouped_gemm_can_gather(g)) {
+      set_error("umaq_moe_prefill_to_peers: rows_k_permuted needs a quantised layer the gate/up GEMM reads by index");
+      return ERR_BAD_ARGUMENT;
+    }
+  }
   return prefill_impl(layer, nullptr, hidden_bf16, expert_indices, indices_are_int64, routing_weights, tokens, top_k,
-                      nullptr, workspace, workspace_bytes, stream_, &seg);
+                      nullptr, workspace, workspace_bytes, stream_, &seg, rows_k_permuted != 0);
 }
 
 }  // extern "C"

@@ -17,7 +17,7 @@ struct PushArgs {
   const void* idx;
   int idx64;
   const float* w;
-  int tokens, top_k, hidden, per_rank, placement;
+  int tokens, top_k, hidden, per_rank, placement, flags;
   umaq_ep_peers peers;
   size_t rows_offset, ids_offset, weights_offset;
   int* present;
@@ -44,7 +44,13 @@ __global__ void __launch_bounds__(kPushWarps * 32) ep_push_kernel(const PushArgs
   if (lane < a.top_k) {
     e = a.idx64 ? (int)reinterpret_cast<const long long*>(a.idx)[(size_t)i * a.top_k + lane]
                 : reinterpret_cast<const int*>(a.idx)[(size_t)i * a.top_k + lane];
-    reinterpret_cast<int*>(base + a.ids_offset)[row * a.top_k + lane] = e;
+    // with UMAQ_EP_LOCAL_IDS the destination gets the id it would compute itself: local to it, or -1
+    int id = e;
+    if (a.flags & 1) {
+      const bool theirs = owner_of(e, G, a.per_rank, a.placement) == p;
+      id = !theirs ? -1 : (a.placement == 0 ? e / G : e - p * a.per_rank);
+    }
+    reinterpret_cast<int*>(base + a.ids_offset)[row * a.top_k + lane] = id;
     reinterpret_cast<float*>(base + a.weights_offset)[row * a.top_k + lane] = a.w[(size_t)i * a.top_k + lane];
   }
   const bool mine = lane < a.top_k && owner_of(e, G, a.per_rank, a.placement) == p;
@@ -59,6 +65,14 @@ __global__ void __launch_bounds__(kPushWarps * 32) ep_push_kernel(const PushArgs
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       if (b + j * 32 + lane < words) v[j] = src[b + j * 32 + lane];
+    if (a.flags & 2) {
+      // k order of the quantised GEMMs: (k0,k1)(k2,k3)(k4,k5)(k6,k7) -> (k0,k4)(k1,k5)(k2,k6)(k3,k7) per run of 8
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 n = v[j];
+        v[j] = make_uint4(prmt(n.x, n.z, 0x5410), prmt(n.x, n.z, 0x7632), prmt(n.y, n.w, 0x5410), prmt(n.y, n.w, 0x7632));
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       if (b + j * 32 + lane < words) dst[b + j * 32 + lane] = v[j];
@@ -103,9 +117,9 @@ __global__ void ep_barrier_kernel(const umaq_ep_peers peers, size_t flags_offset
 }  // namespace
 
 int launch_ep_push(const __nv_bfloat16* x, const void* indices, int idx64, const float* weights, int tokens, int top_k,
-                   int hidden, int per_rank, int placement, const umaq_ep_peers& peers, size_t rows_offset,
+                   int hidden, int per_rank, int placement, int flags, const umaq_ep_peers& peers, size_t rows_offset,
                    size_t ids_offset, size_t weights_offset, int* present, cudaStream_t stream) {
-  if (tokens <= 0 || top_k < 1 || top_k > 32 || hidden % 8 || per_rank < 1 || (placement != 0 && placement != 1) ||
+  if (tokens <= 0 || top_k < 1 || top_k > 32 || hidden % 8 || per_rank < 1 || (placement != 0 && placement != 1) || (flags & ~3) ||
       peers.ranks < 1 || peers.ranks > kMaxPeers || peers.rank < 0 || peers.rank >= peers.ranks ||
       (rows_offset & 15) || (ids_offset & 3) || (weights_offset & 3)) {
     set_error("ep push: unsupported shape or peer table");
@@ -113,7 +127,7 @@ int launch_ep_push(const __nv_bfloat16* x, const void* indices, int idx64, const
   }
   for (int p = 0; p < peers.ranks; ++p)
     if (!peers.base[p]) { set_error("ep push: null peer buffer"); return ERR_BAD_ARGUMENT; }
-  PushArgs a{x, indices, idx64, weights, tokens, top_k, hidden, per_rank, placement, peers, rows_offset, ids_offset,
+  PushArgs a{x, indices, idx64, weights, tokens, top_k, hidden, per_rank, placement, flags, peers, rows_offset, ids_offset,
              weights_offset, present};
   ep_push_kernel<<<dim3((tokens + kPushWarps - 1) / kPushWarps, peers.ranks), kPushWarps * 32, 0, stream>>>(a);
   const cudaError_t e = cudaGetLastError();

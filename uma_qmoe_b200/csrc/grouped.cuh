@@ -101,7 +101,7 @@ int launch_ep_local_ids(const void* indices, int idx64, long long n, int ranks, 
                         int* out, cudaStream_t stream);
 // expert-parallel exchange over peer memory (ep_peer.cu)
 int launch_ep_push(const __nv_bfloat16* x, const void* indices, int idx64, const float* weights, int tokens, int top_k,
-                   int hidden, int per_rank, int placement, const umaq_ep_peers& peers, size_t rows_offset,
+                   int hidden, int per_rank, int placement, int flags, const umaq_ep_peers& peers, size_t rows_offset,
                    size_t ids_offset, size_t weights_offset, int* present, cudaStream_t stream);
 int launch_ep_barrier(const umaq_ep_peers& peers, size_t flags_offset, unsigned* epoch, unsigned* status,
                       cudaStream_t stream);

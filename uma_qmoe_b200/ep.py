@@ -83,13 +83,25 @@ class CudaKernels:
     def local_ids(self, indices: torch.Tensor, ranks: int, rank: int, per_rank: int, interleaved: bool) -> torch.Tensor:
         return self.ops.ep_local_ids(indices, ranks, rank, per_rank, interleaved)
 
+    @property
+    def rows_k_permuted(self) -> bool:
+        """Quantised layers read their activation rows in a permuted k order; the push can write that order."""
+        return self.layer.encoding != "bf16_le"
+
+    @property
+    def push_flags(self) -> int:
+        """The sender does the receiver's two preparation passes: ids local to the destination, rows in k order."""
+        return self.ops.EP_LOCAL_IDS | (self.ops.EP_K_PERMUTED if self.rows_k_permuted else 0)
+
     def local_moe_to_peers(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor, ex: Any) -> None:
-        """Like :meth:`local_moe`, but every token's partial sum goes straight into its owner rank's buffer."""
+        """Like :meth:`local_moe`, but every token's partial sum goes straight into its owner rank's buffer; ``x``
+        and ``local_indices`` as :attr:`push_flags` made the senders write them."""
         n, top_k = local_indices.shape
         if self._ws_moe is None or self._ws_moe_shape != (n, top_k):
             self._ws_moe = self.ops.prefill_workspace(self.layer, n, top_k, None, x.device)
             self._ws_moe_shape = (n, top_k)
-        self.ops.moe_prefill_to_peers(self.layer, x, local_indices, weights, ex.peers, ex.off_parts, ex.tokens, self._ws_moe)
+        self.ops.moe_prefill_to_peers(self.layer, x, local_indices, weights, ex.peers, ex.off_parts, ex.tokens, self._ws_moe,
+                                      rows_k_permuted=self.rows_k_permuted)
 
     def local_moe(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """This rank's experts over all rows of x; local_indices -1 = the route belongs to another rank."""
@@ -271,14 +283,12 @@ class ExpertParallelMoE:
     def peer_push(self, ex: PeerExchange, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor) -> None:
         """Phase 1: this rank's rows (to the ranks that own one of the token's experts) and routes (to all)."""
         self.kernels.ops.ep_push(x, indices, weights, self.per_rank, self.placement == "interleaved", ex.peers,
-                                 ex.off_rows, ex.off_ids, ex.off_w, ex.present)
+                                 ex.off_rows, ex.off_ids, ex.off_w, ex.present, flags=self.kernels.push_flags)
 
     def peer_compute(self, ex: PeerExchange) -> None:
         """Phase 2: this rank's experts over everything that was pushed to it; the combine writes every token's
         partial sum into its owner's buffer."""
-        k = self.kernels
-        local = k.local_ids(ex.all_idx, self.world, self.rank, self.per_rank, self.placement == "interleaved")
-        k.local_moe_to_peers(ex.all_x, local, ex.all_w, ex)
+        self.kernels.local_moe_to_peers(ex.all_x, ex.all_idx, ex.all_w, ex)     # the ids arrived local to this rank
 
     def peer_combine(self, ex: PeerExchange) -> torch.Tensor:
         """Phase 3: the partial sums of the ranks that worked on a token, added in rank order."""

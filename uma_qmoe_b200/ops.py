@@ -285,9 +285,15 @@ def ep_peers(pointers: list[int], rank: int) -> _native.EpPeers:
     return table
 
 
+EP_LOCAL_IDS, EP_K_PERMUTED = 1, 2          # flags of umaq_ep_push
+
+
 def ep_push(hidden: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, experts_per_rank: int, interleaved: bool,
-            peers: _native.EpPeers, rows_offset: int, ids_offset: int, weights_offset: int, present: torch.Tensor) -> None:
-    """Rows and routes of the local tokens into every rank's buffer (see ``umaq_ep_push``)."""
+            peers: _native.EpPeers, rows_offset: int, ids_offset: int, weights_offset: int, present: torch.Tensor,
+            flags: int = 0) -> None:
+    """Rows and routes of the local tokens into every rank's buffer (see ``umaq_ep_push``).  ``flags``:
+    ``EP_LOCAL_IDS`` = the ids arrive local to their destination (-1 for other ranks' routes), ``EP_K_PERMUTED`` =
+    the rows arrive in the k order of the quantised GEMMs."""
     _require_cuda_bf16(hidden, "hidden_states")
     tokens, top_k = indices.shape
     if weights.dtype != torch.float32 or weights.shape != indices.shape or indices.dtype not in (torch.int32, torch.int64):
@@ -296,7 +302,7 @@ def ep_push(hidden: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, 
         raise RuntimeError("present must be int32 [tokens, ranks]")
     code = _native.lib().umaq_ep_push(hidden.data_ptr(), indices.contiguous().data_ptr(), int(indices.dtype == torch.int64),
                                       weights.contiguous().data_ptr(), tokens, top_k, hidden.shape[1], experts_per_rank,
-                                      0 if interleaved else 1, C.byref(peers), rows_offset, ids_offset, weights_offset,
+                                      0 if interleaved else 1, flags, C.byref(peers), rows_offset, ids_offset, weights_offset,
                                       present.data_ptr(), _stream(hidden.device))
     _native.check(code, "umaq_ep_push")
 
@@ -309,13 +315,14 @@ def ep_barrier(peers: _native.EpPeers, flags_offset: int, epoch: torch.Tensor, s
 
 
 def moe_prefill_to_peers(layer: DeviceLayer, hidden: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor,
-                         peers: _native.EpPeers, parts_offset: int, segment_rows: int, workspace: torch.Tensor) -> None:
+                         peers: _native.EpPeers, parts_offset: int, segment_rows: int, workspace: torch.Tensor,
+                         rows_k_permuted: bool = False) -> None:
     """This rank's experts over the pushed rows of all ranks, partial sums written into the owners' buffers."""
     _require_cuda_bf16(hidden, "hidden_states")
     tokens, top_k = local_indices.shape
     code = _native.lib().umaq_moe_prefill_to_peers(
         C.byref(layer.struct()), hidden.data_ptr(), local_indices.data_ptr(), int(local_indices.dtype == torch.int64),
-        weights.data_ptr(), tokens, top_k, C.byref(peers), parts_offset, segment_rows, workspace.data_ptr(),
+        weights.data_ptr(), tokens, top_k, C.byref(peers), parts_offset, segment_rows, int(rows_k_permuted), workspace.data_ptr(),
         workspace.numel(), _stream(hidden.device))
     _native.check(code, "umaq_moe_prefill_to_peers")
 
