@@ -320,34 +320,83 @@ def native_arm(args) -> None:
     else:
         from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE, PeerExchange
         dist = torch.distributed
-        eps = [ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k) for layer in stack.layers]
+        # The rank's tokens go through the stack as `parts` independent micro-batches, each on a stream of its own with
+        # its own exchange buffer and workspaces: while one part's experts hold the tensor cores, the other part's
+        # router, push, barriers and combines (NVLink- and latency-bound) run beside them.  Tokens never interact, so
+        # the parts only meet again in the result.
+        parts = max(1, int(os.environ.get("UMAQ_EP_PARTS", "2")))
+        if share % parts:
+            parts = 1
+        piece = share // parts
+        eps_of = [[ExpertParallelMoE(CudaKernels(layer, shape.top_k), shape.experts, shape.top_k) for layer in stack.layers]
+                  for _ in range(parts)]
+        eps = eps_of[0]
         # Exchange over peer memory (this library's own push / combine kernels on buffers every rank has mapped) when
         # all ranks can map them; otherwise the collective-library exchange (all-gather + all-to-all).
-        ex, why = None, ""
+        exs, why = None, ""
         if os.environ.get("UMAQ_EP_EXCHANGE", "peer") == "peer":
             try:
-                ex = PeerExchange(share, shape.hidden, shape.top_k, rank, world, dev)
+                exs = [PeerExchange(piece, shape.hidden, shape.top_k, rank, world, dev) for _ in range(parts)]
             except Exception as exc:
                 why = f"{type(exc).__name__}: {exc}"[:160]
-        ok = torch.tensor([1 if ex is not None else 0], device=dev)
+        ok = torch.tensor([1 if exs is not None else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if not int(ok.item()):
-            ex = None
+            exs, parts, piece = None, 1, share             # the collectives of two parts would have to be ordered
+        ex = exs[0] if exs is not None else None
         exchange_name = ("peer memory: rows pushed to the ranks that own one of the token's experts, partial sums written "
                          "into the owner's buffer by the combine kernel, flag barriers (no collective on the data path)"
-                         if ex is not None else "all_gather rows + all_to_all partial sums (NCCL)" + (f"; peer mapping failed: {why}" if why else ""))
+                         + (f"; {parts} micro-batches of {piece} tokens per rank on streams of their own" if parts > 1 else "")
+                         if exs is not None else "all_gather rows + all_to_all partial sums (NCCL)" + (f"; peer mapping failed: {why}" if why else ""))
         dist.barrier()
+        side = [torch.cuda.Stream() for _ in range(parts - 1)]
+
+        def part_layer(h, l, x, w, idx):
+            return eps_of[h][l].forward_peer(exs[h], x, idx, w) if exs is not None else eps_of[h][l].forward_gather(x, idx, w)
+
+        def on_parts(x, stages, stage):
+            """rows = stage(h, i, rows) for i < stages on every part h of x, part h on its own stream; the host issues
+            stage i of every part before stage i + 1 of any, so that no part's launches queue up behind another's.
+            The results are joined on the current stream."""
+            if parts == 1:
+                for i in range(stages):
+                    x = stage(0, i, x)
+                return x
+            main = torch.cuda.current_stream()
+            streams = [main] + side
+            fork = torch.cuda.Event()
+            fork.record(main)
+            out = torch.empty_like(x)
+            rows = [x[h * piece:(h + 1) * piece] for h in range(parts)]
+            for s in side:
+                s.wait_event(fork)
+                x.record_stream(s)
+                out.record_stream(s)
+            for i in range(stages):
+                for h in range(parts):
+                    with torch.cuda.stream(streams[h]):
+                        rows[h] = stage(h, i, rows[h])
+            for h in range(parts):
+                with torch.cuda.stream(streams[h]):
+                    out[h * piece:(h + 1) * piece].copy_(rows[h])
+                    if h:
+                        done = torch.cuda.Event()
+                        done.record(streams[h])
+                        main.wait_event(done)
+            return out
 
         def layer_forward(l, x, w, idx):
-            return eps[l].forward_peer(ex, x, idx, w) if ex is not None else eps[l].forward_gather(x, idx, w)
+            """One layer over all of this rank's tokens through the measured exchange (the parts side by side)."""
+            return on_parts(x, 1, lambda h, i, rows: part_layer(h, l, rows, w[h * piece:(h + 1) * piece],
+                                                                idx[h * piece:(h + 1) * piece]))
 
         def run_stack(x):
-            for l in range(LAYERS):
-                w, idx = stack.route(l, x)
-                x = rms_renorm(layer_forward(l, x, w, idx))
-            return x
-        # router; push, barrier, routing table, sort (2), gather, 2 GEMMs, combine to peers, barrier, final combine
-        launches_per_step = LAYERS * (12 if ex is not None else 8)
+            def stage(h, l, rows):
+                w, idx = stack.route(l, rows)
+                return rms_renorm(part_layer(h, l, rows, w, idx))
+            return on_parts(x, LAYERS, stage)
+        # router; push, barrier, sort (2), 2 GEMMs, combine to peers, barrier, final combine; per part
+        launches_per_step = LAYERS * parts * (10 if exs is not None else 8)
 
     def step_resident():
         run_stack(x_dev)
@@ -446,9 +495,10 @@ def native_arm(args) -> None:
         line["cpu_baseline"] = cpu_baseline_subprocess()
     if world > 1:
         line["ep_check"] = ep_check(stack, eps, ex, layer_forward, x_dev, shape, dev, world)
-        line["phases_us"] = ep_phases(stack, eps, ex, x_dev, shape, dev, world)
-        if ex is not None:
-            line["ep_check"]["barrier_timed_out"] = ex.timed_out()
+        line["phases_us"] = ep_phases(stack, eps, ex, x_dev[:piece].contiguous(), shape, dev, world)
+        line["phases_us"]["tokens_per_rank_and_micro_batch"] = piece
+        if exs is not None:
+            line["ep_check"]["barrier_timed_out"] = any(e.timed_out() for e in exs)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
