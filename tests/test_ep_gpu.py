@@ -150,6 +150,39 @@ def test_peer_exchange_with_every_rank_on_one_gpu(ranks, placement):
         assert torch.equal(exs[r].present >= 0, expect)
 
 
+@pytest.mark.parametrize("placement", ["interleaved", "contiguous"])
+def test_push_prepares_the_receivers_input(placement):
+    """With UMAQ_EP_LOCAL_IDS | UMAQ_EP_K_PERMUTED the id table a rank receives equals what ``ep_local_ids`` makes of
+    the global ids there, and the rows it receives equal the k-permutation ``gather_rows`` makes of the senders' rows;
+    without the flags both arrive unchanged.  Rows of tokens with no expert on the rank are not pushed."""
+    from uma_qmoe_b200 import ops
+    from uma_qmoe_b200.ep import PeerExchange
+    ranks, top_k, t, experts = 4, 4, 37, 8
+    per = experts // ranks
+    gen = torch.Generator().manual_seed(SEED + 211)
+    idx = torch.multinomial(torch.ones(ranks * t, experts), top_k, replacement=False, generator=gen).to(torch.int32).to(DEV)
+    idx[5, 1] = -1                                              # an absent route stays absent everywhere
+    w = torch.rand((ranks * t, top_k), generator=gen, dtype=torch.float32).to(DEV)
+    x = syn.activations(SEED + 212, ranks * t).to(DEV)
+    nbytes = PeerExchange.nbytes_for(t, 2048, top_k, ranks)
+    for flags in (0, ops.EP_LOCAL_IDS | ops.EP_K_PERMUTED):
+        buffers = [torch.full((nbytes,), 0xFF, dtype=torch.uint8, device=DEV) for _ in range(ranks)]
+        exs = [PeerExchange(t, 2048, top_k, r, ranks, torch.device(DEV), buffers=buffers) for r in range(ranks)]
+        for r in range(ranks):
+            rows = slice(r * t, (r + 1) * t)
+            ops.ep_push(x[rows].contiguous(), idx[rows].contiguous(), w[rows].contiguous(), per, placement == "interleaved",
+                        exs[r].peers, exs[r].off_rows, exs[r].off_ids, exs[r].off_w, exs[r].present, flags=flags)
+        torch.cuda.synchronize()
+        x_want = ops.gather_rows(x, None, 1, permute=True) if flags else x
+        for p in range(ranks):
+            local = ops.ep_local_ids(idx, ranks, p, per, placement == "interleaved")
+            assert torch.equal(exs[p].all_idx, local if flags else idx)
+            assert torch.equal(exs[p].all_w, w)
+            pushed = (local >= 0).any(dim=1)
+            assert torch.equal(exs[p].all_x[pushed], x_want[pushed])
+            assert (exs[p].all_x[~pushed].view(torch.int16) == -1).all()      # never written: still the fill pattern
+
+
 def _peer_worker(rank, world, port, results):
     import traceback
     try:
