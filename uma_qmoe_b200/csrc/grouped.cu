@@ -77,7 +77,8 @@ struct TileInfo {
 template <int ENC, int MODE>
 __global__ void __launch_bounds__(kGemmThreads + kGatherThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
-                    const __grid_constant__ CUtensorMap map_b1, const GroupedParams p) {
+                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_out,
+                    const GroupedParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // layout: [A stages][packed stages][B stages][2 x scales][control]
   constexpr int kPackedRow = ENC == ENC_Q4 ? BK / 2 : BK;               // bytes of codes per row and k chunk
@@ -91,7 +92,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   float* sScales = reinterpret_cast<float*>(sB + kNumB * kBTile);
   GemmShared& sh = *reinterpret_cast<GemmShared*>(reinterpret_cast<uint8_t*>(sScales) + 2 * BN * kMaxGroups * 4);
   // The down GEMM of a quantised layer stages its results in shared memory (BF16 weight stages are TMA-fed across
-  // tiles and never idle; the gate/up GEMM writes half as much and measured faster with direct stores).
+  // tiles and never idle; the gate/up GEMM writes half as much per tile and measured slower staged, with plain
+  // stores out of the staging area (0.495 against 0.485 ms) and with tensor stores (0.499)).
   constexpr bool kStaged = ENC != ENC_BF16 && MODE == 1;
   static_assert(kBStages >= 2 && kBTile >= kConvertWarps * 4096, "epilogue staging lives in two converted stages");
 
@@ -437,6 +439,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               }
               if (kStaged) {
                 // two chunks = 32 rows x 128 B per piece, pieces in turn: 16-byte slot q of row r at r*128 + ((q ^ r&7) << 4)
+                if (!(c & 1)) {                              // the piece's previous tensor store has read it
+                  if (lane == 0) bulk_wait_read<1>();
+                  __syncwarp();
+                }
                 uint8_t* piece = stage_piece_of((c >> 1) & 1) + lane * 128;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
@@ -450,10 +456,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               }
             }
             if (kStaged && (c & 1)) {
-              // a piece is full: eight lanes write one row's 128 contiguous bytes, four rows per instruction.  The
-              // __syncwarp before the other piece's flush also orders these reads before this piece's next writes.
+              // A piece is full.  A whole group of 32 rows leaves by one tensor store (asynchronous: the warp goes on
+              // with the next chunks while the copy engine reads the piece); a ragged group by plain stores, eight
+              // lanes writing one row's 128 contiguous bytes, four rows per instruction.  One bulk group per piece
+              // either way, so that "at most one group pending" always means the piece about to be written is free.
+              const int group_row = (c >> 2) * BM + quarter * 32;
+              const bool by_tma = p.tma_out && group_row + 32 <= t.nrows && !(p.debug & 4);
+              if (by_tma) fence_proxy_async();               // this lane's staging writes -> visible to the copy engine
               __syncwarp();
-              if (!(p.debug & 3)) {
+              if (by_tma) {
+                if (lane == 0) {
+                  if (!(p.debug & 3))
+                    tma_store_2d(&map_out, f0 + ch * 128 + ((c & 3) >> 1) * 64, t.row0 + group_row, stage_piece_of((c >> 1) & 1));
+                  bulk_commit();
+                }
+              } else if (lane == 0) {
+                bulk_commit();
+              }
+              if (!by_tma && !(p.debug & 3)) {
                 const int q = lane & 7;
                 const uint8_t* piece = stage_piece_of((c >> 1) & 1);
                 __nv_bfloat16* dst = p.out + f0 + ch * 128 + ((c & 3) >> 1) * 64 + q * 8;
@@ -470,10 +490,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           }
         }
-        if (kStaged) __syncwarp();                           // before this warp's next conversion overwrites its rows
+        if (kStaged) {                                       // before this warp's next conversion overwrites its rows
+          if (lane == 0) bulk_wait_read<0>();                // (waiting for the last store one k step later measured the same)
+          __syncwarp();
+        }
       }
     }
   }
+  if (kStaged && warp >= 2 && warp < 2 + kConvertWarps && lane == 0) bulk_wait_all();   // this thread's tensor stores
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -492,7 +516,7 @@ constexpr size_t gemm_smem_bytes() {
 
 template <int ENC, int MODE>
 int launch_one(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1,
-               int n_tiles, cudaStream_t stream) {
+               const CUtensorMap& mo, int n_tiles, cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<ENC, MODE>;
   constexpr size_t smem = gemm_smem_bytes<ENC>();
   static thread_local int configured = -1;
@@ -504,7 +528,7 @@ int launch_one(const GroupedParams& p, const CUtensorMap& ma, const CUtensorMap&
     configured = dev;
   }
   (void)n_tiles;
-  kernel<<<dim3(sm_count()), kGemmThreads + (MODE == 0 && p.gather_route ? kGatherThreads : 0), smem, stream>>>(ma, mb0, mb1, p);
+  kernel<<<dim3(sm_count()), kGemmThreads + (MODE == 0 && p.gather_route ? kGatherThreads : 0), smem, stream>>>(ma, mb0, mb1, mo, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("grouped: launch failed: %s", cudaGetErrorString(e)); return ERR_LAUNCH; }
   return ERR_NONE;
@@ -540,13 +564,13 @@ int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
   }
   if (a.gather_route && (a.mode != 0 || a.gather_top_k < 1)) { set_error("grouped: rows are fetched by index only for the gate/up GEMM"); return ERR_BAD_ARGUMENT; }
   // with rows fetched by index `act` is [tokens, k] and the kernel never uses the activation map: any valid map will do
-  CUtensorMap ma, mb0, mb1;
+  CUtensorMap ma, mb0, mb1, mo;
   if (!make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.act, (uint64_t)K, (uint64_t)(a.gather_route ? BM : a.total_rows), BK, BM,
                 CU_TENSOR_MAP_SWIZZLE_128B))
     return ERR_LAUNCH;
   const uint64_t wrows = (uint64_t)a.num_experts * a.n_rows;
   const uint32_t box_rows = a.mode == 0 ? BN / 2 : BN;
-  bool ok;
+  bool ok, tma_out = false;
   if (a.enc == ENC_BF16) {
     ok = make_map(&mb0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.w0, (uint64_t)K, wrows, BK, box_rows, CU_TENSOR_MAP_SWIZZLE_128B) &&
          make_map(&mb1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.mode == 0 ? a.w1 : a.w0, (uint64_t)K, wrows, BK, box_rows,
@@ -557,7 +581,14 @@ int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
     ok = make_map(&mb0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w0, rowb, wrows, boxb, box_rows, CU_TENSOR_MAP_SWIZZLE_NONE) &&
          make_map(&mb1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.mode == 0 ? a.w1 : a.w0, rowb, wrows, boxb, box_rows,
                   CU_TENSOR_MAP_SWIZZLE_NONE);
+    // the epilogue's tensor stores of 32 rows x 64 columns need a dense [total_rows, n_rows] BF16 output at a 16-byte
+    // boundary; any other output is written with plain stores
+    tma_out = a.mode == 1 && a.out_stride == a.n_rows && !(reinterpret_cast<uintptr_t>(a.out) & 15);
+    if (ok && tma_out)
+      ok = make_map(&mo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out, (uint64_t)a.n_rows, (uint64_t)a.total_rows, 64, 32,
+                    CU_TENSOR_MAP_SWIZZLE_128B);
   }
+  if (!tma_out) mo = ma;                                   // never used: any valid map
   if (!ok) return ERR_LAUNCH;
   GroupedParams p{};
   p.k = K; p.n_rows = a.n_rows;
@@ -566,11 +597,12 @@ int launch_grouped_gemm_single(const GroupedGemmArgs& a, cudaStream_t stream) {
   p.max_tiles = a.max_tiles;
   p.out = a.out; p.out_stride = a.out_stride; p.route_weight = a.route_weight; p.permute_out = a.permute_out;
   { static const int dbg = [] { const char* v = std::getenv("UMAQ_GEMM_DEBUG"); return v ? std::atoi(v) : 0; }(); p.debug = dbg; }
+  p.tma_out = tma_out;
   p.status = a.status;
   p.gather_route = a.gather_route; p.gather_top_k = a.gather_top_k; p.gather_src = static_cast<const __nv_bfloat16*>(a.act);
   const int n_tiles = a.n_rows / (a.mode == 0 ? BN / 2 : BN);
 #define UMAQ_DISPATCH(E)                                                                       \
-  return a.mode == 0 ? launch_one<E, 0>(p, ma, mb0, mb1, n_tiles, stream) : launch_one<E, 1>(p, ma, mb0, mb1, n_tiles, stream)
+  return a.mode == 0 ? launch_one<E, 0>(p, ma, mb0, mb1, mo, n_tiles, stream) : launch_one<E, 1>(p, ma, mb0, mb1, mo, n_tiles, stream)
   if (a.enc == ENC_Q4) { UMAQ_DISPATCH(ENC_Q4); }
   if (a.enc == ENC_Q8) { UMAQ_DISPATCH(ENC_Q8); }
   if (a.enc == ENC_BF16) { UMAQ_DISPATCH(ENC_BF16); }

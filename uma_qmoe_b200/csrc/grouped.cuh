@@ -31,6 +31,7 @@ struct GroupedParams {
   int gather_top_k;
   const __nv_bfloat16* gather_src;
   int debug;
+  int tma_out;                // mode 1, staged results: map_b1 describes `out` and whole 32-row groups leave by tensor store
 };
 
 struct GroupedGemmArgs {
