@@ -7,7 +7,9 @@ layers (hidden 2048, 64 experts, top-8 renormalised, intermediate 1024, W4A16 gr
 the fused router, the expert-parallel dispatch (N > 1), the grouped-GEMM pipeline and the ordered
 combine; the output of a layer, renormalised to unit RMS, is the input of the next.  Weights are
 seeded synthetic (no checkpoint); the 3.4 GB of packed weights exceed L2, so every step streams them
-from HBM.  With N ranks the experts and the tokens are split N ways (strong scaling).
+from HBM.  With N ranks the experts and the tokens are split N ways (strong scaling); from 4 ranks on a rank's
+tokens run as two independent micro-batches on streams of their own (UMAQ_EP_PARTS), one's experts under the
+other's exchange.
 
 One JSON line on rank 0.  `value` = tokens/s with inputs resident on the device; `e2e` = the same
 through torch.ops.uma_qmoe.moe_forward with every step's activations coming from pinned host memory
@@ -52,7 +54,7 @@ CAPTURES = {
     # few per cent of them L2 hits) plus the 2048 activation rows (8.4 MB); the write is the intermediate
     "gemm_gate_up": {"tokens": 2048, "read": 139.4e6, "write": 19.2e6},
     # down GEMM: weights 71.3 MB + the intermediate rows it reads; the write is the weighted per-route output
-    "gemm_down": {"tokens": 2048, "read": 98.4e6, "write": 28.5e6, "weights": 64 * (2048 * 512 + 2048 * 8 * 4)},
+    "gemm_down": {"tokens": 2048, "read": 98.4e6, "write": 31.8e6, "weights": 64 * (2048 * 512 + 2048 * 8 * 4)},
 }
 
 
