@@ -263,6 +263,18 @@ int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, 
                               int indices_are_int64, const float* routing_weights, long long tokens, int top_k,
                               const umaq_ep_peers* peers, size_t parts_offset, int segment_rows, int rows_k_permuted,
                               void* workspace, size_t workspace_bytes, void* stream);
+/* One expert-parallel layer over this rank's tokens from a single host call: umaq_ep_push (with both flags) ->
+ * umaq_ep_barrier -> umaq_moe_prefill_to_peers over the rows that arrived -> umaq_ep_barrier ->
+ * umaq_combine_routes over the partial sums (part_pos[i*ranks + p] = p*tokens + i), the five launches' arguments
+ * being the ones documented above (offsets inside every rank's buffer; present [tokens, ranks]; epoch and status
+ * device words, zero at start).  The workspace is umaq_prefill_workspace_bytes(tokens*ranks, top_k, local experts, ...).
+ * A host whose launch calls are slow (an interpreter, several ranks sharing the cores) spends one call, not five. */
+int umaq_ep_layer(const umaq_layer* layer, const void* hidden_bf16, const void* expert_indices, int indices_are_int64,
+                  const float* routing_weights, int tokens, int top_k, int experts_per_rank, int placement,
+                  const umaq_ep_peers* peers, size_t rows_offset, size_t ids_offset, size_t weights_offset,
+                  size_t parts_offset, size_t flags_offset, int* present, const int* part_pos, unsigned* epoch,
+                  unsigned* status, void* workspace, size_t workspace_bytes, void* out_bf16 /* [tokens, hidden] */,
+                  void* stream);
 /* out[t] = BF16 running sum of weighted[route_pos[t*top_k+s]] over the token's routes in
  * ascending expert order: the accumulation order of the reference's CPU path
  * (src/uma_qmoe/custom_op.py:312-338), in place of

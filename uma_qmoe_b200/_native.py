@@ -75,6 +75,10 @@ SIGNATURES = {
     "umaq_moe_prefill_to_peers": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_longlong,
                                             C.c_int, C.POINTER(EpPeers), C.c_size_t, C.c_int, C.c_int, C.c_void_p,
                                             C.c_size_t, C.c_void_p]),
+    "umaq_ep_layer": (C.c_int, [C.POINTER(Layer), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                C.c_int, C.POINTER(EpPeers), C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
+                                C.c_void_p]),
     "umaq_combine_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                       C.c_void_p, C.c_void_p]),
     "umaq_quantize_groups": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),

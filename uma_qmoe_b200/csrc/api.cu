@@ -424,4 +424,35 @@ int umaq_moe_prefill_to_peers(const umaq_layer* layer, const void* hidden_bf16, 
                       nullptr, workspace, workspace_bytes, stream_, &seg, rows_k_permuted != 0);
 }
 
+int umaq_ep_layer(const umaq_layer* layer, const void* hidden_bf16, const void* expert_indices, int indices_are_int64,
+                  const float* routing_weights, int tokens, int top_k, int experts_per_rank, int placement,
+                  const umaq_ep_peers* peers, size_t rows_offset, size_t ids_offset, size_t weights_offset,
+                  size_t parts_offset, size_t flags_offset, int* present, const int* part_pos, unsigned* epoch,
+                  unsigned* status, void* workspace, size_t workspace_bytes, void* out_bf16, void* stream) {
+  if (!layer || !peers || !part_pos || !epoch || !status || !out_bf16) {
+    set_error("umaq_ep_layer: null argument");
+    return ERR_BAD_ARGUMENT;
+  }
+  if (peers->ranks < 1 || peers->ranks > kMaxPeers || peers->rank < 0 || peers->rank >= peers->ranks ||
+      !peers->base[peers->rank]) {
+    set_error("umaq_ep_layer: bad peer table");
+    return ERR_BAD_ARGUMENT;
+  }
+  const int quant = layer->encoding != ENC_BF16;
+  int rc = umaq_ep_push(hidden_bf16, expert_indices, indices_are_int64, routing_weights, tokens, top_k, layer->hidden,
+                        experts_per_rank, placement, UMAQ_EP_LOCAL_IDS | (quant ? UMAQ_EP_K_PERMUTED : 0), peers,
+                        rows_offset, ids_offset, weights_offset, present, stream);
+  if (rc) return rc;
+  rc = umaq_ep_barrier(peers, flags_offset, epoch, status, stream);
+  if (rc) return rc;
+  uint8_t* mine = static_cast<uint8_t*>(peers->base[peers->rank]);
+  rc = umaq_moe_prefill_to_peers(layer, mine + rows_offset, mine + ids_offset, 0,
+                                 reinterpret_cast<const float*>(mine + weights_offset), (long long)tokens * peers->ranks,
+                                 top_k, peers, parts_offset, tokens, quant, workspace, workspace_bytes, stream);
+  if (rc) return rc;
+  rc = umaq_ep_barrier(peers, flags_offset, epoch, status, stream);
+  if (rc) return rc;
+  return umaq_combine_routes(mine + parts_offset, present, 0, part_pos, tokens, peers->ranks, layer->hidden, out_bf16, stream);
+}
+
 }  // extern "C"

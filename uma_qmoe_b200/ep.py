@@ -103,6 +103,16 @@ class CudaKernels:
         self.ops.moe_prefill_to_peers(self.layer, x, local_indices, weights, ex.peers, ex.off_parts, ex.tokens, self._ws_moe,
                                       rows_k_permuted=self.rows_k_permuted)
 
+    def peer_layer(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, ex: Any, per_rank: int,
+                   interleaved: bool) -> torch.Tensor:
+        """The whole peer-memory layer (push, barrier, local experts + combine to the owners, barrier, final combine)
+        issued by one native call: five launches' worth of host work for the price of one."""
+        n, top_k = ex.tokens * ex.peers.ranks, indices.shape[1]
+        if self._ws_moe is None or self._ws_moe_shape != (n, top_k):
+            self._ws_moe = self.ops.prefill_workspace(self.layer, n, top_k, None, x.device)
+            self._ws_moe_shape = (n, top_k)
+        return self.ops.ep_layer(self.layer, x, indices, weights, per_rank, interleaved, ex, self._ws_moe)
+
     def local_moe(self, x: torch.Tensor, local_indices: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """This rank's experts over all rows of x; local_indices -1 = the route belongs to another rank."""
         n, top_k = local_indices.shape
@@ -298,6 +308,8 @@ class ExpertParallelMoE:
         """Same result contract as :meth:`forward_gather`, with the two exchanges done by this library's own
         kernels over peer memory: rows travel only to ranks that own one of the token's experts, partial sums
         only back from ranks that did some work, and the only synchronisation is a flag barrier per phase."""
+        if hasattr(self.kernels, "peer_layer") and x.is_contiguous() and indices.is_contiguous() and weights.is_contiguous():
+            return self.kernels.peer_layer(x, indices, weights, ex, self.per_rank, self.placement == "interleaved")
         ops = self.kernels.ops
         self.peer_push(ex, x, indices, weights)
         ops.ep_barrier(ex.peers, ex.off_flags, ex.epoch, ex.status)

@@ -327,6 +327,28 @@ def moe_prefill_to_peers(layer: DeviceLayer, hidden: torch.Tensor, local_indices
     _native.check(code, "umaq_moe_prefill_to_peers")
 
 
+def ep_layer(layer: DeviceLayer, hidden: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor, experts_per_rank: int,
+             interleaved: bool, ex, workspace: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One expert-parallel layer over the local tokens through the peer-memory exchange ``ex`` (a
+    :class:`uma_qmoe_b200.ep.PeerExchange`): push, barrier, local experts with the combine writing to the owners,
+    barrier, final combine — all issued by one native call (``umaq_ep_layer``)."""
+    _require_cuda_bf16(hidden, "hidden_states")
+    tokens, top_k = indices.shape
+    if weights.dtype != torch.float32 or weights.shape != indices.shape or indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("routes must be int32/int64 indices and float32 weights of one shape")
+    if tokens != ex.tokens or not hidden.is_contiguous() or not indices.is_contiguous() or not weights.is_contiguous():
+        raise RuntimeError("ep_layer takes contiguous tensors of the exchange's token count")
+    if out is None:
+        out = torch.empty_like(hidden)
+    code = _native.lib().umaq_ep_layer(
+        C.byref(layer.struct()), hidden.data_ptr(), indices.data_ptr(), int(indices.dtype == torch.int64), weights.data_ptr(),
+        tokens, top_k, experts_per_rank, 0 if interleaved else 1, C.byref(ex.peers), ex.off_rows, ex.off_ids, ex.off_w,
+        ex.off_parts, ex.off_flags, ex.present.data_ptr(), ex.part_pos.data_ptr(), ex.epoch.data_ptr(), ex.status.data_ptr(),
+        workspace.data_ptr(), workspace.numel(), out.data_ptr(), _stream(hidden.device))
+    _native.check(code, "umaq_ep_layer")
+    return out
+
+
 def combine_routes(weighted: torch.Tensor, indices: torch.Tensor, route_pos: torch.Tensor,
                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Ordered BF16 top-k combine of per-route weighted outputs."""
