@@ -183,6 +183,30 @@ def test_push_prepares_the_receivers_input(placement):
             assert (exs[p].all_x[~pushed].view(torch.int16) == -1).all()      # never written: still the fill pattern
 
 
+def test_layer_call_with_one_rank_equals_the_plain_prefill():
+    """``umaq_ep_layer`` (push, barrier, local experts, barrier, final combine from one native call) with a single
+    rank: every route is local, the barriers signal and wait for the rank's own flag word, and a one-term BF16 sum is
+    the plain operator's result bit for bit.  Called twice: the epoch counts on, nothing is reset between layers."""
+    from uma_qmoe_b200.ep import CudaKernels, ExpertParallelMoE, PeerExchange
+    full, _ = _rank_layers(1, "interleaved")
+    top_k, t = 4, 70
+    gen = torch.Generator().manual_seed(SEED + 307)
+    idx = torch.multinomial(torch.ones(t, 8), top_k, replacement=False, generator=gen).to(DEV)
+    w = (torch.rand((t, top_k), generator=gen, dtype=torch.float32) / top_k).to(DEV)
+    x = syn.activations(SEED + 308, t).to(DEV)
+    want = _plain(full, x, idx, w)
+    buffers = [torch.full((PeerExchange.nbytes_for(t, 2048, top_k, 1),), 0xFF, dtype=torch.uint8, device=DEV)]
+    buffers[0][-256:] = 0                                       # the flag words start at zero
+    ex = PeerExchange(t, 2048, top_k, 0, 1, torch.device(DEV), buffers=buffers)
+    ep = ExpertParallelMoE(CudaKernels(full, top_k), 8, top_k, world=1, rank=0)
+    for _ in range(2):
+        got = ep.forward_peer(ex, x, idx, w)
+        torch.cuda.synchronize()
+        assert not ex.timed_out()
+        assert torch.equal(got, want)
+    assert int(ex.epoch.item()) == 4
+
+
 def _peer_worker(rank, world, port, results):
     import traceback
     try:
