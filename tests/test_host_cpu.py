@@ -30,6 +30,16 @@ def test_library_loads_without_a_gpu_and_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in include/umaq_b200.h but not exported"
 
 
+def test_header_constants_match_the_python_side():
+    """The flag and error values the Python wrappers pass are the ones the header defines."""
+    from uma_qmoe_b200 import ops
+    text = (ROOT / "include" / "umaq_b200.h").read_text()
+    defines = {name: int(value) for name, value in re.findall(r"^#define\s+(UMAQ_[A-Z0-9_]+)\s+(-?\d+)\s*$", text, flags=re.M)}
+    assert defines["UMAQ_EP_LOCAL_IDS"] == ops.EP_LOCAL_IDS
+    assert defines["UMAQ_EP_K_PERMUTED"] == ops.EP_K_PERMUTED
+    assert ops.EP_LOCAL_IDS & ops.EP_K_PERMUTED == 0
+
+
 def test_build_info_names_the_target_and_the_source_digest():
     from uma_qmoe_b200 import build
     lib = _native.lib()
