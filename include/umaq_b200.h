@@ -193,7 +193,9 @@ int umaq_gather_rows(const void* hidden_bf16, const int* sorted_route, int top_k
  * tile kernels at src/uma_qmoe/native/packed_q4_kernel.cu:560-776 and :894-1099.
  * variant: 0 = the library picks (CTA pairs for BF16 weights on 16,384 routes or more, one-CTA tiles
  * otherwise), 1 = persistent one-CTA tiles, 2 = persistent CTA pairs (tcgen05 cta_group::2; same tiles,
- * slower on B200 for the quantised encodings). */
+ * slower on B200 for the quantised encodings).  out is a dense [total_rows, I or H] BF16 matrix; the
+ * mode-1 kernel of a quantised layer writes it with tensor stores when it starts on a 16-byte boundary,
+ * with plain stores otherwise (same bytes either way). */
 int umaq_grouped_gemm(const umaq_layer* layer, int mode, const void* act_bf16, long long total_rows,
                       const int* num_tiles, const int* tile_table, int max_tiles, const float* route_weight,
                       int permute_out, void* out_bf16, unsigned* status, int variant, void* stream);
