@@ -123,6 +123,13 @@ def _worker(rank: int, world: int, port: int, out, placement: str, fixed):
         if fixed is None:
             y = ep.forward(x[sl], idx[sl], w[sl])
             dropped = False
+        elif fixed == "micro":
+            # a rank's tokens as two independent micro-batches, one after the other: the same collectives in the same
+            # order on every rank, and the same result as one batch because tokens never interact
+            half = share // 2
+            xs, ids, ws = x[sl], idx[sl], w[sl]
+            y = torch.cat([ep.forward(xs[:half], ids[:half], ws[:half]), ep.forward(xs[half:], ids[half:], ws[half:])])
+            dropped = False
         elif fixed == "gather":
             y = ep.forward_gather(x[sl], idx[sl], w[sl])
             dropped = False
@@ -167,6 +174,12 @@ def _run(placement, fixed, world=2):
 @pytest.mark.parametrize("placement", ["interleaved", "contiguous"])
 def test_two_rank_exchange_matches_single_rank(placement):
     got, _ = _run(placement, None)
+    assert np.array_equal(got, _single_rank().float().numpy())
+
+
+@pytest.mark.timeout(120)
+def test_micro_batches_of_a_rank_give_the_result_of_one_batch():
+    got, _ = _run("interleaved", "micro")
     assert np.array_equal(got, _single_rank().float().numpy())
 
 
